@@ -1,0 +1,181 @@
+/*
+ * qt_b200.h -- C ABI of the B200 (sm_100a) quantize + scaled low-precision GEMM library.
+ *
+ * Every entry point takes plain device pointers, sizes, strides (in ELEMENTS) and a CUDA
+ * stream handle (a cudaStream_t passed as void*; NULL = the legacy default stream). Nothing
+ * here allocates device memory unless its comment says so; all launches are asynchronous on
+ * the given stream. A return value of 0 means the work was enqueued; any other value is an
+ * error code (QT_ERR_*) and qt_last_error() holds a human-readable message for the calling
+ * thread. Pointers are borrowed for the duration of the enqueued work.
+ *
+ * The "replaces" notes cite the gau-nernst/quantized-training source (path:line inside that
+ * project) whose behaviour the entry point reproduces.
+ */
+#ifndef QT_B200_H
+#define QT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums ------------------------------------------------------------------------------ */
+
+/* element types of tensors crossing the boundary */
+enum {
+    QT_BF16 = 0,    /* bfloat16 */
+    QT_F32 = 1,     /* float    */
+    QT_I8 = 2,      /* int8     */
+    QT_E4M3 = 3,    /* float8 e4m3fn (finite, no inf; max 448) */
+    QT_E5M2 = 4,    /* float8 e5m2   */
+    QT_I32 = 5,     /* int32    */
+    QT_F16 = 6      /* half     */
+};
+
+/* error codes */
+enum {
+    QT_OK = 0,
+    QT_ERR_INVALID = 1,     /* bad argument: shape, stride, alignment, dtype      */
+    QT_ERR_CUDA = 2,        /* a CUDA runtime / driver call failed                */
+    QT_ERR_UNSUPPORTED = 3, /* valid request outside what the kernels implement   */
+    QT_ERR_DEVICE = 4       /* a kernel reported a bounded wait that ran out      */
+};
+
+/* ---- library -------------------------------------------------------------------------------- */
+
+/* Message of the last error on the calling thread ("" if none). Never NULL. */
+const char* qt_last_error(void);
+
+/* Library version, e.g. "qt_b200 0.1 sm_100a". */
+const char* qt_version(void);
+
+/*
+ * Reads and clears the device-side status word of the current device (synchronises the
+ * device). 0 = no kernel has given up on a bounded wait since the last call. Non-zero values
+ * encode (role << 8 | barrier id) of the wait that ran out.
+ */
+int qt_device_status(int* status_out);
+
+/* ---- piece 1: absmax quantize ----------------------------------------------------------- */
+
+/*
+ * Row-wise symmetric absmax quantize.
+ *   scale[r]  = max_c |x[r,c]| / qmax            (fp32 math; qmax = 127 for QT_I8, 448 for QT_E4M3)
+ *   q[r,c]    = cast(round(x[r,c] / max(scale[r], eps)))   clamped to [-128,127] (int8) or [-448,448]
+ * round = round-half-to-even, or floor(v + u) with u ~ U[0,1) from Philox4x32-10 keyed by
+ * (seed, offset) when stochastic != 0 (int8 only).
+ * x: [rows, cols], element (r,c) at x + r*x_row_stride + c, dtype x_dtype (QT_BF16 | QT_F32).
+ * q: [rows, cols] contiguous. scale: [rows] of scale_dtype (QT_BF16 | QT_F32) -- the value
+ * stored is the UNCLAMPED scale rounded to scale_dtype.
+ * replaces: subclasses/int8.py:12-26 (quantize_int8 with dim=-1).
+ */
+int qt_quantize_rowwise(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                        void* q, int q_dtype, void* scale, int scale_dtype, float eps,
+                        int stochastic, uint64_t seed, uint64_t offset, void* stream);
+
+/*
+ * Same as qt_quantize_rowwise and, in the same pass over x, the per-column absolute maximum
+ * col_absmax[c] = max_r |x[r,c]| (fp32, [cols]). col_absmax is zeroed by this call (on the
+ * stream) before the kernel runs. Lets a later qt_quantize_colwise_t skip its reduction pass.
+ * replaces: the pair of quantize_int8 calls on one activation in
+ * subclasses/mixed_precision.py:100-108,147-193 (row-wise in forward, column-wise in backward).
+ */
+int qt_quantize_rowwise_colabsmax(const void* x, int x_dtype, int64_t rows, int64_t cols,
+                                  int64_t x_row_stride, void* q, int q_dtype, void* scale,
+                                  int scale_dtype, float* col_absmax, float eps, int stochastic,
+                                  uint64_t seed, uint64_t offset, void* stream);
+
+/*
+ * Per-column absolute maximum: col_absmax[c] = max_r |x[r,c]| (fp32, [cols]); zeroed first.
+ * replaces: the amax reduction of quantize_int8(x.T, dim=1), subclasses/int8.py:16.
+ */
+int qt_col_absmax(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                  float* col_absmax, void* stream);
+
+/*
+ * Column-wise quantize with the transpose materialised: for x [rows, cols],
+ *   scale[c] = col_absmax[c] / qmax ; qt[c, r] = cast(round(x[r,c] / max(scale[c], eps)))
+ * qt: [cols, rows] contiguous; scale: [cols]. col_absmax must hold the per-column absmax of x
+ * (from qt_col_absmax or qt_quantize_rowwise_colabsmax).
+ * The Philox counter of element (r,c) is that of the transposed element index c*rows + r, so
+ * stochastic results equal qt_quantize_rowwise applied to a materialised transpose.
+ * replaces: quantize_int8(B.T, sr, dim=1) followed by .contiguous(),
+ * subclasses/mixed_precision.py:102-105.
+ */
+int qt_quantize_colwise_t(const void* x, int x_dtype, int64_t rows, int64_t cols,
+                          int64_t x_row_stride, const float* col_absmax, void* qt, int q_dtype,
+                          void* scale, int scale_dtype, float eps, int stochastic, uint64_t seed,
+                          uint64_t offset, void* stream);
+
+/*
+ * Tile-wise absmax quantize: one scale per (tile_r x tile_c) tile of x [rows, cols];
+ * scale is [ceil(rows/tile_r), ceil(cols/tile_c)] contiguous. tile_r in {1, 128}, tile_c = 128
+ * (1x128 activations, 128x128 weights). Round-half-to-even only.
+ * replaces: no function in the reference (its benchmark draws tile scales at random,
+ * benchmark_mm.py:87-89); the arithmetic is quantize_int8's (subclasses/int8.py:15-25) per tile.
+ */
+int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                     int tile_r, int tile_c, void* q, int q_dtype, void* scale, int scale_dtype,
+                     float eps, void* stream);
+
+/* ---- piece 2: tcgen05 GEMMs ----------------------------------------------------------------- */
+
+/*
+ * Operand addressing for all GEMMs: A is [M,K] with element (m,k) at a + m*a_sm + k*a_sk and B is
+ * [K,N] with element (k,n) at b + k*b_sk + n*b_sn. Exactly one stride of each operand must be 1:
+ *   a_sk == 1 : A row-major (K-major)        a_sm == 1 : A column-major (M-major)
+ *   b_sk == 1 : B column-major (K-major)     b_sn == 1 : B row-major (N-major)
+ * so A@B.T is (a_sk=1,b_sk=1), A@B is (a_sk=1,b_sn=1), A.T@B is (a_sm=1,b_sn=1).
+ * The non-unit stride must be a multiple of 16 and the base pointers 16-byte aligned (TMA).
+ * C is [M,N] row-major with row stride ldc (elements).
+ */
+
+/*
+ * C(int32) = A(int8) @ B(int8), exact.
+ * replaces: gn_kernels int8_mm, kernels/gn_kernels/triton_mm.py:112-128 (_matmul_kernel :53-109).
+ */
+int qt_int8_mm(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn,
+               int32_t* c, int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
+ * C = cast( (fp32(A @ B) * scale_a[m]) * scale_b[n] ) with A, B both int8 (int32 accumulate) or
+ * both fp8 (ab_dtype QT_E4M3 / QT_E5M2 per operand, fp32 accumulate). scale_a: [M]; scale_b: [N],
+ * or one element when scale_b_is_scalar != 0. Scales and C share scale_dtype (QT_BF16 | QT_F32).
+ * replaces: gn_kernels scaled_mm, kernels/gn_kernels/triton_mm.py:345,349-373,382-407
+ * (_scaled_mm_kernel :146-220).
+ */
+int qt_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype,
+                 int64_t b_sk, int64_t b_sn, const void* scale_a, const void* scale_b,
+                 int scale_b_is_scalar, int scale_dtype, void* c, int64_t ldc, int64_t M, int64_t N,
+                 int64_t K, void* stream);
+
+/*
+ * Tile-scaled GEMM: for each block kb of qk reduction elements
+ *   acc[m,n] += fp32(A[m,kb] @ B[kb,n]) * scale_a[m/qm, kb] * scale_b[kb, n/qn]
+ * scale_a: [ceil(M/qm), K/qk] with strides (sa_s0, sa_s1); scale_b: [K/qk, ceil(N/qn)] with strides
+ * (sb_s0, sb_s1). Supported: qk = 128, qm in {1, 128}, qn in {1, 128}; K % 128 == 0.
+ * replaces: gn_kernels tile_scaled_mm, kernels/gn_kernels/triton_mm.py:346,410-441
+ * (_tile_scaled_mm_kernel :223-342).
+ */
+int qt_tile_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b,
+                      int b_dtype, int64_t b_sk, int64_t b_sn, const void* scale_a, int64_t sa_s0,
+                      int64_t sa_s1, const void* scale_b, int64_t sb_s0, int64_t sb_s1, int qm, int qn,
+                      int qk, int scale_dtype, void* c, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                      void* stream);
+
+/* ---- self-tests ------------------------------------------------------------------------------ */
+
+/*
+ * Exhaustive check of the quantize kernels' bf16 division (correctly rounded reciprocal + one
+ * fused correction) against IEEE division, over every finite bf16 absmax a >= 0 and every bf16 x
+ * with |x| <= a, for d = max(a / qmax(q_dtype), eps). mismatches[0] = quotients that differ in any
+ * bit, mismatches[1] = quantized bytes that differ. Allocates 16 bytes of device memory and
+ * synchronises the device. Test utility; no counterpart in the reference.
+ */
+int qt_selftest_division(int q_dtype, float eps, unsigned long long* mismatches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QT_B200_H */

@@ -1,0 +1,553 @@
+// tcgen05 GEMMs for sm_100a: int8 x int8 -> int32 (kind::i8) and fp8 x fp8 -> fp32 (kind::f8f6f4),
+// with raw, row/column-scaled and tile-scaled epilogues.
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0      TMA producer   global -> 128B-swizzled shared-memory stages (cp.async.bulk.tensor)
+//   warp 1      MMA issuer     one elected lane issues tcgen05.mma; accumulators live in TMEM
+//   warps 2..5  epilogue       tcgen05.ld TMEM -> registers -> scale -> global
+// The accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of tile i overlaps
+// the main loop of tile i+1. Stages and accumulators are handed over through mbarriers; every wait
+// is bounded and reports through the device status word instead of spinning forever.
+//
+// Operand layouts: both operands may be K-major or MN-major in global memory; MN-major tiles are
+// fetched as [K][128 B of M or N] boxes and described to the tensor core as MN-major, so A@B.T,
+// A@B and A.T@B run without any transpose pass. No TMA multicast is used anywhere.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace qt {
+
+namespace {
+
+// ---- tile configuration ---------------------------------------------------------------------
+
+constexpr int BM = 128;      // tile rows  (= UMMA M, one TMEM lane per row)
+constexpr int BN = 256;      // tile cols  (= UMMA N, one TMEM column per col)
+constexpr int BK = 128;      // reduction elements per stage (8-bit => 128 bytes = one swizzle row)
+constexpr int UMMA_K = 32;   // reduction elements per tcgen05.mma for 8-bit operands
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK;                 // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK;                 // 32 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int NUM_EPI_THREADS = 128;
+constexpr int TMEM_COLS = 512;                         // 2 accumulators x BN fp32/int32 columns
+constexpr int GROUP_M = 8;                             // rasterisation: 8 row-tiles share B panels in L2
+
+// shared memory carve-up (offsets from a 1024-byte aligned base)
+constexpr int SMEM_STAGES_OFF = 0;
+constexpr int SMEM_COLSCALE_OFF = STAGES * STAGE_BYTES;             // float [4 epilogue warps][BN]
+constexpr int SMEM_BAR_OFF = SMEM_COLSCALE_OFF + 4 * BN * 4;        // mbarriers
+constexpr int NUM_BARRIERS = 2 * STAGES + 4;
+constexpr int SMEM_TMEMPTR_OFF = SMEM_BAR_OFF + NUM_BARRIERS * 8;
+constexpr int SMEM_ABORT_OFF = SMEM_TMEMPTR_OFF + 4;
+constexpr int SMEM_TOTAL = SMEM_ABORT_OFF + 4 + 1024;               // + alignment slack
+
+constexpr uint32_t WAIT_LIMIT = 1u << 26;  // polls before a wait gives up (seconds, not minutes)
+
+enum Epilogue { EPI_RAW = 0, EPI_ROWCOL = 1, EPI_TILE = 2 };
+
+struct GemmParams {
+    int64_t M, N, K;
+    void* c;
+    int64_t ldc;
+    const void* scale_a;
+    const void* scale_b;
+    int scale_b_is_scalar;
+    int scale_dtype;  // QT_BF16 | QT_F32 ; also the output dtype of scaled epilogues
+    // tile-scaled only
+    int64_t sa_s0, sa_s1, sb_s0, sb_s1;
+    int qm, qn;
+    int* status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait. Returns false (and records `code`) when the limit is hit or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int KIND>  // 0 = i8, 1 = f8f6f4
+__device__ __forceinline__ void tcgen05_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (KIND == 0) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base lane + t).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- descriptors ----------------------------------------------------------------------------
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+//   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4   bits [46,48) version = 1     bits [61,64) layout = 2 (SW128)
+// K-major tile ([rows][128 B of K]): 8-row groups are 1024 B apart (SBO); LBO unused (1).
+// MN-major tile ([K][128 B of M/N]): 8-k groups are 1024 B apart (SBO); the next 128-wide M/N
+// chunk starts LBO bytes later.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor (kind::i8 / kind::f8f6f4 / kind::f16 share the layout):
+//   [4,6) D format (1 = f32, 2 = s32)   [7,10) A format   [10,13) B format
+//   [15] A major (1 = MN)   [16] B major (1 = MN)   [17,23) N >> 3   [24,29) M >> 4
+__host__ __device__ constexpr uint32_t make_idesc(int d_fmt, int a_fmt, int b_fmt, bool a_mn, bool b_mn, int m, int n) {
+    return ((uint32_t)d_fmt << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(a_mn ? 1 : 0) << 15) |
+           ((uint32_t)(b_mn ? 1 : 0) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---- tile scheduler -------------------------------------------------------------------------
+
+struct TileCoord {
+    int m, n;
+};
+// Grouped rasterisation: GROUP_M row-tiles sweep all column-tiles before moving down, so the CTAs
+// that run together share A and B panels in L2.
+__device__ __forceinline__ TileCoord tile_coord(int64_t tile, int tiles_m, int tiles_n) {
+    const int64_t width = (int64_t)GROUP_M * tiles_n;
+    const int group = (int)(tile / width);
+    const int first_m = group * GROUP_M;
+    const int group_size = (tiles_m - first_m) < GROUP_M ? (tiles_m - first_m) : GROUP_M;
+    const int in_group = (int)(tile % width);
+    return TileCoord{first_m + in_group % group_size, in_group / group_size};
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float load_scale(const void* p, int dtype, int64_t i) {
+    return dtype == QT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]) : reinterpret_cast<const float*>(p)[i];
+}
+
+// ---- the kernel -----------------------------------------------------------------------------
+
+// KIND: 0 int8 (s32 accumulate), 1 fp8 (f32 accumulate). A_MN / B_MN: operand is MN-major in
+// global memory. The fp8 element formats (e4m3 / e5m2 per operand) arrive in `idesc`.
+template <int KIND, int EPI, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p,
+            const uint32_t idesc) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    float* s_colscale = reinterpret_cast<float*>(smem + SMEM_COLSCALE_OFF);
+    volatile uint32_t* s_tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + SMEM_TMEMPTR_OFF);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + SMEM_ABORT_OFF);
+
+    const uint32_t bar_base = smem_base + SMEM_BAR_OFF;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+    auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int tiles_m = (int)((p.M + BM - 1) / BM);
+    const int tiles_n = (int)((p.N + BN - 1) / BN);
+    const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
+    const int num_kb = (int)((p.K + BK - 1) / BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tmem_full_bar(b), 1);
+            mbar_init(tmem_empty_bar(b), NUM_EPI_THREADS);
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_base + SMEM_TMEMPTR_OFF), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *s_tmem_ptr;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+            const int m0 = tc.m * BM, n0 = tc.n * BN;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(empty_bar(stage), phase ^ 1u, s_abort, p.status, 0x100 | stage);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t a_dst = smem_base + SMEM_STAGES_OFF + stage * STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+                    const int k0 = kb * BK;
+                    mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+                    if constexpr (A_MN) tma_load_2d(a_dst, &tmap_a, full_bar(stage), m0, k0);
+                    else tma_load_2d(a_dst, &tmap_a, full_bar(stage), k0, m0);
+                    if constexpr (B_MN) {
+                        tma_load_2d(b_dst, &tmap_b, full_bar(stage), n0, k0);
+                        tma_load_2d(b_dst + BK * 128, &tmap_b, full_bar(stage), n0 + 128, k0);
+                    } else {
+                        tma_load_2d(b_dst, &tmap_b, full_bar(stage), k0, n0);
+                    }
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+        // Drain: wait until the MMA warp has released every stage this warp filled, so no TMA
+        // write is still in flight when the CTA exits.
+        for (int s = 0; s < STAGES && ok; ++s) {
+            ok = mbar_wait(empty_bar(stage), phase ^ 1u, s_abort, p.status, 0x180 | stage);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, s_abort, p.status, 0x200 | acc);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(full_bar(stage), phase, s_abort, p.status, 0x300 | stage);
+                if (!ok) break;
+                tcgen05_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_addr = smem_base + SMEM_STAGES_OFF + stage * STAGE_BYTES;
+                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // K-major: step 32 bytes inside the 128-byte swizzle row.
+                        // MN-major: step 32 k-rows of 128 bytes.
+                        const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + k * UMMA_K * 128, BK * 128, 1024)
+                                                     : make_smem_desc(a_addr + k * UMMA_K, 16, 1024);
+                        const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + k * UMMA_K * 128, BK * 128, 1024)
+                                                     : make_smem_desc(b_addr + k * UMMA_K, 16, 1024);
+                        tcgen05_mma<KIND>(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty_bar(stage));  // stage reusable once these MMAs retire
+                    if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar(acc));
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    } else {
+        // ===== epilogue =====
+        const int ew = warp & 3;  // TMEM lane quarter this warp may read
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+            const int64_t m0 = (int64_t)tc.m * BM, n0 = (int64_t)tc.n * BN;
+            const int64_t row = m0 + ew * 32 + lane;
+
+            float row_scale = 0.0f;
+            float* cs_warp = s_colscale + (warp - 2) * BN;  // private to this warp: no cross-warp barrier
+            if constexpr (EPI == EPI_ROWCOL) {
+                // stage this tile's column scales as fp32
+                for (int j = lane; j < BN; j += 32) {
+                    const int64_t n = n0 + j;
+                    cs_warp[j] = (n < p.N) ? load_scale(p.scale_b, p.scale_dtype, p.scale_b_is_scalar ? 0 : n) : 0.0f;
+                }
+                if (row < p.M) row_scale = load_scale(p.scale_a, p.scale_dtype, row);
+                __syncwarp();
+            }
+
+            ok = mbar_wait(tmem_full_bar(acc), acc_phase, s_abort, p.status, 0x400 | acc);
+            if (!ok) break;
+            tcgen05_fence_after();
+
+            const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(t_row + c * 32, r);
+                tmem_ld_wait();
+                const int64_t n = n0 + c * 32;
+                if (row < p.M && n < p.N) {
+                    if constexpr (EPI == EPI_RAW) {
+                        // int32 (or fp32 bit pattern) straight out
+                        uint32_t* dst = reinterpret_cast<uint32_t*>(p.c) + row * p.ldc + n;
+                        if (n + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && n + j < p.N; ++j) dst[j] = r[j];
+                        }
+                    } else {
+                        const float* cs = cs_warp + c * 32;
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float a = (KIND == 0) ? (float)(int32_t)r[j] : __uint_as_float(r[j]);
+                            v[j] = __fmul_rn(__fmul_rn(a, row_scale), cs[j]);
+                        }
+                        if (p.scale_dtype == QT_BF16) {
+                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + row * p.ldc + n;
+                            if (n + 32 <= p.N && (p.ldc & 7) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 8)
+                                    *reinterpret_cast<uint4*>(dst + j) =
+                                        make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                                                   pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+                            } else {
+                                for (int j = 0; j < 32 && n + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+                            }
+                        } else {
+                            float* dst = reinterpret_cast<float*>(p.c) + row * p.ldc + n;
+                            if (n + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            } else {
+                                for (int j = 0; j < 32 && n + j < p.N; ++j) dst[j] = v[j];
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            mbar_arrive(tmem_empty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn* out) {
+    static EncodeTiledFn cached = nullptr;
+    if (!cached) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        QT_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || !fn) return fail(QT_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+        cached = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    *out = cached;
+    return QT_OK;
+}
+
+// 2-D byte tensor map: `inner` contiguous bytes per line, `outer` lines `pitch` bytes apart,
+// box = box_inner x box_outer, 128-byte swizzle, out-of-range reads return zero.
+int make_tmap(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch, uint32_t box_inner,
+              uint32_t box_outer) {
+    EncodeTiledFn encode;
+    if (int rc = get_encode_fn(&encode)) return rc;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(QT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, pitch %llu)", (int)r,
+                                       (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)pitch);
+    return QT_OK;
+}
+
+template <int KIND, int EPI>
+int launch_layout(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, uint32_t idesc,
+                  int grid, cudaStream_t stream) {
+#define QT_LAUNCH(AMN, BMN)                                                                                        \
+    do {                                                                                                           \
+        auto kfn = gemm_kernel<KIND, EPI, AMN, BMN>;                                                               \
+        static bool attr_set[64] = {false};                                                                        \
+        int dev = 0;                                                                                               \
+        QT_CUDA_CHECK(cudaGetDevice(&dev));                                                                        \
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {                                                              \
+            QT_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));     \
+            if (dev >= 0 && dev < 64) attr_set[dev] = true;                                                        \
+        }                                                                                                          \
+        kfn<<<grid, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, p, idesc);                                          \
+    } while (0)
+    if (!a_mn && !b_mn) QT_LAUNCH(false, false);
+    else if (!a_mn && b_mn) QT_LAUNCH(false, true);
+    else if (a_mn && b_mn) QT_LAUNCH(true, true);
+    else QT_LAUNCH(true, false);
+#undef QT_LAUNCH
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
+int fp8_format(int dtype) { return dtype == QT_E4M3 ? 0 : 1; }
+
+int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype, int64_t b_sk,
+                  int64_t b_sn, GemmParams p, void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const int64_t M = p.M, N = p.N, K = p.K;
+    QT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative dimension");
+    QT_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "gemm: dimension exceeds 2^31");
+    const bool is_i8 = a_dtype == QT_I8 && b_dtype == QT_I8;
+    const bool is_f8 = (a_dtype == QT_E4M3 || a_dtype == QT_E5M2) && (b_dtype == QT_E4M3 || b_dtype == QT_E5M2);
+    QT_REQUIRE(is_i8 || is_f8, "gemm: operands must both be int8 or both be fp8 (got %d, %d)", a_dtype, b_dtype);
+    if (M == 0 || N == 0) return QT_OK;
+    QT_REQUIRE(a && b && p.c, "gemm: null operand");
+    QT_REQUIRE(K > 0, "gemm: K must be positive (zero-length reductions are handled by the caller)");
+    QT_REQUIRE((a_sk == 1) != (a_sm == 1) || (M == 1 || K == 1), "gemm: exactly one stride of A must be 1 (got %lld, %lld)", (long long)a_sm, (long long)a_sk);
+    QT_REQUIRE((b_sk == 1) != (b_sn == 1) || (N == 1 || K == 1), "gemm: exactly one stride of B must be 1 (got %lld, %lld)", (long long)b_sk, (long long)b_sn);
+    const bool a_mn = (a_sk != 1);  // A stored [K][M]
+    const bool b_mn = (b_sk != 1);  // B stored [K][N]
+    const int64_t a_pitch = a_mn ? a_sk : a_sm;
+    const int64_t b_pitch = b_mn ? b_sk : b_sn;
+    QT_REQUIRE(aligned_to(a, 16) && aligned_to(b, 16), "gemm: operand base pointers must be 16-byte aligned");
+    QT_REQUIRE(a_pitch % 16 == 0 && b_pitch % 16 == 0, "gemm: the non-unit operand strides must be multiples of 16 (got %lld, %lld)", (long long)a_pitch, (long long)b_pitch);
+    QT_REQUIRE(a_pitch >= (a_mn ? M : K) && b_pitch >= (b_mn ? N : K), "gemm: operand stride smaller than the contiguous extent");
+    QT_REQUIRE(p.ldc >= N, "gemm: ldc smaller than N");
+
+    CUtensorMap ta, tb;
+    if (a_mn) { if (int rc = make_tmap(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)a_pitch, 128, BK)) return rc; }
+    else      { if (int rc = make_tmap(&ta, a, (uint64_t)K, (uint64_t)M, (uint64_t)a_pitch, BK, BM)) return rc; }
+    if (b_mn) { if (int rc = make_tmap(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)b_pitch, 128, BK)) return rc; }
+    else      { if (int rc = make_tmap(&tb, b, (uint64_t)K, (uint64_t)N, (uint64_t)b_pitch, BK, BN)) return rc; }
+
+    if (int rc = device_status_ptr(&p.status)) return rc;
+
+    const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int sms = num_sms();
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    const uint32_t idesc = is_i8 ? make_idesc(2, 1, 1, a_mn, b_mn, BM, BN)
+                                 : make_idesc(1, fp8_format(a_dtype), fp8_format(b_dtype), a_mn, b_mn, BM, BN);
+    if (is_i8) {
+        if (epi == EPI_RAW) return launch_layout<0, EPI_RAW>(a_mn, b_mn, ta, tb, p, idesc, grid, stream);
+        if (epi == EPI_ROWCOL) return launch_layout<0, EPI_ROWCOL>(a_mn, b_mn, ta, tb, p, idesc, grid, stream);
+    } else {
+        if (epi == EPI_ROWCOL) return launch_layout<1, EPI_ROWCOL>(a_mn, b_mn, ta, tb, p, idesc, grid, stream);
+    }
+    return fail(QT_ERR_UNSUPPORTED, "gemm: epilogue %d not implemented for this operand type", epi);
+}
+
+}  // namespace
+
+}  // namespace qt
+
+using namespace qt;
+
+extern "C" int qt_int8_mm(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, int32_t* c,
+                          int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream) {
+    GemmParams p = {};
+    p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc;
+    return gemm_dispatch(EPI_RAW, a, QT_I8, a_sm, a_sk, b, QT_I8, b_sk, b_sn, p, stream);
+}
+
+extern "C" int qt_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype, int64_t b_sk,
+                            int64_t b_sn, const void* scale_a, const void* scale_b, int scale_b_is_scalar, int scale_dtype,
+                            void* c, int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream) {
+    QT_REQUIRE(scale_dtype == QT_BF16 || scale_dtype == QT_F32, "scaled_mm: scale_dtype must be QT_BF16 or QT_F32 (got %d)", scale_dtype);
+    QT_REQUIRE((scale_a && scale_b) || M == 0 || N == 0, "scaled_mm: null scale pointer");
+    GemmParams p = {};
+    p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc;
+    p.scale_a = scale_a; p.scale_b = scale_b; p.scale_b_is_scalar = scale_b_is_scalar; p.scale_dtype = scale_dtype;
+    return gemm_dispatch(EPI_ROWCOL, a, a_dtype, a_sm, a_sk, b, b_dtype, b_sk, b_sn, p, stream);
+}
+
+extern "C" int qt_tile_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype,
+                                 int64_t b_sk, int64_t b_sn, const void* scale_a, int64_t sa_s0, int64_t sa_s1,
+                                 const void* scale_b, int64_t sb_s0, int64_t sb_s1, int qm, int qn, int qk, int scale_dtype,
+                                 void* c, int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream) {
+    (void)a; (void)a_dtype; (void)a_sm; (void)a_sk; (void)b; (void)b_dtype; (void)b_sk; (void)b_sn; (void)scale_a; (void)sa_s0;
+    (void)sa_s1; (void)scale_b; (void)sb_s0; (void)sb_s1; (void)qm; (void)qn; (void)qk; (void)scale_dtype; (void)c; (void)ldc;
+    (void)M; (void)N; (void)K; (void)stream;
+    return fail(QT_ERR_UNSUPPORTED, "tile_scaled_mm: not implemented yet");
+}

@@ -1,0 +1,805 @@
+// Absmax quantize kernels (HBM-bound): row-wise, row-wise + column absmax, column absmax,
+// column-wise with transpose, tile-wise. bf16 / fp32 in; int8 or fp8 out plus one scale per
+// row / column / tile.
+//
+// Arithmetic follows quantize_int8 of the reference project (subclasses/int8.py:12-26):
+//   scale = absmax / qmax            (fp32, IEEE division)
+//   v     = x / max(scale, eps)      (fp32, IEEE division -- never a reciprocal multiply)
+//   q     = clamp(round_half_even(v)) or clamp(floor(v + u)), u ~ U[0,1)
+//   the returned scale is the UNCLAMPED scale rounded to the scale dtype.
+//
+// Division: for bf16 inputs the quotient is produced by a correctly rounded reciprocal plus one
+// fused residual correction (3 full-rate ops instead of the ~10 of div.rn). qt_selftest_division
+// checks that sequence against div.rn over every (bf16 x, bf16 absmax) pair; fp32 inputs use
+// div.rn directly.
+#include "common.cuh"
+
+namespace qt {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr float kRoundMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to integer (half-even)
+
+// ---- 8-element vectors ----------------------------------------------------------------------
+
+template <typename XT>
+struct Vec8;
+
+template <>
+struct Vec8<__nv_bfloat16> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void zero() { raw = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+        f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+        f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xFFFF0000u);
+        f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xFFFF0000u);
+    }
+};
+
+template <>
+struct Vec8<float> {
+    float4 lo, hi;
+    __device__ __forceinline__ void load(const float* p) {
+        lo = *reinterpret_cast<const float4*>(p);
+        hi = *reinterpret_cast<const float4*>(p + 4);
+    }
+    __device__ __forceinline__ void zero() { lo = make_float4(0, 0, 0, 0); hi = lo; }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w;
+        f[4] = hi.x; f[5] = hi.y; f[6] = hi.z; f[7] = hi.w;
+    }
+};
+
+template <typename XT>
+__device__ __forceinline__ float to_float(XT v);
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+
+// Load 8 elements starting at column `col` of a row; columns >= cols read as zero.
+template <typename XT>
+__device__ __forceinline__ void load_vec8(Vec8<XT>& v, const XT* row, int64_t col, int64_t cols, bool vec_ok) {
+    if (col + 8 <= cols && vec_ok) {
+        v.load(row + col);
+    } else {
+        float f[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = (col + k < cols) ? to_float<XT>(row[col + k]) : 0.0f;
+        // re-pack through the float path (exact for bf16 and fp32 values)
+        if constexpr (sizeof(XT) == 2) {
+            v.raw.x = (__float_as_uint(f[0]) >> 16) | (__float_as_uint(f[1]) & 0xFFFF0000u);
+            v.raw.y = (__float_as_uint(f[2]) >> 16) | (__float_as_uint(f[3]) & 0xFFFF0000u);
+            v.raw.z = (__float_as_uint(f[4]) >> 16) | (__float_as_uint(f[5]) & 0xFFFF0000u);
+            v.raw.w = (__float_as_uint(f[6]) >> 16) | (__float_as_uint(f[7]) & 0xFFFF0000u);
+        } else {
+            v.lo = make_float4(f[0], f[1], f[2], f[3]);
+            v.hi = make_float4(f[4], f[5], f[6], f[7]);
+        }
+    }
+}
+
+// ---- division -------------------------------------------------------------------------------
+
+__device__ __forceinline__ float recip_rn(float d) { return __frcp_rn(d); }
+__device__ __forceinline__ float div_rn(float x, float d) { return __fdiv_rn(x, d); }
+
+// Divider by a fixed positive d. EXACT selects div.rn; otherwise the reciprocal sequence.
+template <bool EXACT>
+struct Divider {
+    float d, r;
+    bool tiny;  // reciprocal would overflow: use div.rn
+    __device__ __forceinline__ explicit Divider(float d_) : d(d_), r(recip_rn(d_)), tiny(d_ < 1e-30f) {}
+    __device__ __forceinline__ float operator()(float x) const {
+        if (EXACT || tiny) {
+            return div_rn(x, d);
+        } else {
+            const float q0 = __fmul_rn(x, r);
+            const float e = __fmaf_rn(-q0, d, x);
+            return __fmaf_rn(e, r, q0);
+        }
+    }
+};
+
+// ---- rounding to a byte ---------------------------------------------------------------------
+
+// int8 from a pre-divided value, round-half-even, clamp [-128, 127]. Clamping before rounding is
+// equivalent because both bounds are integers.
+__device__ __forceinline__ uint32_t int8_rne(float v) {
+    v = fminf(fmaxf(v, -128.0f), 127.0f);
+    return __float_as_uint(__fadd_rn(v, kRoundMagic)) & 0xFFu;
+}
+
+// int8 from floor(v + u), clamp [-128, 127].
+__device__ __forceinline__ uint32_t int8_sr(float v, float u) {
+    float w = __fadd_rn(v, u);
+    w = fminf(fmaxf(w, -128.0f), 127.5f);
+    float r = __fsub_rn(__fadd_rn(w, kRoundMagic), kRoundMagic);  // nearest integer
+    if (r > w) r -= 1.0f;                                          // -> floor
+    return __float_as_uint(__fadd_rn(r, kRoundMagic)) & 0xFFu;
+}
+
+// Quantize 8 pre-divided values into 8 bytes (two 32-bit words).
+__device__ __forceinline__ uint2 pack8(const float (&v)[8], int q_dtype, bool stochastic, const float (&u)[8]) {
+    uint32_t b[8];
+    if (q_dtype == QT_I8) {
+        if (stochastic) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) b[k] = int8_sr(v[k], u[k]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) b[k] = int8_rne(v[k]);
+        }
+    } else {
+        const __nv_fp8_interpretation_t kind = (q_dtype == QT_E4M3) ? __NV_E4M3 : __NV_E5M2;
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) {
+            const uint32_t two = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(v[k], v[k + 1]), __NV_SATFINITE, kind);
+            b[k] = two & 0xFFu;
+            b[k + 1] = (two >> 8) & 0xFFu;
+        }
+    }
+    uint2 out;
+    out.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+    out.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+    return out;
+}
+
+// Uniforms for 8 consecutive elements starting at linear index idx.
+__device__ __forceinline__ void uniforms8(float (&u)[8], int64_t idx, uint64_t seed, uint64_t offset) {
+    if ((idx & 3) == 0) {
+        const Philox4 a = philox4x32_10((uint64_t)idx >> 2, offset, seed);
+        const Philox4 b = philox4x32_10(((uint64_t)idx >> 2) + 1, offset, seed);
+        u[0] = u01_from_bits(a.x); u[1] = u01_from_bits(a.y); u[2] = u01_from_bits(a.z); u[3] = u01_from_bits(a.w);
+        u[4] = u01_from_bits(b.x); u[5] = u01_from_bits(b.y); u[6] = u01_from_bits(b.z); u[7] = u01_from_bits(b.w);
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint64_t i = (uint64_t)(idx + k);
+            const Philox4 a = philox4x32_10(i >> 2, offset, seed);
+            const uint32_t w = (i & 3) == 0 ? a.x : ((i & 3) == 1 ? a.y : ((i & 3) == 2 ? a.z : a.w));
+            u[k] = u01_from_bits(w);
+        }
+    }
+}
+
+__device__ __forceinline__ float uniform1(int64_t idx, uint64_t seed, uint64_t offset) {
+    const uint64_t i = (uint64_t)idx;
+    const Philox4 a = philox4x32_10(i >> 2, offset, seed);
+    const uint32_t w = (i & 3) == 0 ? a.x : ((i & 3) == 1 ? a.y : ((i & 3) == 2 ? a.z : a.w));
+    return u01_from_bits(w);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+
+// Store 8 quantized bytes at q[idx .. idx+8) honouring the row end.
+__device__ __forceinline__ void store_bytes8(uint8_t* q, int64_t idx, int64_t valid, uint2 bytes, bool vec_ok) {
+    if (valid >= 8 && vec_ok) {
+        *reinterpret_cast<uint2*>(q + idx) = bytes;
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (k < valid) q[idx + k] = (uint8_t)(((k < 4 ? bytes.x : bytes.y) >> (8 * (k & 3))) & 0xFFu);
+    }
+}
+
+// ---- row-wise -------------------------------------------------------------------------------
+
+struct RowwiseParams {
+    const void* x;
+    int64_t rows, cols, stride;
+    uint8_t* q;
+    void* scale;
+    float* col_absmax;
+    int q_dtype, scale_dtype;
+    float eps;
+    int stochastic;
+    uint64_t seed, offset;
+    int vec_load, vec_store;
+};
+
+// TPR threads cooperate on one row, each holding VPT vectors of 8 elements in registers, so a row
+// of up to TPR*VPT*8 columns is read from HBM exactly once. With COLABS each thread also keeps the
+// running |x| maximum of its columns over all rows the CTA visits; the CTA folds those into one
+// atomic max per column at the end.
+template <typename XT, int TPR, int VPT, bool COLABS>
+__global__ void __launch_bounds__(kThreads) rowwise_kernel(const RowwiseParams p) {
+    constexpr int RPC = kThreads / TPR;  // rows per CTA per iteration
+    constexpr int WPR = TPR / 32;        // warps per row
+    constexpr bool EXACT_DIV = sizeof(XT) != 2;
+    __shared__ float s_red[kThreads / 32];
+    __shared__ float s_col[(COLABS && RPC > 1) ? TPR * VPT * 8 : 1];
+
+    const int sub = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int warp = threadIdx.x >> 5;
+    const XT* x = reinterpret_cast<const XT*>(p.x);
+    const float qmax = qmax_of(p.q_dtype);
+
+    float colmax[COLABS ? VPT : 1][8];
+    if constexpr (COLABS) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) colmax[i][k] = 0.0f;
+        if constexpr (RPC > 1) {
+            for (int i = threadIdx.x; i < TPR * VPT * 8; i += kThreads) s_col[i] = 0.0f;
+        }
+    }
+
+    for (int64_t base = (int64_t)blockIdx.x * RPC; base < p.rows; base += (int64_t)gridDim.x * RPC) {
+        const int64_t row = base + sub;
+        const bool valid = row < p.rows;
+        const XT* xrow = x + (valid ? row : 0) * p.stride;
+
+        Vec8<XT> v[VPT];
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int64_t col = ((int64_t)i * TPR + t) * 8;
+            if (valid && col < p.cols) load_vec8<XT>(v[i], xrow, col, p.cols, p.vec_load != 0);
+            else v[i].zero();
+        }
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            float f[8];
+            v[i].unpack(f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float a = fabsf(f[k]);
+                amax = fmaxf(amax, a);
+                if constexpr (COLABS) colmax[i][k] = fmaxf(colmax[i][k], a);
+            }
+        }
+        amax = warp_max(amax);
+        if constexpr (WPR > 1) {
+            if ((threadIdx.x & 31) == 0) s_red[warp] = amax;
+            __syncthreads();
+            amax = s_red[sub * WPR];
+#pragma unroll
+            for (int w = 1; w < WPR; ++w) amax = fmaxf(amax, s_red[sub * WPR + w]);
+            __syncthreads();
+        }
+
+        const float scale = __fdiv_rn(amax, qmax);
+        const Divider<EXACT_DIV> div(fmaxf(scale, p.eps));
+        if (valid && t == 0) store_scale(p.scale, p.scale_dtype, row, scale);
+
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int64_t col = ((int64_t)i * TPR + t) * 8;
+            if (valid && col < p.cols) {
+                float f[8], u[8];
+                v[i].unpack(f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] = div(f[k]);
+                const int64_t idx = row * p.cols + col;
+                if (p.stochastic) uniforms8(u, idx, p.seed, p.offset);
+                const uint2 bytes = pack8(f, p.q_dtype, p.stochastic != 0, u);
+                store_bytes8(p.q, idx, p.cols - col, bytes, p.vec_store != 0);
+            }
+        }
+    }
+
+    if constexpr (COLABS) {
+        if constexpr (RPC > 1) {
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    atomicMax(reinterpret_cast<unsigned int*>(&s_col[(i * TPR + t) * 8 + k]), __float_as_uint(colmax[i][k]));
+            __syncthreads();
+            for (int c = threadIdx.x; c < TPR * VPT * 8; c += kThreads)
+                if (c < p.cols) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c), __float_as_uint(s_col[c]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int64_t c = ((int64_t)i * TPR + t) * 8 + k;
+                    if (c < p.cols) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c), __float_as_uint(colmax[i][k]));
+                }
+        }
+    }
+}
+
+// Any width, any alignment: one CTA per row, two passes (the second normally hits L2).
+template <typename XT, bool COLABS>
+__global__ void __launch_bounds__(kThreads) rowwise_generic_kernel(const RowwiseParams p) {
+    __shared__ float s_red[kThreads / 32];
+    __shared__ float s_amax;
+    const XT* x = reinterpret_cast<const XT*>(p.x);
+    const float qmax = qmax_of(p.q_dtype);
+    for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const XT* xrow = x + row * p.stride;
+        float amax = 0.0f;
+        for (int64_t c = threadIdx.x; c < p.cols; c += kThreads) {
+            const float a = fabsf(to_float<XT>(xrow[c]));
+            amax = fmaxf(amax, a);
+            if constexpr (COLABS) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c), __float_as_uint(a));
+        }
+        amax = warp_max(amax);
+        if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = s_red[0];
+            for (int w = 1; w < kThreads / 32; ++w) m = fmaxf(m, s_red[w]);
+            s_amax = m;
+        }
+        __syncthreads();
+        const float scale = __fdiv_rn(s_amax, qmax);
+        const float d = fmaxf(scale, p.eps);
+        if (threadIdx.x == 0) store_scale(p.scale, p.scale_dtype, row, scale);
+        for (int64_t c = threadIdx.x; c < p.cols; c += kThreads) {
+            const float v = __fdiv_rn(to_float<XT>(xrow[c]), d);
+            const int64_t idx = row * p.cols + c;
+            const float u = p.stochastic ? uniform1(idx, p.seed, p.offset) : 0.0f;
+            p.q[idx] = (uint8_t)quantize_byte(v, p.q_dtype, p.stochastic != 0, u);
+        }
+        __syncthreads();
+    }
+}
+
+template <typename XT, int TPR, int VPT, bool COLABS>
+int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
+    constexpr int RPC = kThreads / TPR;
+    const int64_t want = (p.rows + RPC - 1) / RPC;
+    // With COLABS fewer, longer-lived CTAs mean fewer column atomics.
+    const int64_t cap = (int64_t)num_sms() * (COLABS ? 4 : 8);
+    const int grid = (int)(want < cap ? want : cap);
+    rowwise_kernel<XT, TPR, VPT, COLABS><<<grid, kThreads, 0, stream>>>(p);
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
+template <typename XT, bool COLABS>
+int launch_rowwise(const RowwiseParams& p, cudaStream_t stream) {
+    const int64_t c = p.cols;
+    if (!p.vec_load || c > 32768) {
+        const int64_t cap = (int64_t)num_sms() * 8;
+        const int grid = (int)(p.rows < cap ? p.rows : cap);
+        rowwise_generic_kernel<XT, COLABS><<<grid, kThreads, 0, stream>>>(p);
+        QT_CUDA_CHECK(cudaGetLastError());
+        return QT_OK;
+    }
+    if (c <= 256) return launch_rowwise_cfg<XT, 32, 1, COLABS>(p, stream);
+    if (c <= 512) return launch_rowwise_cfg<XT, 32, 2, COLABS>(p, stream);
+    if (c <= 1024) return launch_rowwise_cfg<XT, 32, 4, COLABS>(p, stream);
+    if (c <= 2048) return launch_rowwise_cfg<XT, 64, 4, COLABS>(p, stream);
+    if (c <= 4096) return launch_rowwise_cfg<XT, 128, 4, COLABS>(p, stream);
+    if (c <= 8192) return launch_rowwise_cfg<XT, 256, 4, COLABS>(p, stream);
+    if (c <= 16384) return launch_rowwise_cfg<XT, 256, 8, COLABS>(p, stream);
+    return launch_rowwise_cfg<XT, 256, 16, COLABS>(p, stream);
+}
+
+int check_quant_args(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t stride, const void* q,
+                     int q_dtype, const void* scale, int scale_dtype) {
+    QT_REQUIRE(x_dtype == QT_BF16 || x_dtype == QT_F32, "quantize: x_dtype must be QT_BF16 or QT_F32 (got %d)", x_dtype);
+    QT_REQUIRE(q_dtype == QT_I8 || q_dtype == QT_E4M3 || q_dtype == QT_E5M2, "quantize: q_dtype must be QT_I8, QT_E4M3 or QT_E5M2 (got %d)", q_dtype);
+    QT_REQUIRE(scale_dtype == QT_BF16 || scale_dtype == QT_F32, "quantize: scale_dtype must be QT_BF16 or QT_F32 (got %d)", scale_dtype);
+    QT_REQUIRE(rows >= 0 && cols >= 0, "quantize: negative shape (%lld, %lld)", (long long)rows, (long long)cols);
+    QT_REQUIRE(stride >= cols, "quantize: row stride %lld smaller than cols %lld", (long long)stride, (long long)cols);
+    if (rows > 0 && cols > 0) QT_REQUIRE(x && q && scale, "quantize: null pointer");
+    return QT_OK;
+}
+
+int quantize_rowwise_impl(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t stride, void* q,
+                          int q_dtype, void* scale, int scale_dtype, float* col_absmax, bool want_colabs,
+                          float eps, int stochastic, uint64_t seed, uint64_t offset, void* stream_) {
+    if (int rc = check_quant_args(x, x_dtype, rows, cols, stride, q, q_dtype, scale, scale_dtype)) return rc;
+    QT_REQUIRE(!stochastic || q_dtype == QT_I8, "quantize: stochastic rounding is defined for int8 output only");
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (want_colabs) {
+        QT_REQUIRE(col_absmax || cols == 0, "quantize: col_absmax is null");
+        if (cols > 0) QT_CUDA_CHECK(cudaMemsetAsync(col_absmax, 0, sizeof(float) * cols, stream));
+    }
+    if (rows == 0 || cols == 0) return QT_OK;
+
+    RowwiseParams p;
+    p.x = x; p.rows = rows; p.cols = cols; p.stride = stride;
+    p.q = reinterpret_cast<uint8_t*>(q); p.scale = scale; p.col_absmax = col_absmax;
+    p.q_dtype = q_dtype; p.scale_dtype = scale_dtype; p.eps = eps; p.stochastic = stochastic;
+    p.seed = seed; p.offset = offset;
+    const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
+    p.vec_load = aligned_to(x, 16) && ((stride * esz) % 16 == 0);
+    p.vec_store = aligned_to(q, 8) && (cols % 8 == 0);
+
+    if (x_dtype == QT_BF16)
+        return want_colabs ? launch_rowwise<__nv_bfloat16, true>(p, stream) : launch_rowwise<__nv_bfloat16, false>(p, stream);
+    return want_colabs ? launch_rowwise<float, true>(p, stream) : launch_rowwise<float, false>(p, stream);
+}
+
+// ---- column absmax --------------------------------------------------------------------------
+
+// Each CTA owns a strip of 256*8 columns x a slab of rows; threads hold 8 column maxima in
+// registers, then one atomic max per column per CTA.
+template <typename XT>
+__global__ void __launch_bounds__(kThreads) col_absmax_kernel(const XT* __restrict__ x, int64_t rows, int64_t cols,
+                                                               int64_t stride, float* __restrict__ out,
+                                                               int64_t rows_per_cta, int vec_ok) {
+    const int64_t col = ((int64_t)blockIdx.x * kThreads + threadIdx.x) * 8;
+    if (col >= cols) return;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_cta;
+    const int64_t r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
+    float m[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) m[k] = 0.0f;
+    int64_t r = r0;
+    for (; r + 4 <= r1; r += 4) {
+        Vec8<XT> v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) load_vec8<XT>(v[j], x + (r + j) * stride, col, cols, vec_ok != 0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float f[8];
+            v[j].unpack(f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) m[k] = fmaxf(m[k], fabsf(f[k]));
+        }
+    }
+    for (; r < r1; ++r) {
+        Vec8<XT> v;
+        float f[8];
+        load_vec8<XT>(v, x + r * stride, col, cols, vec_ok != 0);
+        v.unpack(f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) m[k] = fmaxf(m[k], fabsf(f[k]));
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        if (col + k < cols) atomicMax(reinterpret_cast<unsigned int*>(out + col + k), __float_as_uint(m[k]));
+}
+
+// ---- column-wise quantize + transpose ---------------------------------------------------------
+
+struct ColwiseParams {
+    const void* x;
+    int64_t rows, cols, stride;
+    const float* col_absmax;
+    uint8_t* qt;
+    void* scale;
+    int q_dtype, scale_dtype;
+    float eps;
+    int stochastic;
+    uint64_t seed, offset;
+    int vec_load, vec_store;
+};
+
+// Tile = 128 rows x 64 columns of x. Thread (rq, cg) reads 4 consecutive rows x 8 columns,
+// quantizes with the 8 column scales, packs the 4 row-consecutive bytes of each column into one
+// word and parks it in shared memory; warps then stream each output row (128 bytes of the
+// transposed tensor) to HBM. x is read once, qt written once.
+constexpr int kTileR = 128, kTileC = 64;
+
+template <typename XT>
+__global__ void __launch_bounds__(kThreads) colwise_t_kernel(const ColwiseParams p) {
+    constexpr bool EXACT_DIV = sizeof(XT) != 2;
+    __shared__ uint32_t s_tile[kTileC][kTileR / 4 + 1];
+    const XT* x = reinterpret_cast<const XT*>(p.x);
+    const float qmax = qmax_of(p.q_dtype);
+    const int cg = threadIdx.x & 7;   // column group (8 columns)
+    const int rq = threadIdx.x >> 3;  // row quad (4 rows)
+    const int64_t c0 = (int64_t)blockIdx.x * kTileC;
+    const int64_t col = c0 + cg * 8;
+
+    // column scales for this thread's 8 columns
+    float dsc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float am = (col + k < p.cols) ? p.col_absmax[col + k] : 0.0f;
+        const float sc = __fdiv_rn(am, qmax);
+        dsc[k] = fmaxf(sc, p.eps);
+        if (blockIdx.y == 0 && rq == 0 && col + k < p.cols) store_scale(p.scale, p.scale_dtype, col + k, sc);
+    }
+
+    for (int64_t rb = blockIdx.y; rb * kTileR < p.rows; rb += gridDim.y) {
+        const int64_t r0 = rb * kTileR + rq * 4;
+        Vec8<XT> v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (r0 + j < p.rows && col < p.cols) load_vec8<XT>(v[j], x + (r0 + j) * p.stride, col, p.cols, p.vec_load != 0);
+            else v[j].zero();
+        }
+        float f[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j].unpack(f[j]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const Divider<EXACT_DIV> div(dsc[k]);
+            uint32_t word = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float q = div(f[j][k]);
+                uint32_t b;
+                if (p.q_dtype == QT_I8) {
+                    if (p.stochastic) {
+                        const float u = uniform1((col + k) * p.rows + r0 + j, p.seed, p.offset);
+                        b = int8_sr(q, u);
+                    } else {
+                        b = int8_rne(q);
+                    }
+                } else {
+                    b = quantize_byte(q, p.q_dtype, false, 0.0f);
+                }
+                word |= b << (8 * j);
+            }
+            s_tile[cg * 8 + k][rq] = word;
+        }
+        __syncthreads();
+        // 8 warps x 8 output rows each; lane l carries bytes [4l, 4l+4) of the 128-byte row segment
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+        for (int i = 0; i < kTileC / 8; ++i) {
+            const int cc = warp * (kTileC / 8) + i;
+            const int64_t oc = c0 + cc;
+            const int64_t orow0 = rb * kTileR + lane * 4;
+            if (oc < p.cols && orow0 < p.rows) {
+                const uint32_t word = s_tile[cc][lane];
+                uint8_t* dst = p.qt + oc * p.rows + orow0;
+                if (orow0 + 4 <= p.rows && p.vec_store) {
+                    *reinterpret_cast<uint32_t*>(dst) = word;
+                } else {
+                    for (int j = 0; j < 4 && orow0 + j < p.rows; ++j) dst[j] = (uint8_t)((word >> (8 * j)) & 0xFFu);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---- tile-wise ------------------------------------------------------------------------------
+
+struct TileParams {
+    const void* x;
+    int64_t rows, cols, stride;
+    uint8_t* q;
+    void* scale;
+    int64_t scale_cols;
+    int q_dtype, scale_dtype;
+    float eps;
+    int vec_load, vec_store;
+};
+
+// 1 x 128 tiles: 16 lanes per tile, 16 tiles per CTA iteration.
+template <typename XT>
+__global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p) {
+    constexpr bool EXACT_DIV = sizeof(XT) != 2;
+    const XT* x = reinterpret_cast<const XT*>(p.x);
+    const float qmax = qmax_of(p.q_dtype);
+    const int64_t tiles_per_row = p.scale_cols;
+    const int64_t n_tiles = p.rows * tiles_per_row;
+    const int l16 = threadIdx.x & 15;
+    const float zero_u[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    // all 16 lanes of a group follow the same trip count so the shuffles stay converged
+    for (int64_t tbase = (int64_t)blockIdx.x * (kThreads / 16); tbase < n_tiles; tbase += (int64_t)gridDim.x * (kThreads / 16)) {
+        const int64_t tile = tbase + (threadIdx.x >> 4);
+        const bool valid = tile < n_tiles;
+        const int64_t row = valid ? tile / tiles_per_row : 0;
+        const int64_t col = (valid ? tile % tiles_per_row : 0) * 128 + l16 * 8;
+        Vec8<XT> v;
+        if (valid && col < p.cols) load_vec8<XT>(v, x + row * p.stride, col, p.cols, p.vec_load != 0);
+        else v.zero();
+        float f[8];
+        v.unpack(f);
+        float amax = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        const float sc = __fdiv_rn(amax, qmax);
+        const Divider<EXACT_DIV> div(fmaxf(sc, p.eps));
+        if (valid && l16 == 0) store_scale(p.scale, p.scale_dtype, tile, sc);
+        if (valid && col < p.cols) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) f[k] = div(f[k]);
+            const uint2 bytes = pack8(f, p.q_dtype, false, zero_u);
+            store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
+        }
+    }
+}
+
+// 128 x 128 tiles: one CTA per tile; thread (r16, c16) holds 8 vectors (rows r16 + 16 i).
+template <typename XT>
+__global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams p) {
+    constexpr bool EXACT_DIV = sizeof(XT) != 2;
+    __shared__ float s_red[kThreads / 32];
+    const XT* x = reinterpret_cast<const XT*>(p.x);
+    const float qmax = qmax_of(p.q_dtype);
+    const int64_t tile_c = blockIdx.x, tile_r = blockIdx.y;
+    const int c16 = threadIdx.x & 15, r16 = threadIdx.x >> 4;
+    const int64_t col = tile_c * 128 + c16 * 8;
+    const float zero_u[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    Vec8<XT> v[8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int64_t row = tile_r * 128 + r16 + 16 * i;
+        if (row < p.rows && col < p.cols) load_vec8<XT>(v[i], x + row * p.stride, col, p.cols, p.vec_load != 0);
+        else v[i].zero();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float f[8];
+        v[i].unpack(f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
+    }
+    amax = warp_max(amax);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = s_red[0];
+#pragma unroll
+    for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, s_red[w]);
+    const float sc = __fdiv_rn(amax, qmax);
+    const Divider<EXACT_DIV> div(fmaxf(sc, p.eps));
+    if (threadIdx.x == 0) store_scale(p.scale, p.scale_dtype, tile_r * p.scale_cols + tile_c, sc);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int64_t row = tile_r * 128 + r16 + 16 * i;
+        if (row < p.rows && col < p.cols) {
+            float f[8];
+            v[i].unpack(f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) f[k] = div(f[k]);
+            const uint2 bytes = pack8(f, p.q_dtype, false, zero_u);
+            store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
+        }
+    }
+}
+
+// ---- exhaustive check of the reciprocal division ------------------------------------------------
+
+// For every non-negative finite bf16 absmax a (blockIdx) and every finite bf16 x with |x| <= a,
+// compare Divider<false> with div.rn for d = max(a / qmax, eps).
+__global__ void division_selftest_kernel(int q_dtype, float eps, unsigned long long* mismatches) {
+    const float qmax = qmax_of(q_dtype);
+    unsigned long long bad = 0, bad_q = 0;
+    for (uint32_t abits = blockIdx.x; abits < 0x7F80u; abits += gridDim.x) {
+        const float a = bf16_bits_to_float(abits);
+        const float d = fmaxf(__fdiv_rn(a, qmax), eps);
+        const Divider<false> fast(d);
+        for (uint32_t xb = threadIdx.x; xb <= abits; xb += blockDim.x) {
+            const float x = bf16_bits_to_float(xb);
+            const float want = __fdiv_rn(x, d);
+            const float got = fast(x);
+            bad += (__float_as_uint(want) != __float_as_uint(got));
+            const float want_n = __fdiv_rn(-x, d), got_n = fast(-x);
+            bad += (__float_as_uint(want_n) != __float_as_uint(got_n));
+            bad_q += (quantize_byte(want, q_dtype, false, 0.f) != quantize_byte(got, q_dtype, false, 0.f));
+            bad_q += (quantize_byte(want_n, q_dtype, false, 0.f) != quantize_byte(got_n, q_dtype, false, 0.f));
+        }
+    }
+    if (bad) atomicAdd(mismatches, bad);
+    if (bad_q) atomicAdd(mismatches + 1, bad_q);
+}
+
+}  // namespace
+
+}  // namespace qt
+
+// ---- C ABI ------------------------------------------------------------------------------------
+
+using namespace qt;
+
+extern "C" int qt_quantize_rowwise(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                                   void* q, int q_dtype, void* scale, int scale_dtype, float eps, int stochastic,
+                                   uint64_t seed, uint64_t offset, void* stream) {
+    return quantize_rowwise_impl(x, x_dtype, rows, cols, x_row_stride, q, q_dtype, scale, scale_dtype, nullptr, false,
+                                 eps, stochastic, seed, offset, stream);
+}
+
+extern "C" int qt_quantize_rowwise_colabsmax(const void* x, int x_dtype, int64_t rows, int64_t cols,
+                                             int64_t x_row_stride, void* q, int q_dtype, void* scale, int scale_dtype,
+                                             float* col_absmax, float eps, int stochastic, uint64_t seed,
+                                             uint64_t offset, void* stream) {
+    return quantize_rowwise_impl(x, x_dtype, rows, cols, x_row_stride, q, q_dtype, scale, scale_dtype, col_absmax, true,
+                                 eps, stochastic, seed, offset, stream);
+}
+
+extern "C" int qt_col_absmax(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                             float* col_absmax, void* stream_) {
+    QT_REQUIRE(x_dtype == QT_BF16 || x_dtype == QT_F32, "col_absmax: x_dtype must be QT_BF16 or QT_F32 (got %d)", x_dtype);
+    QT_REQUIRE(rows >= 0 && cols >= 0 && x_row_stride >= cols, "col_absmax: bad shape/stride");
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (cols == 0) return QT_OK;
+    QT_REQUIRE(col_absmax, "col_absmax: output is null");
+    QT_CUDA_CHECK(cudaMemsetAsync(col_absmax, 0, sizeof(float) * cols, stream));
+    if (rows == 0) return QT_OK;
+    QT_REQUIRE(x, "col_absmax: x is null");
+    const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
+    const int vec_ok = aligned_to(x, 16) && ((x_row_stride * esz) % 16 == 0);
+    const int64_t strips = (cols + kThreads * 8 - 1) / (kThreads * 8);
+    // enough row slabs to fill the machine a few times over, at least 32 rows each
+    int64_t slabs = ((int64_t)num_sms() * 8 + strips - 1) / strips;
+    const int64_t max_slabs = (rows + 31) / 32;
+    if (slabs > max_slabs) slabs = max_slabs;
+    if (slabs < 1) slabs = 1;
+    if (slabs > 65535) slabs = 65535;
+    const int64_t rows_per_cta = (rows + slabs - 1) / slabs;
+    dim3 grid((unsigned)strips, (unsigned)((rows + rows_per_cta - 1) / rows_per_cta));
+    if (x_dtype == QT_BF16)
+        col_absmax_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), rows, cols, x_row_stride, col_absmax, rows_per_cta, vec_ok);
+    else
+        col_absmax_kernel<float><<<grid, kThreads, 0, stream>>>(reinterpret_cast<const float*>(x), rows, cols, x_row_stride, col_absmax, rows_per_cta, vec_ok);
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
+extern "C" int qt_quantize_colwise_t(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                                     const float* col_absmax, void* qt_out, int q_dtype, void* scale, int scale_dtype,
+                                     float eps, int stochastic, uint64_t seed, uint64_t offset, void* stream_) {
+    if (int rc = check_quant_args(x, x_dtype, rows, cols, x_row_stride, qt_out, q_dtype, scale, scale_dtype)) return rc;
+    QT_REQUIRE(!stochastic || q_dtype == QT_I8, "quantize: stochastic rounding is defined for int8 output only");
+    if (cols == 0) return QT_OK;
+    QT_REQUIRE(col_absmax, "quantize_colwise_t: col_absmax is null");
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    ColwiseParams p;
+    p.x = x; p.rows = rows; p.cols = cols; p.stride = x_row_stride; p.col_absmax = col_absmax;
+    p.qt = reinterpret_cast<uint8_t*>(qt_out); p.scale = scale; p.q_dtype = q_dtype; p.scale_dtype = scale_dtype;
+    p.eps = eps; p.stochastic = stochastic; p.seed = seed; p.offset = offset;
+    const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
+    p.vec_load = aligned_to(x, 16) && ((x_row_stride * esz) % 16 == 0);
+    p.vec_store = aligned_to(qt_out, 4) && (rows % 4 == 0);
+    const int64_t col_tiles = (cols + kTileC - 1) / kTileC;
+    int64_t row_tiles = (rows + kTileR - 1) / kTileR;
+    if (row_tiles < 1) row_tiles = 1;  // rows == 0 still writes the (zero) scales
+    if (row_tiles > 65535) row_tiles = 65535;
+    dim3 grid((unsigned)col_tiles, (unsigned)row_tiles);
+    if (x_dtype == QT_BF16) colwise_t_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(p);
+    else colwise_t_kernel<float><<<grid, kThreads, 0, stream>>>(p);
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
+extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                                int tile_r, int tile_c, void* q, int q_dtype, void* scale, int scale_dtype, float eps,
+                                void* stream_) {
+    if (int rc = check_quant_args(x, x_dtype, rows, cols, x_row_stride, q, q_dtype, scale, scale_dtype)) return rc;
+    if (!((tile_r == 1 || tile_r == 128) && tile_c == 128))
+        return fail(QT_ERR_UNSUPPORTED, "quantize_tile: tile %dx%d not implemented (1x128 and 128x128 are)", tile_r, tile_c);
+    if (rows == 0 || cols == 0) return QT_OK;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    TileParams p;
+    p.x = x; p.rows = rows; p.cols = cols; p.stride = x_row_stride; p.q = reinterpret_cast<uint8_t*>(q);
+    p.scale = scale; p.scale_cols = (cols + 127) / 128; p.q_dtype = q_dtype; p.scale_dtype = scale_dtype; p.eps = eps;
+    const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
+    p.vec_load = aligned_to(x, 16) && ((x_row_stride * esz) % 16 == 0);
+    p.vec_store = aligned_to(q, 8) && (cols % 8 == 0);
+    if (tile_r == 1) {
+        const int64_t n_tiles = rows * p.scale_cols;
+        const int64_t want = (n_tiles + 15) / 16;
+        const int64_t cap = (int64_t)num_sms() * 16;
+        const int grid = (int)(want < cap ? want : cap);
+        if (x_dtype == QT_BF16) tile_1x128_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(p);
+        else tile_1x128_kernel<float><<<grid, kThreads, 0, stream>>>(p);
+    } else {
+        const int64_t tr = (rows + 127) / 128;
+        if (tr > 65535) return fail(QT_ERR_UNSUPPORTED, "quantize_tile: more than 65535 row tiles");
+        dim3 grid((unsigned)p.scale_cols, (unsigned)tr);
+        if (x_dtype == QT_BF16) tile_128x128_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(p);
+        else tile_128x128_kernel<float><<<grid, kThreads, 0, stream>>>(p);
+    }
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
+extern "C" int qt_selftest_division(int q_dtype, float eps, unsigned long long* mismatches_host) {
+    QT_REQUIRE(mismatches_host, "selftest_division: null output");
+    unsigned long long* d = nullptr;
+    QT_CUDA_CHECK(cudaMalloc(&d, 2 * sizeof(unsigned long long)));
+    QT_CUDA_CHECK(cudaMemset(d, 0, 2 * sizeof(unsigned long long)));
+    division_selftest_kernel<<<num_sms() * 8, 256>>>(q_dtype, eps, d);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(mismatches_host, d, 2 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) return fail(QT_ERR_CUDA, "selftest_division: %s", cudaGetErrorString(e));
+    return QT_OK;
+}

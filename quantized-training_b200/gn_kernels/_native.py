@@ -1,0 +1,112 @@
+"""ctypes binding of libqt_b200.so (the C ABI declared in include/qt_b200.h).
+
+The library is the only compute path: if it is missing or a call fails this module raises,
+it never falls back to PyTorch or CPU code.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_char_p, c_float, c_int, c_int64, c_uint64, c_void_p
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).with_name("libqt_b200.so")
+
+# element type codes of include/qt_b200.h
+QT_BF16, QT_F32, QT_I8, QT_E4M3, QT_E5M2, QT_I32, QT_F16 = range(7)
+
+DTYPE_CODE = {
+    torch.bfloat16: QT_BF16,
+    torch.float32: QT_F32,
+    torch.int8: QT_I8,
+    torch.float8_e4m3fn: QT_E4M3,
+    torch.float8_e5m2: QT_E5M2,
+    torch.int32: QT_I32,
+    torch.float16: QT_F16,
+}
+
+# name -> (restype, argtypes): one entry per symbol of include/qt_b200.h
+SIGNATURES = {
+    "qt_last_error": (c_char_p, []),
+    "qt_version": (c_char_p, []),
+    "qt_device_status": (c_int, [ctypes.POINTER(c_int)]),
+    "qt_quantize_rowwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int,
+                                    c_float, c_int, c_uint64, c_uint64, c_void_p]),
+    "qt_quantize_rowwise_colabsmax": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p,
+                                              c_int, c_void_p, c_float, c_int, c_uint64, c_uint64, c_void_p]),
+    "qt_col_absmax": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "qt_quantize_colwise_t": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p,
+                                      c_int, c_float, c_int, c_uint64, c_uint64, c_void_p]),
+    "qt_quantize_tile": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int, c_void_p,
+                                 c_int, c_float, c_void_p]),
+    "qt_int8_mm": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                           c_int64, c_void_p]),
+    "qt_scaled_mm": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
+                             c_int, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "qt_tile_scaled_mm": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64,
+                                  c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int64,
+                                  c_int64, c_int64, c_int64, c_void_p]),
+    "qt_selftest_division": (c_int, [c_int, c_float, ctypes.POINTER(ctypes.c_ulonglong)]),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not LIB_PATH.exists():
+                    raise RuntimeError(
+                        f"{LIB_PATH} is missing: build it with `python quantized-training_b200/csrc/build.py` "
+                        "(there is no fallback path)"
+                    )
+                lib = ctypes.CDLL(str(LIB_PATH))
+                for name, (res, args) in SIGNATURES.items():
+                    if not hasattr(lib, name):
+                        continue  # optional symbols are checked by the tests against the header
+                    fn = getattr(lib, name)
+                    fn.restype = res
+                    fn.argtypes = args
+                _lib = lib
+    return _lib
+
+
+def check(rc: int) -> None:
+    """Turn a non-zero return code into a RuntimeError carrying the library's message."""
+    if rc != 0:
+        msg = load().qt_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"qt_b200 error {rc}: {msg}")
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"dtype {dtype} does not cross the qt_b200 boundary") from None
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("qt_b200 kernels run on CUDA tensors only (there is no CPU path)")
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+    return dev
+
+
+def device_status() -> int:
+    """Status word written by kernels whose bounded waits ran out (0 = fine). Synchronises."""
+    out = c_int(0)
+    check(load().qt_device_status(ctypes.byref(out)))
+    return out.value

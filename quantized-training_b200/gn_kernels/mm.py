@@ -1,0 +1,149 @@
+"""int8_mm / scaled_mm / tile_scaled_mm with the reference's names, schemas and argument checks
+(kernels/gn_kernels/triton_mm.py:112-128,345-441), running on the tcgen05 kernels."""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import _native as nv
+from ._lib import lib, lib_ops
+
+_F8 = (torch.float8_e4m3fn, torch.float8_e5m2)
+
+
+def _operand(t: Tensor, k_dim: int) -> Tensor:
+    """Return `t` (or a re-laid-out copy) that the TMA path accepts: one unit stride, the other a
+    multiple of 16 bytes, 16-byte aligned base. K-major copies are padded along K with zeros."""
+    mn_dim = 1 - k_dim
+    s_k, s_mn = t.stride(k_dim), t.stride(mn_dim)
+    n_k, n_mn = t.shape[k_dim], t.shape[mn_dim]
+    ok_kmajor = s_k == 1 and s_mn % 16 == 0 and s_mn >= n_k
+    ok_mnmajor = s_mn == 1 and s_k % 16 == 0 and s_k >= n_mn
+    if (ok_kmajor or ok_mnmajor) and t.data_ptr() % 16 == 0 and n_k > 1 and n_mn > 1:
+        return t
+    # rebuild as K-major with a padded pitch
+    pitch = max(16, -(-n_k // 16) * 16)
+    buf = torch.zeros((n_mn, pitch), dtype=t.dtype, device=t.device)
+    view = buf[:, :n_k]
+    view.copy_(t if k_dim == 1 else t.T)
+    return view if k_dim == 1 else view.T
+
+
+def _strides_a(a: Tensor) -> tuple[int, int]:
+    return a.stride(0), a.stride(1)
+
+
+lib.define("int8_mm(Tensor A, Tensor B) -> Tensor")
+lib.define("scaled_mm(Tensor A, Tensor B, Tensor scale_A, Tensor scale_B) -> Tensor")
+lib.define("tile_scaled_mm(Tensor A, Tensor B, Tensor scale_A, Tensor scale_B) -> Tensor")
+
+
+def int8_mm(A: Tensor, B: Tensor) -> Tensor:
+    """int32 C = A @ B for int8 A [M,K], B [K,N], any of the A@B.T / A@B / A.T@B layouts."""
+    assert A.dtype is torch.int8 and B.dtype is torch.int8
+    assert A.shape[1] == B.shape[0]
+    return lib_ops.int8_mm(A, B)
+
+
+@torch.library.impl(lib, "int8_mm", "Meta")
+def _(a: Tensor, b: Tensor):
+    return torch.empty((a.shape[0], b.shape[1]), device=a.device, dtype=torch.int32)
+
+
+@torch.library.impl(lib, "int8_mm", "CUDA")
+def _(A: Tensor, B: Tensor):
+    dev = nv.require_cuda(A, B)
+    M, K = A.shape
+    N = B.shape[1]
+    C = torch.empty((M, N), dtype=torch.int32, device=dev)
+    if M == 0 or N == 0:
+        return C
+    if K == 0:
+        return C.zero_()
+    A, B = _operand(A, 1), _operand(B, 0)
+    with torch.cuda.device(dev):
+        nv.check(nv.load().qt_int8_mm(A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1),
+                                      C.data_ptr(), C.stride(0), M, N, K, nv.stream_ptr(dev)))
+    return C
+
+
+def scaled_mm(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor) -> Tensor:
+    """Matmul of quantized A [M,K] and B [K,N] (both int8 or both fp8) with de-scaling.
+
+    Scale shapes select the variant, as in the reference wrapper (triton_mm.py:349-373):
+      * `scale_A` [M,1] with `scale_B` [1,N] or [1,1]: row/column (or row/tensor) scaling;
+      * otherwise tile-wise: `scale_A` [M/qm, K/qk], `scale_B` [K/qk, N/qn].
+    Two conveniences the reference's own callers need but its wrapper rejects: `scale_B` given as
+    [N,1] (Int8LinearWeight.scale, subclasses/int8.py:157) is read as [1,N], and a 0-dim `scale_B`
+    (BitNet's tensor scale, subclasses/bitnet.py:140) as [1,1]. Output dtype = scale dtype.
+    """
+    assert (A.dtype == B.dtype == torch.int8) or (A.dtype in _F8 and B.dtype in _F8)
+    assert scale_A.dtype == scale_B.dtype
+    if scale_B.ndim == 0:
+        scale_B = scale_B.view(1, 1)
+    elif scale_B.ndim == 2 and scale_B.shape == (B.shape[1], 1) and B.shape[1] != 1 and scale_A.shape == (A.shape[0], 1):
+        scale_B = scale_B.view(1, -1)
+    assert A.ndim == B.ndim == scale_A.ndim == scale_B.ndim == 2
+    assert A.shape[1] == B.shape[0]
+
+    if scale_A.shape == (A.shape[0], 1) and scale_B.shape in ((1, B.shape[1]), (1, 1)):
+        assert scale_A.is_contiguous()
+        assert scale_B.is_contiguous()
+        return lib_ops.scaled_mm(A, B, scale_A, scale_B)
+
+    assert scale_A.shape[1] == scale_B.shape[0]
+    return lib_ops.tile_scaled_mm(A, B, scale_A, scale_B)
+
+
+@torch.library.impl(lib, "scaled_mm", "Meta")
+@torch.library.impl(lib, "tile_scaled_mm", "Meta")
+def _(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor):
+    return torch.empty((A.shape[0], B.shape[1]), device=A.device, dtype=scale_A.dtype)
+
+
+def _scale_dtype_ok(scale: Tensor) -> None:
+    if scale.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"scales must be bfloat16 or float32, got {scale.dtype}")
+
+
+@torch.library.impl(lib, "scaled_mm", "CUDA")
+def _(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor):
+    dev = nv.require_cuda(A, B, row_scale, col_scale)
+    _scale_dtype_ok(row_scale)
+    M, K = A.shape
+    N = B.shape[1]
+    C = torch.empty((M, N), dtype=row_scale.dtype, device=dev)
+    if M == 0 or N == 0:
+        return C
+    if K == 0:
+        return C.zero_()
+    A, B = _operand(A, 1), _operand(B, 0)
+    row_scale, col_scale = row_scale.contiguous(), col_scale.contiguous()
+    with torch.cuda.device(dev):
+        nv.check(nv.load().qt_scaled_mm(
+            A.data_ptr(), nv.code(A.dtype), A.stride(0), A.stride(1), B.data_ptr(), nv.code(B.dtype), B.stride(0),
+            B.stride(1), row_scale.data_ptr(), col_scale.data_ptr(), int(col_scale.numel() == 1 and N != 1),
+            nv.code(row_scale.dtype), C.data_ptr(), C.stride(0), M, N, K, nv.stream_ptr(dev)))
+    return C
+
+
+@torch.library.impl(lib, "tile_scaled_mm", "CUDA")
+def _(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor):
+    dev = nv.require_cuda(A, B, scale_A, scale_B)
+    _scale_dtype_ok(scale_A)
+    M, K = A.shape
+    N = B.shape[1]
+    C = torch.empty((M, N), dtype=scale_A.dtype, device=dev)
+    if M == 0 or N == 0:
+        return C
+    if K == 0:
+        return C.zero_()
+    qm, qk, qn = M // scale_A.shape[0], K // scale_A.shape[1], N // scale_B.shape[1]
+    A, B = _operand(A, 1), _operand(B, 0)
+    with torch.cuda.device(dev):
+        nv.check(nv.load().qt_tile_scaled_mm(
+            A.data_ptr(), nv.code(A.dtype), A.stride(0), A.stride(1), B.data_ptr(), nv.code(B.dtype), B.stride(0),
+            B.stride(1), scale_A.data_ptr(), scale_A.stride(0), scale_A.stride(1), scale_B.data_ptr(), scale_B.stride(0),
+            scale_B.stride(1), qm, qn, qk, nv.code(scale_A.dtype), C.data_ptr(), C.stride(0), M, N, K,
+            nv.stream_ptr(dev)))
+    return C

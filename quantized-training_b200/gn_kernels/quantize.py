@@ -1,0 +1,198 @@
+"""Absmax quantize operators (row-wise, column-wise + transpose, tile-wise) on the sm_100a kernels.
+
+The arithmetic is that of the reference's `quantize_int8` (subclasses/int8.py:12-26); these ops
+exist so the quantize step is one HBM pass instead of a chain of eager / inductor kernels.
+"""
+from __future__ import annotations
+
+import itertools
+
+import torch
+from torch import Tensor
+
+from . import _native as nv
+from ._lib import lib, lib_ops
+
+_F8 = (torch.float8_e4m3fn, torch.float8_e5m2)
+_philox_calls = itertools.count(1)
+
+
+def next_philox_key(device: torch.device) -> tuple[int, int]:
+    """(seed, offset) for one stochastic-rounding launch: the seed follows torch.manual_seed on
+    that device, the offset counts launches in this process, so runs are reproducible."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    seed = torch.cuda.default_generators[idx].initial_seed() & 0xFFFFFFFFFFFFFFFF
+    return seed, next(_philox_calls)
+
+
+def _rows_view(x: Tensor) -> Tensor:
+    """2-D view with unit inner stride (copies only when the layout forces it)."""
+    if x.ndim != 2:
+        raise ValueError(f"expected a 2-D tensor, got shape {tuple(x.shape)}")
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"quantize kernels take bfloat16 or float32 input, got {x.dtype}")
+    if x.shape[1] > 1 and x.stride(1) != 1:
+        x = x.contiguous()
+    if x.shape[0] > 1 and x.stride(0) < x.shape[1]:
+        x = x.contiguous()
+    return x
+
+
+def _row_stride(x: Tensor) -> int:
+    return x.stride(0) if x.shape[0] > 1 else max(x.shape[1], 1)
+
+
+# ---- op definitions ---------------------------------------------------------------------------
+
+lib.define("quantize_rowwise(Tensor x, ScalarType out_dtype, ScalarType scale_dtype, bool stochastic, float eps, int seed, int offset) -> (Tensor, Tensor)")
+lib.define("quantize_rowwise_colabsmax(Tensor x, ScalarType out_dtype, ScalarType scale_dtype, bool stochastic, float eps, int seed, int offset) -> (Tensor, Tensor, Tensor)")
+lib.define("col_absmax(Tensor x) -> Tensor")
+lib.define("quantize_colwise_t(Tensor x, Tensor col_absmax, ScalarType out_dtype, ScalarType scale_dtype, bool stochastic, float eps, int seed, int offset) -> (Tensor, Tensor)")
+lib.define("quantize_tile(Tensor x, int tile_r, int tile_c, ScalarType out_dtype, ScalarType scale_dtype, float eps) -> (Tensor, Tensor)")
+
+
+@torch.library.impl(lib, "quantize_rowwise", "Meta")
+def _(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
+    return x.new_empty(x.shape, dtype=out_dtype), x.new_empty((x.shape[0], 1), dtype=scale_dtype)
+
+
+@torch.library.impl(lib, "quantize_rowwise", "CUDA")
+def _(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
+    x = _rows_view(x)
+    dev = nv.require_cuda(x)
+    rows, cols = x.shape
+    q = torch.empty((rows, cols), dtype=out_dtype, device=dev)
+    scale = torch.empty((rows, 1), dtype=scale_dtype, device=dev)
+    with torch.cuda.device(dev):
+        nv.check(nv.load().qt_quantize_rowwise(
+            x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), q.data_ptr(), nv.code(out_dtype),
+            scale.data_ptr(), nv.code(scale_dtype), eps, int(stochastic), seed, offset, nv.stream_ptr(dev)))
+    return q, scale
+
+
+@torch.library.impl(lib, "quantize_rowwise_colabsmax", "Meta")
+def _(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
+    return (x.new_empty(x.shape, dtype=out_dtype), x.new_empty((x.shape[0], 1), dtype=scale_dtype),
+            x.new_empty((x.shape[1],), dtype=torch.float32))
+
+
+@torch.library.impl(lib, "quantize_rowwise_colabsmax", "CUDA")
+def _(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
+    x = _rows_view(x)
+    dev = nv.require_cuda(x)
+    rows, cols = x.shape
+    q = torch.empty((rows, cols), dtype=out_dtype, device=dev)
+    scale = torch.empty((rows, 1), dtype=scale_dtype, device=dev)
+    colmax = torch.empty((cols,), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        nv.check(nv.load().qt_quantize_rowwise_colabsmax(
+            x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), q.data_ptr(), nv.code(out_dtype),
+            scale.data_ptr(), nv.code(scale_dtype), colmax.data_ptr(), eps, int(stochastic), seed, offset,
+            nv.stream_ptr(dev)))
+    return q, scale, colmax
+
+
+@torch.library.impl(lib, "col_absmax", "Meta")
+def _(x):
+    return x.new_empty((x.shape[1],), dtype=torch.float32)
+
+
+@torch.library.impl(lib, "col_absmax", "CUDA")
+def _(x):
+    x = _rows_view(x)
+    dev = nv.require_cuda(x)
+    rows, cols = x.shape
+    colmax = torch.empty((cols,), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        nv.check(nv.load().qt_col_absmax(x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x),
+                                         colmax.data_ptr(), nv.stream_ptr(dev)))
+    return colmax
+
+
+@torch.library.impl(lib, "quantize_colwise_t", "Meta")
+def _(x, col_absmax, out_dtype, scale_dtype, stochastic, eps, seed, offset):
+    return x.new_empty((x.shape[1], x.shape[0]), dtype=out_dtype), x.new_empty((x.shape[1], 1), dtype=scale_dtype)
+
+
+@torch.library.impl(lib, "quantize_colwise_t", "CUDA")
+def _(x, col_absmax, out_dtype, scale_dtype, stochastic, eps, seed, offset):
+    x = _rows_view(x)
+    dev = nv.require_cuda(x, col_absmax)
+    rows, cols = x.shape
+    if col_absmax.dtype != torch.float32 or col_absmax.numel() != cols or not col_absmax.is_contiguous():
+        raise ValueError("col_absmax must be a contiguous float32 tensor with one entry per column of x")
+    qt = torch.empty((cols, rows), dtype=out_dtype, device=dev)
+    scale = torch.empty((cols, 1), dtype=scale_dtype, device=dev)
+    with torch.cuda.device(dev):
+        nv.check(nv.load().qt_quantize_colwise_t(
+            x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), col_absmax.data_ptr(), qt.data_ptr(),
+            nv.code(out_dtype), scale.data_ptr(), nv.code(scale_dtype), eps, int(stochastic), seed, offset,
+            nv.stream_ptr(dev)))
+    return qt, scale
+
+
+@torch.library.impl(lib, "quantize_tile", "Meta")
+def _(x, tile_r, tile_c, out_dtype, scale_dtype, eps):
+    sr, sc = -(-x.shape[0] // tile_r), -(-x.shape[1] // tile_c)
+    return x.new_empty(x.shape, dtype=out_dtype), x.new_empty((sr, sc), dtype=scale_dtype)
+
+
+@torch.library.impl(lib, "quantize_tile", "CUDA")
+def _(x, tile_r, tile_c, out_dtype, scale_dtype, eps):
+    x = _rows_view(x)
+    dev = nv.require_cuda(x)
+    rows, cols = x.shape
+    q = torch.empty((rows, cols), dtype=out_dtype, device=dev)
+    scale = torch.empty((-(-rows // tile_r), -(-cols // tile_c)), dtype=scale_dtype, device=dev)
+    with torch.cuda.device(dev):
+        nv.check(nv.load().qt_quantize_tile(
+            x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), tile_r, tile_c, q.data_ptr(),
+            nv.code(out_dtype), scale.data_ptr(), nv.code(scale_dtype), eps, nv.stream_ptr(dev)))
+    return q, scale
+
+
+# ---- Python wrappers --------------------------------------------------------------------------
+
+def _key(x: Tensor, stochastic: bool) -> tuple[int, int]:
+    return next_philox_key(x.device) if stochastic else (0, 0)
+
+
+def quantize_rowwise(x: Tensor, out_dtype: torch.dtype = torch.int8, stochastic_rounding: bool = False, *,
+                     eps: float = 1e-12, scale_dtype: torch.dtype | None = None, key: tuple[int, int] | None = None):
+    """Per-row absmax quantize of a 2-D tensor: returns (q [R,C], scale [R,1]).
+
+    `scale` comes back in `x.dtype` unless `scale_dtype` says otherwise, as quantize_int8 does
+    (subclasses/int8.py:26). `key` = (seed, offset) pins the stochastic-rounding stream.
+    """
+    seed, offset = key if key is not None else _key(x, stochastic_rounding)
+    return lib_ops.quantize_rowwise(x, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
+
+
+def quantize_rowwise_colabsmax(x: Tensor, out_dtype: torch.dtype = torch.int8, stochastic_rounding: bool = False, *,
+                               eps: float = 1e-12, scale_dtype: torch.dtype | None = None,
+                               key: tuple[int, int] | None = None):
+    """quantize_rowwise plus the per-column |x| maximum ([C] float32) from the same pass over x."""
+    seed, offset = key if key is not None else _key(x, stochastic_rounding)
+    return lib_ops.quantize_rowwise_colabsmax(x, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
+
+
+def col_absmax(x: Tensor) -> Tensor:
+    """Per-column |x| maximum of a 2-D tensor, float32 [C]."""
+    return lib_ops.col_absmax(x)
+
+
+def quantize_colwise_t(x: Tensor, out_dtype: torch.dtype = torch.int8, stochastic_rounding: bool = False, *,
+                       eps: float = 1e-12, scale_dtype: torch.dtype | None = None, col_absmax_: Tensor | None = None,
+                       key: tuple[int, int] | None = None):
+    """Per-column absmax quantize with the transpose materialised: returns (q [C,R], scale [C,1]),
+    equal to quantizing `x.T` row-wise and calling `.contiguous()` (subclasses/mixed_precision.py:102-105)."""
+    if col_absmax_ is None:
+        col_absmax_ = lib_ops.col_absmax(x)
+    seed, offset = key if key is not None else _key(x, stochastic_rounding)
+    return lib_ops.quantize_colwise_t(x, col_absmax_, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
+
+
+def quantize_tile(x: Tensor, tile_shape: tuple[int, int], out_dtype: torch.dtype = torch.int8, *, eps: float = 1e-12,
+                  scale_dtype: torch.dtype | None = None):
+    """Per-tile absmax quantize (tiles 1x128 or 128x128): returns (q [R,C], scale [R/tr, C/tc])."""
+    return lib_ops.quantize_tile(x, tile_shape[0], tile_shape[1], out_dtype, scale_dtype or x.dtype, eps)

@@ -1,0 +1,325 @@
+"""Benchmark of the hot path: dynamic row-wise INT8 quantize + scaled INT8 GEMM (A @ B.T) at 8192^3.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--size S]
+
+One "step" is one pass of the path over one batch of synthetic input:
+    weight shard [S/N_gpus, S] bf16 --row-wise quantize--> int8 + scales
+        --all-gather over NCCL (N_gpus > 1)--> full int8 weight [S, S] + scales
+    activation [S, S] bf16 --row-wise quantize--> int8 + scales
+    scaled_mm(int8 A, int8 W^T, row scales, column scales) -> bf16 [S, S]        (tcgen05 kind::i8)
+Every rank runs its own activation batch (weak scaling); the weight all-gather is the only exchange.
+
+The line printed by rank 0 follows the driver's contract: whole-job TOPS (`value`), the same
+measured through the public API from pinned host buffers (`e2e`), the GEMM's roofline, a CPU
+baseline of the same path on the host cores, clocks sampled during the timed region.
+`--impl reference` times the reference's CPU form of the path (oracle/cpu_path.py) instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT), str(ROOT / "quantized-training_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+METRIC = "scaled_int8_gemm_tops"
+UNIT = "TOPS"
+NOMINAL_INT8_DENSE_TOPS = 4500.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--size", type=int, default=8192, help="M = N = K")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return d.get("hbm_gbs"), d.get("bf16_tflops"), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason sampler running beside the timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, reasons = [], set()
+        for line in self.file.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                out["sm_max_mhz"] = float(parts[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        if sm:
+            out["sm_mhz"] = statistics.median(sm)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def cpu_reference_step(A, B):
+    from oracle import cpu_path
+
+    return cpu_path.dynamic_int8_linear(A, B)
+
+
+def time_cpu_path(size: int, steps: int, warmup: int):
+    """Time the reference's CPU form of the path (torch eager quantize + torch._int_mm + scale) with
+    all host threads. Returns (TOPS, threads, seconds per step)."""
+    torch.manual_seed(2024)
+    A = torch.randn(size, size).bfloat16()
+    B = (torch.randn(size, size) * 0.02).bfloat16()
+    for _ in range(warmup):
+        cpu_reference_step(A, B)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_reference_step(A, B)
+    dt = (time.perf_counter() - t0) / steps
+    return 2.0 * size ** 3 / dt / 1e12, torch.get_num_threads(), dt
+
+
+def run_reference(args, rank: int):
+    """`--impl reference`: the reference's own CPU implementation of the path, rank 0 only."""
+    if rank != 0:
+        return
+    size = args.size
+    # a full 8192^3 pass is seconds of CPU work; cap the number of passes so the run stays bounded
+    steps = max(1, min(args.steps, 5))
+    warmup = max(1, min(args.warmup, 1))
+    tops, threads, dt = time_cpu_path(size, steps, warmup)
+    sample = f"{steps} full passes of the {size}^3 workload after {warmup} warm-up (of --steps {args.steps})"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": f"rowwise dynamic INT8 quantize + scaled INT8 GEMM A@B.T, M=N=K={size}, bf16 in/out",
+                   "where": "host CPU cores, torch eager quantize + torch._int_mm + scale (oracle/cpu_path.py)"},
+        "cpu_baseline": {"value": tops, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback (use --impl reference for the CPU arm)")
+
+    import gn_kernels
+    from gn_kernels import _native
+
+    _native.load()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    S = args.size
+    assert S % world == 0, "the weight rows must split evenly over the ranks"
+    shard_rows = S // world
+    torch.manual_seed(2024 + rank)
+    A_host = torch.randn(S, S).bfloat16().pin_memory()
+    torch.manual_seed(2024)  # the weight is the same tensor on every rank; each rank owns a row slice
+    W_full_host = (torch.randn(S, S) * 0.02).bfloat16()
+    W_host = W_full_host[rank * shard_rows:(rank + 1) * shard_rows].contiguous().pin_memory()
+    del W_full_host
+    A = A_host.to(dev)
+    W = W_host.to(dev)
+    out_host = torch.empty((S, S), dtype=torch.bfloat16).pin_memory()
+
+    wq_full = torch.empty((S, S), dtype=torch.int8, device=dev)
+    ws_full = torch.empty((S, 1), dtype=torch.bfloat16, device=dev)
+    gemm_events = []
+
+    def step(a_dev, w_dev, record_gemm=False):
+        wq, ws = gn_kernels.quantize_rowwise(w_dev)
+        if world > 1:
+            dist.all_gather_into_tensor(wq_full, wq)
+            dist.all_gather_into_tensor(ws_full, ws)
+            wq_all, ws_all = wq_full, ws_full
+        else:
+            wq_all, ws_all = wq, ws
+        aq, as_ = gn_kernels.quantize_rowwise(a_dev)
+        if record_gemm:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        out = gn_kernels.scaled_mm(aq, wq_all.T, as_, ws_all.view(1, -1))
+        if record_gemm:
+            e1.record()
+            gemm_events.append((e0, e1))
+        return out
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing ---------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step(A, W)
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        out = step(A, W, record_gemm=True)
+    stop.record()
+    sync_all()
+    ms_total = max_over_ranks(start.elapsed_time(stop))
+    ms_per_step = ms_total / args.steps
+    gemm_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in gemm_events)
+    status = _native.device_status()
+    if status != 0:
+        raise SystemExit(f"a kernel reported a bounded wait that ran out (status {status:#x})")
+
+    # ---- end to end through the public API from pinned host buffers -----------------------------
+    def e2e_step():
+        a_dev = A_host.to(dev, non_blocking=True)
+        w_dev = W_host.to(dev, non_blocking=True)
+        o = step(a_dev, w_dev)
+        out_host.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    e2e_steps = max(3, min(args.steps, 10))
+    s2, t2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t2.record()
+    sync_all()
+    e2e_ms = max_over_ranks(s2.elapsed_time(t2)) / e2e_steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    flops = 2.0 * S ** 3
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
+    hbm_peak, bf16_peak, peak_kind = measured_peaks()
+    int8_peak = 2.0 * bf16_peak  # kind::i8 issues at twice the bf16 rate; the driver measures bf16 only
+    achieved = flops / (gemm_ms * 1e-3) / 1e12
+    traffic_path = ROOT / "profiles" / "gemm_scaled_int8_traffic.json"
+    traffic = None
+    if traffic_path.exists():
+        try:
+            traffic = json.loads(traffic_path.read_text()).get("dram_bytes_per_launch_8192")
+        except Exception:
+            traffic = None
+
+    cpu_baseline = None
+    if not args.no_cpu_baseline:
+        tops, threads, dt = time_cpu_path(S, 3 if S >= 8192 else 5, 1)
+        cpu_baseline = {"value": tops, "unit": UNIT, "cores": threads, "kind": "port",
+                        "sample": f"3 full passes of the {S}^3 workload after 1 warm-up ({dt:.2f} s each), torch eager quantize + torch._int_mm on the host"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {
+            "workload": f"rowwise dynamic INT8 quantize (activation + weight shard) + scaled INT8 GEMM A@B.T, M=N=K={S} per GPU, bf16 in/out",
+            "weight_all_gather": "int8 rows + bf16 scales over NCCL" if world > 1 else "none (1 GPU)",
+            "l2": "inputs larger than L2 (2 x 134 MB bf16 in, 2 x 67 MB int8 operands, 134 MB out per step)",
+            "value_is": "2*M*N*K * n_gpus / step time; the step includes both quantize kernels",
+        },
+        "gemm_only": {"tops": achieved, "ms": gemm_ms},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
+                     "frac": achieved / int8_peak, "traffic": traffic,
+                     "peak_is": f"2 x {peak_kind} dense bf16 burst ({bf16_peak} TF/s); nominal dense INT8 is {NOMINAL_INT8_DENSE_TOPS} TOPS",
+                     "kernel": "gemm_kernel<int8, row/col-scaled, K-major A, K-major B>"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": A_host.numel() * 2 + W_host.numel() * 2,
+                "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": e2e_ms},
+        "gpu_launches": 3 * args.steps,
+        "clocks": clocks,
+    }
+    if cpu_baseline is not None:
+        line["cpu_baseline"] = cpu_baseline
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

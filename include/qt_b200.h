@@ -164,6 +164,49 @@ int qt_tile_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, co
                       int qk, int scale_dtype, void* c, int64_t ldc, int64_t M, int64_t N, int64_t K,
                       void* stream);
 
+/* ---- BitNet b1.58 weight path ------------------------------------------------------------------ */
+
+/*
+ * out[0] = mean(|x|) in fp32 over numel elements (deterministic two-stage reduction).
+ * workspace: caller-provided scratch of at least 8192 bytes, 8-byte aligned; contents undefined
+ * afterwards. replaces: get_bitnet_scale, subclasses/bitnet.py:110-112.
+ */
+int qt_abs_mean(const void* x, int x_dtype, int64_t numel, float* out, void* workspace,
+                int64_t workspace_bytes, void* stream);
+
+/*
+ * Ternary weight quantize: q = clip(round_half_even(w / max(scale[0], eps)), -1, 1), scale a device
+ * fp32 scalar. pack_2bit == 0: out is int8 [numel]. pack_2bit != 0: out is int8 [numel/4], four
+ * 2-bit two's-complement values per byte, the first in the top bits (numel % 4 == 0; rows of a
+ * [N,K] weight pack along K when K % 4 == 0).
+ * replaces: quantize_bitnet_weight + _pack_i2_in_i8, subclasses/bitnet.py:115-118,185-195.
+ */
+int qt_bitnet_quantize_weight(const void* w, int w_dtype, int64_t numel, const float* scale, float eps,
+                              void* out, int pack_2bit, void* stream);
+
+/*
+ * Inverse of the 2-bit packing: int8 [numel_packed] -> int8 [4 * numel_packed], sign-extended.
+ * replaces: _unpack_i2_in_i8, subclasses/bitnet.py:198-201.
+ */
+int qt_unpack_i2(const void* packed, int64_t numel_packed, void* out, void* stream);
+
+/* ---- optimizer ------------------------------------------------------------------------------- */
+
+/*
+ * One AdamW step on one parameter tensor with bf16 states: fp32 math, states written back in bf16,
+ * a bf16 parameter written back with stochastic rounding (bits + 16 random bits, truncated) when
+ * stochastic != 0, otherwise round-to-nearest; an fp32 parameter is written back as is.
+ * beta1/beta2 are doubles because the reference forms the lerp weight (1 - beta) in double before
+ * it is rounded to fp32. bias_correction1 = 1 - beta1^step and sqrt_bias_correction2 =
+ * sqrt(1 - beta2^step) are computed by the caller in fp32. exp_avg / exp_avg_sq are bf16 [numel].
+ * replaces: other_optim/bf16_sr.py:78-124 (adamw), called per parameter from AdamWBF16SR.step :30-75.
+ */
+int qt_adamw_bf16_sr(void* p, int p_dtype, const void* grad, int grad_dtype, void* exp_avg,
+                     void* exp_avg_sq, int64_t numel, float lr, double beta1, double beta2,
+                     float weight_decay, float eps, float bias_correction1,
+                     float sqrt_bias_correction2, int stochastic, uint64_t seed, uint64_t offset,
+                     void* stream);
+
 /* ---- self-tests ------------------------------------------------------------------------------ */
 
 /*

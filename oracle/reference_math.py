@@ -348,10 +348,36 @@ def adamw_bf16_sr(p, grad, step: float, exp_avg, exp_avg_sq, lr: float, beta1: f
     return out_p, round_to_bf16(new_m), round_to_bf16(new_v)
 
 
+def fma32(a: np.ndarray, b: np.ndarray, c: np.ndarray) -> np.ndarray:
+    """Correctly rounded fp32 fused multiply-add a*b + c, computed through float64.
+
+    The product of two fp32 values is exact in float64; the float64 sum is rounded once, and the
+    rare double-rounding case (the float64 sum lands exactly on an fp32 tie while the discarded
+    error is non-zero) is repaired with the exact TwoSum error term."""
+    a64, b64, c64 = (np.asarray(t, dtype=np.float32).astype(np.float64) for t in (a, b, c))
+    prod = a64 * b64
+    s = prod + c64
+    bb = s - prod
+    err = (prod - (s - bb)) + (c64 - bb)
+    r = s.astype(np.float32)
+    d = s - r.astype(np.float64)
+    up = np.nextafter(r, np.float32(np.inf)).astype(np.float64)
+    dn = np.nextafter(r, np.float32(-np.inf)).astype(np.float64)
+    with np.errstate(invalid="ignore"):
+        tie_up = (d > 0) & (d == (up - r.astype(np.float64)) / 2) & (err > 0)
+        tie_dn = (d < 0) & (d == (dn - r.astype(np.float64)) / 2) & (err < 0)
+    r = np.where(tie_up, up.astype(np.float32), r)
+    r = np.where(tie_dn, dn.astype(np.float32), r)
+    return r.astype(np.float32)
+
+
 def lerp(a: np.ndarray, b: np.ndarray, w: np.float32) -> np.ndarray:
-    """torch.lerp for a scalar weight < 0.5: a + w * (b - a), fp32 (ATen lerp formula)."""
+    """torch.lerp with a scalar weight: ATen evaluates `a + w * (b - a)` for |w| < 0.5 as one fused
+    multiply-add (vectorised fmadd on CPU, contracted FFMA on CUDA), else `b - (b - a) * (1 - w)`
+    the same way."""
     a = np.asarray(a, dtype=np.float32)
     b = np.asarray(b, dtype=np.float32)
-    if w < 0.5:
-        return (a + (w * (b - a).astype(np.float32)).astype(np.float32)).astype(np.float32)
-    return (b - ((b - a).astype(np.float32) * (np.float32(1) - w)).astype(np.float32)).astype(np.float32)
+    diff = (b - a).astype(np.float32)
+    if abs(w) < 0.5:
+        return fma32(np.full_like(diff, w), diff, a)
+    return fma32(-diff, np.full_like(diff, np.float32(1) - w), b)

@@ -1,0 +1,169 @@
+// AdamW with bf16 optimizer states and a stochastically rounded bf16 weight write-back, one fused
+// HBM pass per parameter tensor (14 bytes per bf16 parameter: read p, g, m, v; write p, m, v).
+//
+// Arithmetic follows `adamw` of the reference project (other_optim/bf16_sr.py:78-124), evaluated
+// op by op in fp32 the way its eager form does:
+//   m' = lerp(m, g, 1-beta1) ; v' = lerp(v, g*g, 1-beta2)          (lerp = one fused multiply-add)
+//   denom = sqrt(v') / sqrt(bc2) + eps ; numer = m' / bc1
+//   p' = (p - (lr*wd) * p) - (lr * numer) / denom
+//   bf16 weights: bits(p') + 16 random bits, low 16 bits dropped     (bf16_sr.py:108-122)
+// The bias corrections bc1, bc2 and sqrt(bc2) are computed by the caller (they are scalars).
+#include "common.cuh"
+
+namespace qt {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+struct AdamParams {
+    void* p;
+    const void* g;
+    __nv_bfloat16* m;
+    __nv_bfloat16* v;
+    int64_t n;
+    float lr_wd, lr, w1, w2, bc1, sqrt_bc2, eps;
+    int stochastic;
+    uint64_t seed, offset;
+};
+
+template <typename T>
+__device__ __forceinline__ float ld(const T* p, int64_t i);
+template <>
+__device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+template <>
+__device__ __forceinline__ float ld<float>(const float* p, int64_t i) { return p[i]; }
+
+__device__ __forceinline__ float lerp_fma(float a, float b, float w) {
+    const float diff = __fsub_rn(b, a);
+    return fabsf(w) < 0.5f ? __fmaf_rn(w, diff, a) : __fmaf_rn(-diff, __fsub_rn(1.0f, w), b);
+}
+
+// One element. Returns the fp32 updated weight; writes m, v through references.
+__device__ __forceinline__ float adam_update(float p, float g, float& m, float& v, const AdamParams& a) {
+    m = lerp_fma(m, g, a.w1);
+    v = lerp_fma(v, __fmul_rn(g, g), a.w2);
+    const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), a.sqrt_bc2), a.eps);
+    const float numer = __fdiv_rn(m, a.bc1);
+    const float decayed = __fsub_rn(p, __fmul_rn(a.lr_wd, p));
+    return __fsub_rn(decayed, __fdiv_rn(__fmul_rn(a.lr, numer), denom));
+}
+
+__device__ __forceinline__ uint32_t sr_bf16_bits(float x, uint32_t rand16) {
+    return (__float_as_uint(x) + (rand16 & 0xFFFFu)) >> 16;
+}
+
+template <typename PT, typename GT>
+__global__ void __launch_bounds__(kThreads) adamw_kernel(const AdamParams a) {
+    PT* p = reinterpret_cast<PT*>(a.p);
+    const GT* g = reinterpret_cast<const GT*>(a.g);
+    const int64_t n4 = (a.n + 3) / 4;
+    for (int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x; q < n4; q += (int64_t)gridDim.x * kThreads) {
+        const int64_t i0 = q * 4;
+        Philox4 r = {0, 0, 0, 0};
+        if (a.stochastic) r = philox4x32_10((uint64_t)q, a.offset, a.seed);
+        const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+        if (i0 + 4 <= a.n) {
+            float pv[4], gv[4], mv[4], vv[4];
+            // 4 consecutive elements: 8-byte (bf16) or 16-byte (fp32) accesses; tensors from the
+            // caching allocator are at least 16-byte aligned and i0 is a multiple of 4
+            if constexpr (sizeof(PT) == 2) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(p + i0);
+                pv[0] = __uint_as_float(raw.x << 16); pv[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+                pv[2] = __uint_as_float(raw.y << 16); pv[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+            } else {
+                const float4 raw = *reinterpret_cast<const float4*>(p + i0);
+                pv[0] = raw.x; pv[1] = raw.y; pv[2] = raw.z; pv[3] = raw.w;
+            }
+            if constexpr (sizeof(GT) == 2) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(g + i0);
+                gv[0] = __uint_as_float(raw.x << 16); gv[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+                gv[2] = __uint_as_float(raw.y << 16); gv[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+            } else {
+                const float4 raw = *reinterpret_cast<const float4*>(g + i0);
+                gv[0] = raw.x; gv[1] = raw.y; gv[2] = raw.z; gv[3] = raw.w;
+            }
+            {
+                const uint2 rm = *reinterpret_cast<const uint2*>(a.m + i0);
+                const uint2 rv = *reinterpret_cast<const uint2*>(a.v + i0);
+                mv[0] = __uint_as_float(rm.x << 16); mv[1] = __uint_as_float(rm.x & 0xFFFF0000u);
+                mv[2] = __uint_as_float(rm.y << 16); mv[3] = __uint_as_float(rm.y & 0xFFFF0000u);
+                vv[0] = __uint_as_float(rv.x << 16); vv[1] = __uint_as_float(rv.x & 0xFFFF0000u);
+                vv[2] = __uint_as_float(rv.y << 16); vv[3] = __uint_as_float(rv.y & 0xFFFF0000u);
+            }
+            float np[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) np[k] = adam_update(pv[k], gv[k], mv[k], vv[k], a);
+            uint2 om, ov;
+            {
+                const __nv_bfloat162 m01 = __floats2bfloat162_rn(mv[0], mv[1]), m23 = __floats2bfloat162_rn(mv[2], mv[3]);
+                const __nv_bfloat162 v01 = __floats2bfloat162_rn(vv[0], vv[1]), v23 = __floats2bfloat162_rn(vv[2], vv[3]);
+                om.x = *reinterpret_cast<const uint32_t*>(&m01); om.y = *reinterpret_cast<const uint32_t*>(&m23);
+                ov.x = *reinterpret_cast<const uint32_t*>(&v01); ov.y = *reinterpret_cast<const uint32_t*>(&v23);
+            }
+            *reinterpret_cast<uint2*>(a.m + i0) = om;
+            *reinterpret_cast<uint2*>(a.v + i0) = ov;
+            if constexpr (sizeof(PT) == 2) {
+                uint32_t b[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    b[k] = a.stochastic ? sr_bf16_bits(np[k], rw[k]) : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(np[k]));
+                *reinterpret_cast<uint2*>(p + i0) = make_uint2((b[0] & 0xFFFFu) | (b[1] << 16), (b[2] & 0xFFFFu) | (b[3] << 16));
+            } else {
+                *reinterpret_cast<float4*>(p + i0) = make_float4(np[0], np[1], np[2], np[3]);
+            }
+        } else {
+            for (int k = 0; k < 4 && i0 + k < a.n; ++k) {
+                const int64_t i = i0 + k;
+                float m = __bfloat162float(a.m[i]), v = __bfloat162float(a.v[i]);
+                const float np = adam_update(ld<PT>(p, i), ld<GT>(g, i), m, v, a);
+                a.m[i] = __float2bfloat16_rn(m);
+                a.v[i] = __float2bfloat16_rn(v);
+                if constexpr (sizeof(PT) == 2) {
+                    const uint32_t b = a.stochastic ? sr_bf16_bits(np, rw[k]) : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(np));
+                    p[i] = __ushort_as_bfloat16((unsigned short)(b & 0xFFFFu));
+                } else {
+                    p[i] = np;
+                }
+            }
+        }
+    }
+}
+
+}  // namespace
+
+}  // namespace qt
+
+using namespace qt;
+
+extern "C" int qt_adamw_bf16_sr(void* p, int p_dtype, const void* grad, int grad_dtype, void* exp_avg, void* exp_avg_sq,
+                                int64_t numel, float lr, double beta1, double beta2, float weight_decay, float eps,
+                                float bias_correction1, float sqrt_bias_correction2, int stochastic, uint64_t seed,
+                                uint64_t offset, void* stream_) {
+    QT_REQUIRE(p_dtype == QT_BF16 || p_dtype == QT_F32, "adamw: parameter dtype must be QT_BF16 or QT_F32 (got %d)", p_dtype);
+    QT_REQUIRE(grad_dtype == QT_BF16 || grad_dtype == QT_F32, "adamw: gradient dtype must be QT_BF16 or QT_F32 (got %d)", grad_dtype);
+    QT_REQUIRE(numel >= 0, "adamw: negative numel");
+    QT_REQUIRE(!stochastic || p_dtype == QT_BF16, "adamw: stochastic rounding applies to bf16 parameters only");
+    if (numel == 0) return QT_OK;
+    QT_REQUIRE(p && grad && exp_avg && exp_avg_sq, "adamw: null pointer");
+    QT_REQUIRE(aligned_to(p, 16) && aligned_to(grad, 16) && aligned_to(exp_avg, 8) && aligned_to(exp_avg_sq, 8),
+               "adamw: tensors must be 16-byte aligned");
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    AdamParams a;
+    a.p = p; a.g = grad; a.m = reinterpret_cast<__nv_bfloat16*>(exp_avg); a.v = reinterpret_cast<__nv_bfloat16*>(exp_avg_sq);
+    a.n = numel;
+    a.lr = lr; a.lr_wd = lr * weight_decay;  // fp32 product, as `lr * weight_decay` on an fp32 lr tensor
+    // lerp weights: the Python doubles (1 - beta) rounded to fp32, as ATen does for an fp32 tensor
+    a.w1 = (float)(1.0 - beta1); a.w2 = (float)(1.0 - beta2);
+    a.bc1 = bias_correction1; a.sqrt_bc2 = sqrt_bias_correction2; a.eps = eps;
+    a.stochastic = stochastic; a.seed = seed; a.offset = offset;
+    const int64_t want = ((numel + 3) / 4 + kThreads - 1) / kThreads;
+    const int64_t cap = (int64_t)num_sms() * 16;
+    const int grid = (int)(want < cap ? want : cap);
+    if (p_dtype == QT_BF16 && grad_dtype == QT_BF16) adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, stream>>>(a);
+    else if (p_dtype == QT_BF16) adamw_kernel<__nv_bfloat16, float><<<grid, kThreads, 0, stream>>>(a);
+    else if (grad_dtype == QT_BF16) adamw_kernel<float, __nv_bfloat16><<<grid, kThreads, 0, stream>>>(a);
+    else adamw_kernel<float, float><<<grid, kThreads, 0, stream>>>(a);
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}

@@ -12,7 +12,11 @@
 // fused residual correction (3 full-rate ops instead of the ~10 of div.rn). qt_selftest_division
 // checks that sequence against div.rn over every (bf16 x, bf16 absmax) pair; fp32 inputs use
 // div.rn directly.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace qt {
 
@@ -93,6 +97,7 @@ struct Divider {
     float d, r;
     bool tiny;  // reciprocal would overflow: use div.rn
     __device__ __forceinline__ explicit Divider(float d_) : d(d_), r(recip_rn(d_)), tiny(d_ < 1e-30f) {}
+    __device__ __forceinline__ Divider(float d_, float r_) : d(d_), r(r_), tiny(d_ < 1e-30f) {}
     __device__ __forceinline__ float operator()(float x) const {
         if (EXACT || tiny) {
             return div_rn(x, d);
@@ -120,6 +125,17 @@ __device__ __forceinline__ uint32_t int8_sr(float v, float u) {
     float r = __fsub_rn(__fadd_rn(w, kRoundMagic), kRoundMagic);  // nearest integer
     if (r > w) r -= 1.0f;                                          // -> floor
     return __float_as_uint(__fadd_rn(r, kRoundMagic)) & 0xFFu;
+}
+
+// f[k] <- f[k] / d for 8 values. The reciprocal sequence returns +0 for -0; fp8 keeps the sign of
+// zero, so zero inputs pass through unchanged there.
+template <bool EXACT>
+__device__ __forceinline__ void divide8(float (&f)[8], const Divider<EXACT>& div, bool keep_zero_sign) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float q = div(f[k]);
+        f[k] = (keep_zero_sign && f[k] == 0.0f) ? f[k] : q;
+    }
 }
 
 // Quantize 8 pre-divided values into 8 bytes (two 32-bit words).
@@ -205,59 +221,140 @@ struct RowwiseParams {
     int vec_load, vec_store;
 };
 
-// TPR threads cooperate on one row, each holding VPT vectors of 8 elements in registers, so a row
-// of up to TPR*VPT*8 columns is read from HBM exactly once. With COLABS each thread also keeps the
-// running |x| maximum of its columns over all rows the CTA visits; the CTA folds those into one
-// atomic max per column at the end.
-template <typename XT, int TPR, int VPT, bool COLABS>
-__global__ void __launch_bounds__(kThreads) rowwise_kernel(const RowwiseParams p) {
+// ---- packed bf16 helpers -----------------------------------------------------------------------
+
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t w) { return *reinterpret_cast<const __nv_bfloat162*>(&w); }
+__device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<const uint32_t*>(&v); }
+
+// |x| of both halves (clear the sign bits) and the lane-wise maximum of two packed pairs.
+__device__ __forceinline__ uint32_t abs2(uint32_t w) { return w & 0x7FFF7FFFu; }
+__device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) { return as_u32(__hmax2(as_bf162(a), as_bf162(b))); }
+
+// Four rounded floats (value + kRoundMagic) -> four int8 bytes: the low mantissa byte of each.
+__device__ __forceinline__ uint32_t pack4_magic(float t0, float t1, float t2, float t3) {
+    const uint32_t lo = __byte_perm(__float_as_uint(t0), __float_as_uint(t1), 0x0040);
+    const uint32_t hi = __byte_perm(__float_as_uint(t2), __float_as_uint(t3), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
+}
+
+// Quantize the 8 bf16 values of `raw` (element index idx of the output) with divider `div`.
+// No clamp on the round-half-even int8 path: |x| <= absmax and d >= absmax/127 * (1 - 2^-24) bound
+// the quotient by 127.00001, which rounds to 127.
+template <bool SR>
+__device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider<false>& div, int q_dtype, int64_t idx,
+                                               uint64_t seed, uint64_t offset) {
+    float f[8];
+    f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+    f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+    f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xFFFF0000u);
+    f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xFFFF0000u);
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = div(f[k]);
+    uint2 out;
+    if (q_dtype == QT_I8) {
+        if constexpr (SR) {
+            float u[8];
+            uniforms8(u, idx, seed, offset);
+            uint32_t b[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) b[k] = int8_sr(v[k], u[k]);
+            out.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+            out.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = __fadd_rn(v[k], kRoundMagic);
+            out.x = pack4_magic(v[0], v[1], v[2], v[3]);
+            out.y = pack4_magic(v[4], v[5], v[6], v[7]);
+        }
+    } else {
+        const __nv_fp8_interpretation_t kind = (q_dtype == QT_E4M3) ? __NV_E4M3 : __NV_E5M2;
+        uint32_t h[4];
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) {
+            // the reciprocal sequence returns +0 for x = -0; restore the sign of zero inputs
+            const float a = (f[k] == 0.0f) ? f[k] : v[k];
+            const float b = (f[k + 1] == 0.0f) ? f[k + 1] : v[k + 1];
+            h[k >> 1] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, kind);
+        }
+        out.x = h[0] | (h[1] << 16);
+        out.y = h[2] | (h[3] << 16);
+    }
+    return out;
+}
+
+// Row-wise kernel for bf16 rows that fit in registers. TPR threads cooperate on one row, each
+// holding VPT 16-byte vectors, so a row of up to TPR*VPT*8 columns is read from HBM exactly once.
+// The next row's loads are issued before the current row is reduced and quantized (register double
+// buffer), which keeps HBM requests in flight through the reduction and the stores. With COLABS
+// each thread also keeps the running |x| maximum of its columns (packed bf16 pairs) over all rows
+// the CTA visits; the CTA folds those into one atomic max per column at the end.
+template <int TPR, int VPT, bool COLABS, bool SR>
+__global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (COLABS || SR ? 3 : 4) : (VPT <= 8 ? 2 : 1)))
+rowwise_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;  // rows per CTA per iteration
     constexpr int WPR = TPR / 32;        // warps per row
-    constexpr bool EXACT_DIV = sizeof(XT) != 2;
+    constexpr bool PREFETCH = VPT <= 4;
     __shared__ float s_red[kThreads / 32];
-    __shared__ float s_col[(COLABS && RPC > 1) ? TPR * VPT * 8 : 1];
+    __shared__ uint32_t s_col[COLABS ? TPR * VPT * 4 : 1];  // packed bf16 pairs, one per two columns
 
     const int sub = threadIdx.x / TPR;
     const int t = threadIdx.x % TPR;
     const int warp = threadIdx.x >> 5;
-    const XT* x = reinterpret_cast<const XT*>(p.x);
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x);
     const float qmax = qmax_of(p.q_dtype);
+    const int64_t step = (int64_t)gridDim.x * RPC;
 
-    float colmax[COLABS ? VPT : 1][8];
+    uint32_t colmax[COLABS ? VPT : 1][4];
     if constexpr (COLABS) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i)
 #pragma unroll
-            for (int k = 0; k < 8; ++k) colmax[i][k] = 0.0f;
-        if constexpr (RPC > 1) {
-            for (int i = threadIdx.x; i < TPR * VPT * 8; i += kThreads) s_col[i] = 0.0f;
-        }
+            for (int k = 0; k < 4; ++k) colmax[i][k] = 0u;
+        for (int i = threadIdx.x; i < TPR * VPT * 4; i += kThreads) s_col[i] = 0u;
+        __syncthreads();
     }
 
-    for (int64_t base = (int64_t)blockIdx.x * RPC; base < p.rows; base += (int64_t)gridDim.x * RPC) {
-        const int64_t row = base + sub;
+    auto load_row = [&](uint4 (&v)[VPT], int64_t row) {
         const bool valid = row < p.rows;
-        const XT* xrow = x + (valid ? row : 0) * p.stride;
-
-        Vec8<XT> v[VPT];
-        float amax = 0.0f;
+        const __nv_bfloat16* xrow = x + (valid ? row : 0) * p.stride;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int64_t col = ((int64_t)i * TPR + t) * 8;
-            if (valid && col < p.cols) load_vec8<XT>(v[i], xrow, col, p.cols, p.vec_load != 0);
-            else v[i].zero();
-        }
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            float f[8];
-            v[i].unpack(f);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float a = fabsf(f[k]);
-                amax = fmaxf(amax, a);
-                if constexpr (COLABS) colmax[i][k] = fmaxf(colmax[i][k], a);
+            if (valid && col + 8 <= p.cols) {
+                v[i] = *reinterpret_cast<const uint4*>(xrow + col);
+            } else if (valid && col < p.cols) {
+                Vec8<__nv_bfloat16> tmp;
+                load_vec8<__nv_bfloat16>(tmp, xrow, col, p.cols, false);
+                v[i] = tmp.raw;
+            } else {
+                v[i] = make_uint4(0, 0, 0, 0);
             }
         }
+    };
+
+    uint4 cur[VPT], nxt[PREFETCH ? VPT : 1];
+    int64_t base = (int64_t)blockIdx.x * RPC;
+    if (base < p.rows) load_row(cur, base + sub);
+
+    for (; base < p.rows; base += step) {
+        const int64_t row = base + sub;
+        const bool valid = row < p.rows;
+        if constexpr (PREFETCH) {
+            if (base + step < p.rows) load_row(nxt, base + step + sub);
+        }
+
+        uint32_t m2 = 0u;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const uint32_t a0 = abs2(cur[i].x), a1 = abs2(cur[i].y), a2 = abs2(cur[i].z), a3 = abs2(cur[i].w);
+            m2 = max2(m2, max2(max2(a0, a1), max2(a2, a3)));
+            if constexpr (COLABS) {
+                colmax[i][0] = max2(colmax[i][0], a0); colmax[i][1] = max2(colmax[i][1], a1);
+                colmax[i][2] = max2(colmax[i][2], a2); colmax[i][3] = max2(colmax[i][3], a3);
+            }
+        }
+        float amax = fmaxf(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xFFFF0000u));
         amax = warp_max(amax);
         if constexpr (WPR > 1) {
             if ((threadIdx.x & 31) == 0) s_red[warp] = amax;
@@ -268,46 +365,65 @@ __global__ void __launch_bounds__(kThreads) rowwise_kernel(const RowwiseParams p
             __syncthreads();
         }
 
-        const float scale = __fdiv_rn(amax, qmax);
-        const Divider<EXACT_DIV> div(fmaxf(scale, p.eps));
+        const float scale = div_rn(amax, qmax);
+        const Divider<false> div(fmaxf(scale, p.eps));
         if (valid && t == 0) store_scale(p.scale, p.scale_dtype, row, scale);
 
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int64_t col = ((int64_t)i * TPR + t) * 8;
             if (valid && col < p.cols) {
-                float f[8], u[8];
-                v[i].unpack(f);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) f[k] = div(f[k]);
                 const int64_t idx = row * p.cols + col;
-                if (p.stochastic) uniforms8(u, idx, p.seed, p.offset);
-                const uint2 bytes = pack8(f, p.q_dtype, p.stochastic != 0, u);
+                const uint2 bytes = quantize_vec8<SR>(cur[i], div, p.q_dtype, idx, p.seed, p.offset);
                 store_bytes8(p.q, idx, p.cols - col, bytes, p.vec_store != 0);
             }
+        }
+
+        if constexpr (PREFETCH) {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) cur[i] = nxt[i];
+        } else {
+            if (base + step < p.rows) load_row(cur, base + step + sub);
         }
     }
 
     if constexpr (COLABS) {
+        constexpr int PAIRS = TPR * VPT * 4;
+        // 1. fold the CTA's sub-rows (they cover the same columns) in shared memory
         if constexpr (RPC > 1) {
-            __syncthreads();
+#pragma unroll 1
+            for (int turn = 0; turn < RPC; ++turn) {
+                if (sub == turn) {
 #pragma unroll
-            for (int i = 0; i < VPT; ++i)
+                    for (int i = 0; i < VPT; ++i)
 #pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    atomicMax(reinterpret_cast<unsigned int*>(&s_col[(i * TPR + t) * 8 + k]), __float_as_uint(colmax[i][k]));
-            __syncthreads();
-            for (int c = threadIdx.x; c < TPR * VPT * 8; c += kThreads)
-                if (c < p.cols) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c), __float_as_uint(s_col[c]));
+                        for (int k = 0; k < 4; ++k) {
+                            const int pair = (i * TPR + t) * 4 + k;
+                            s_col[pair] = max2(s_col[pair], colmax[i][k]);
+                        }
+                }
+                __syncthreads();
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const int64_t c = ((int64_t)i * TPR + t) * 8 + k;
-                    if (c < p.cols) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c), __float_as_uint(colmax[i][k]));
-                }
+                for (int k = 0; k < 4; ++k) s_col[(i * TPR + t) * 4 + k] = colmax[i][k];
         }
+        // 2. fold the CTAs of the thread-block cluster through distributed shared memory; each CTA
+        //    owns a slice of the columns and issues one atomic max per column for the whole cluster
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const unsigned n_cta = cluster.num_blocks(), rank = cluster.block_rank();
+        for (int pair = rank * kThreads + threadIdx.x; pair < PAIRS; pair += n_cta * kThreads) {
+            uint32_t m = 0u;
+            for (unsigned c = 0; c < n_cta; ++c) m = max2(m, cluster.map_shared_rank(s_col, c)[pair]);
+            const int64_t c0 = (int64_t)pair * 2;
+            // fp32 bit patterns of non-negative values order like unsigned integers
+            if (c0 < p.cols) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c0), m << 16);
+            if (c0 + 1 < p.cols) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c0 + 1), m & 0xFFFF0000u);
+        }
+        cluster.sync();  // nobody leaves while a peer may still read its shared memory
     }
 }
 
@@ -348,36 +464,73 @@ __global__ void __launch_bounds__(kThreads) rowwise_generic_kernel(const Rowwise
     }
 }
 
-template <typename XT, int TPR, int VPT, bool COLABS>
+constexpr int kClusterSize = 8;  // CTAs per cluster in the column-absmax variant (portable maximum)
+
+template <int TPR, int VPT, bool COLABS, bool SR>
 int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
     constexpr int RPC = kThreads / TPR;
+    constexpr int CTAS_PER_SM = (VPT <= 4 ? (COLABS || SR ? 3 : 4) : (VPT <= 8 ? 2 : 1));
     const int64_t want = (p.rows + RPC - 1) / RPC;
-    // With COLABS fewer, longer-lived CTAs mean fewer column atomics.
-    const int64_t cap = (int64_t)num_sms() * (COLABS ? 4 : 8);
-    const int grid = (int)(want < cap ? want : cap);
-    rowwise_kernel<XT, TPR, VPT, COLABS><<<grid, kThreads, 0, stream>>>(p);
+    const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
+    int64_t grid = want < cap ? want : cap;
+    auto kfn = rowwise_kernel<TPR, VPT, COLABS, SR>;
+    if constexpr (COLABS) {
+        grid = (grid + kClusterSize - 1) / kClusterSize * kClusterSize;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = kClusterSize;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        QT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kfn, p));
+    } else {
+        kfn<<<(unsigned)grid, kThreads, 0, stream>>>(p);
+        QT_CUDA_CHECK(cudaGetLastError());
+    }
+    return QT_OK;
+}
+
+template <bool COLABS, bool SR>
+int launch_rowwise_bf16(const RowwiseParams& p, cudaStream_t stream) {
+    const int64_t c = p.cols;
+    if (c <= 256) return launch_rowwise_cfg<32, 1, COLABS, SR>(p, stream);
+    if (c <= 512) return launch_rowwise_cfg<32, 2, COLABS, SR>(p, stream);
+    if (c <= 1024) return launch_rowwise_cfg<32, 4, COLABS, SR>(p, stream);
+    if (c <= 2048) return launch_rowwise_cfg<64, 4, COLABS, SR>(p, stream);
+    if (c <= 4096) return launch_rowwise_cfg<128, 4, COLABS, SR>(p, stream);
+    if (c <= 8192) return launch_rowwise_cfg<256, 4, COLABS, SR>(p, stream);
+    if (c <= 16384) return launch_rowwise_cfg<256, 8, COLABS, SR>(p, stream);
+    if constexpr (!COLABS) return launch_rowwise_cfg<256, 16, COLABS, SR>(p, stream);
+    return fail(QT_ERR_UNSUPPORTED, "unreachable");
+}
+
+template <typename XT, bool COLABS>
+int launch_rowwise_generic(const RowwiseParams& p, cudaStream_t stream) {
+    const int64_t cap = (int64_t)num_sms() * 8;
+    const int grid = (int)(p.rows < cap ? p.rows : cap);
+    rowwise_generic_kernel<XT, COLABS><<<grid, kThreads, 0, stream>>>(p);
     QT_CUDA_CHECK(cudaGetLastError());
     return QT_OK;
 }
 
-template <typename XT, bool COLABS>
-int launch_rowwise(const RowwiseParams& p, cudaStream_t stream) {
-    const int64_t c = p.cols;
-    if (!p.vec_load || c > 32768) {
-        const int64_t cap = (int64_t)num_sms() * 8;
-        const int grid = (int)(p.rows < cap ? p.rows : cap);
-        rowwise_generic_kernel<XT, COLABS><<<grid, kThreads, 0, stream>>>(p);
-        QT_CUDA_CHECK(cudaGetLastError());
-        return QT_OK;
+// Fast path: bf16 rows, 16-byte aligned, that fit the register-resident kernel, with a positive
+// eps (the unclamped rounding relies on max(scale, eps) not being denormal). Everything else --
+// fp32 input, odd alignment, very wide rows -- takes the generic two-pass kernel.
+int launch_rowwise(const RowwiseParams& p, int x_dtype, bool colabs, cudaStream_t stream) {
+    const bool fast = x_dtype == QT_BF16 && p.vec_load && p.eps >= 1e-30f && p.cols <= (colabs ? 16384 : 32768);
+    if (fast) {
+        if (colabs) return p.stochastic ? launch_rowwise_bf16<true, true>(p, stream) : launch_rowwise_bf16<true, false>(p, stream);
+        return p.stochastic ? launch_rowwise_bf16<false, true>(p, stream) : launch_rowwise_bf16<false, false>(p, stream);
     }
-    if (c <= 256) return launch_rowwise_cfg<XT, 32, 1, COLABS>(p, stream);
-    if (c <= 512) return launch_rowwise_cfg<XT, 32, 2, COLABS>(p, stream);
-    if (c <= 1024) return launch_rowwise_cfg<XT, 32, 4, COLABS>(p, stream);
-    if (c <= 2048) return launch_rowwise_cfg<XT, 64, 4, COLABS>(p, stream);
-    if (c <= 4096) return launch_rowwise_cfg<XT, 128, 4, COLABS>(p, stream);
-    if (c <= 8192) return launch_rowwise_cfg<XT, 256, 4, COLABS>(p, stream);
-    if (c <= 16384) return launch_rowwise_cfg<XT, 256, 8, COLABS>(p, stream);
-    return launch_rowwise_cfg<XT, 256, 16, COLABS>(p, stream);
+    if (x_dtype == QT_BF16)
+        return colabs ? launch_rowwise_generic<__nv_bfloat16, true>(p, stream) : launch_rowwise_generic<__nv_bfloat16, false>(p, stream);
+    return colabs ? launch_rowwise_generic<float, true>(p, stream) : launch_rowwise_generic<float, false>(p, stream);
 }
 
 int check_quant_args(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t stride, const void* q,
@@ -412,15 +565,62 @@ int quantize_rowwise_impl(const void* x, int x_dtype, int64_t rows, int64_t cols
     p.vec_load = aligned_to(x, 16) && ((stride * esz) % 16 == 0);
     p.vec_store = aligned_to(q, 8) && (cols % 8 == 0);
 
-    if (x_dtype == QT_BF16)
-        return want_colabs ? launch_rowwise<__nv_bfloat16, true>(p, stream) : launch_rowwise<__nv_bfloat16, false>(p, stream);
-    return want_colabs ? launch_rowwise<float, true>(p, stream) : launch_rowwise<float, false>(p, stream);
+    return launch_rowwise(p, x_dtype, want_colabs, stream);
 }
 
 // ---- column absmax --------------------------------------------------------------------------
 
-// Each CTA owns a strip of 256*8 columns x a slab of rows; threads hold 8 column maxima in
-// registers, then one atomic max per column per CTA.
+// bf16 fast path: a CTA covers 256 columns (lane = 8 columns = 16 bytes, so a warp reads 512
+// contiguous bytes of a row) x a slab of rows (warp w takes rows w, w+8, ...; four rows in flight
+// per thread). Packed bf16 maxima; shared-memory fold over the 8 warps; one atomic per column per CTA.
+__global__ void __launch_bounds__(kThreads) col_absmax_bf16_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows,
+                                                                    int64_t cols, int64_t stride, float* __restrict__ out,
+                                                                    int64_t rows_per_cta) {
+    __shared__ uint32_t s_m[kThreads / 32][32 * 4];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t col = (int64_t)blockIdx.x * 256 + lane * 8;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_cta;
+    const int64_t r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
+    uint32_t m[4] = {0u, 0u, 0u, 0u};
+    if (col < cols) {
+        const bool full = col + 8 <= cols;
+        int64_t r = r0 + warp;
+        for (; r + 24 < r1; r += 32) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (full) v[j] = *reinterpret_cast<const uint4*>(x + (r + 8 * j) * stride + col);
+                else { Vec8<__nv_bfloat16> t; load_vec8<__nv_bfloat16>(t, x + (r + 8 * j) * stride, col, cols, false); v[j] = t.raw; }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                m[0] = max2(m[0], abs2(v[j].x)); m[1] = max2(m[1], abs2(v[j].y));
+                m[2] = max2(m[2], abs2(v[j].z)); m[3] = max2(m[3], abs2(v[j].w));
+            }
+        }
+        for (; r < r1; r += 8) {
+            uint4 v;
+            if (full) v = *reinterpret_cast<const uint4*>(x + r * stride + col);
+            else { Vec8<__nv_bfloat16> t; load_vec8<__nv_bfloat16>(t, x + r * stride, col, cols, false); v = t.raw; }
+            m[0] = max2(m[0], abs2(v.x)); m[1] = max2(m[1], abs2(v.y));
+            m[2] = max2(m[2], abs2(v.z)); m[3] = max2(m[3], abs2(v.w));
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) s_m[warp][lane * 4 + k] = m[k];
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        uint32_t f = 0u;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) f = max2(f, s_m[w][threadIdx.x]);
+        const int64_t c0 = (int64_t)blockIdx.x * 256 + threadIdx.x * 2;
+        if (c0 < cols) atomicMax(reinterpret_cast<unsigned int*>(out + c0), f << 16);
+        if (c0 + 1 < cols) atomicMax(reinterpret_cast<unsigned int*>(out + c0 + 1), f & 0xFFFF0000u);
+    }
+}
+
+// Generic path (fp32 input or unaligned rows): a strip of 256*8 columns x a slab of rows per CTA;
+// threads hold 8 column maxima in registers, then one atomic max per column per CTA.
 template <typename XT>
 __global__ void __launch_bounds__(kThreads) col_absmax_kernel(const XT* __restrict__ x, int64_t rows, int64_t cols,
                                                                int64_t stride, float* __restrict__ out,
@@ -480,7 +680,7 @@ struct ColwiseParams {
 constexpr int kTileR = 128, kTileC = 64;
 
 template <typename XT>
-__global__ void __launch_bounds__(kThreads) colwise_t_kernel(const ColwiseParams p) {
+__global__ void __launch_bounds__(kThreads, 3) colwise_t_kernel(const ColwiseParams p) {
     constexpr bool EXACT_DIV = sizeof(XT) != 2;
     __shared__ uint32_t s_tile[kTileC][kTileR / 4 + 1];
     const XT* x = reinterpret_cast<const XT*>(p.x);
@@ -489,14 +689,16 @@ __global__ void __launch_bounds__(kThreads) colwise_t_kernel(const ColwiseParams
     const int rq = threadIdx.x >> 3;  // row quad (4 rows)
     const int64_t c0 = (int64_t)blockIdx.x * kTileC;
     const int64_t col = c0 + cg * 8;
+    const bool rne_i8 = p.q_dtype == QT_I8 && !p.stochastic;
 
-    // column scales for this thread's 8 columns
-    float dsc[8];
+    // dividers for this thread's 8 columns (one correctly rounded reciprocal each, hoisted)
+    float dsc[8], rcp[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         const float am = (col + k < p.cols) ? p.col_absmax[col + k] : 0.0f;
-        const float sc = __fdiv_rn(am, qmax);
+        const float sc = div_rn(am, qmax);
         dsc[k] = fmaxf(sc, p.eps);
+        rcp[k] = recip_rn(dsc[k]);
         if (blockIdx.y == 0 && rq == 0 && col + k < p.cols) store_scale(p.scale, p.scale_dtype, col + k, sc);
     }
 
@@ -513,23 +715,29 @@ __global__ void __launch_bounds__(kThreads) colwise_t_kernel(const ColwiseParams
         for (int j = 0; j < 4; ++j) v[j].unpack(f[j]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const Divider<EXACT_DIV> div(dsc[k]);
-            uint32_t word = 0;
+            Divider<EXACT_DIV> div(dsc[k], rcp[k]);
+            float q[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float q = div(f[j][k]);
-                uint32_t b;
-                if (p.q_dtype == QT_I8) {
-                    if (p.stochastic) {
+            for (int j = 0; j < 4; ++j) q[j] = div(f[j][k]);
+            uint32_t word;
+            if (rne_i8) {
+                // clamp kept: col_absmax comes from the caller, not from this pass
+#pragma unroll
+                for (int j = 0; j < 4; ++j) q[j] = __fadd_rn(fminf(fmaxf(q[j], -128.0f), 127.0f), kRoundMagic);
+                word = pack4_magic(q[0], q[1], q[2], q[3]);
+            } else {
+                word = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t b;
+                    if (p.q_dtype == QT_I8) {
                         const float u = uniform1((col + k) * p.rows + r0 + j, p.seed, p.offset);
-                        b = int8_sr(q, u);
+                        b = int8_sr(q[j], u);
                     } else {
-                        b = int8_rne(q);
+                        b = quantize_byte(f[j][k] == 0.0f ? f[j][k] : q[j], p.q_dtype, false, 0.0f);
                     }
-                } else {
-                    b = quantize_byte(q, p.q_dtype, false, 0.0f);
+                    word |= b << (8 * j);
                 }
-                word |= b << (8 * j);
             }
             s_tile[cg * 8 + k][rq] = word;
         }
@@ -598,8 +806,7 @@ __global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p
         const Divider<EXACT_DIV> div(fmaxf(sc, p.eps));
         if (valid && l16 == 0) store_scale(p.scale, p.scale_dtype, tile, sc);
         if (valid && col < p.cols) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) f[k] = div(f[k]);
+            divide8(f, div, p.q_dtype != QT_I8);
             const uint2 bytes = pack8(f, p.q_dtype, false, zero_u);
             store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
         }
@@ -647,8 +854,7 @@ __global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams
         if (row < p.rows && col < p.cols) {
             float f[8];
             v[i].unpack(f);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) f[k] = div(f[k]);
+            divide8(f, div, p.q_dtype != QT_I8);
             const uint2 bytes = pack8(f, p.q_dtype, false, zero_u);
             store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
         }
@@ -716,8 +922,22 @@ extern "C" int qt_col_absmax(const void* x, int x_dtype, int64_t rows, int64_t c
     QT_REQUIRE(x, "col_absmax: x is null");
     const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
     const int vec_ok = aligned_to(x, 16) && ((x_row_stride * esz) % 16 == 0);
+    if (x_dtype == QT_BF16 && vec_ok) {
+        const int64_t strips = (cols + 255) / 256;
+        // enough row slabs to fill the machine about eight times over, at least 64 rows each
+        int64_t slabs = ((int64_t)num_sms() * 8 + strips - 1) / strips;
+        const int64_t max_slabs = (rows + 63) / 64;
+        if (slabs > max_slabs) slabs = max_slabs;
+        if (slabs < 1) slabs = 1;
+        if (slabs > 65535) slabs = 65535;
+        int64_t rows_per_cta = (rows + slabs - 1) / slabs;
+        rows_per_cta = (rows_per_cta + 7) / 8 * 8;
+        dim3 grid((unsigned)strips, (unsigned)((rows + rows_per_cta - 1) / rows_per_cta));
+        col_absmax_bf16_kernel<<<grid, kThreads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), rows, cols, x_row_stride, col_absmax, rows_per_cta);
+        QT_CUDA_CHECK(cudaGetLastError());
+        return QT_OK;
+    }
     const int64_t strips = (cols + kThreads * 8 - 1) / (kThreads * 8);
-    // enough row slabs to fill the machine a few times over, at least 32 rows each
     int64_t slabs = ((int64_t)num_sms() * 8 + strips - 1) / strips;
     const int64_t max_slabs = (rows + 31) / 32;
     if (slabs > max_slabs) slabs = max_slabs;

@@ -48,6 +48,11 @@ SIGNATURES = {
     "qt_tile_scaled_mm": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64,
                                   c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int64,
                                   c_int64, c_int64, c_int64, c_void_p]),
+    "qt_abs_mean": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
+    "qt_bitnet_quantize_weight": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_float, c_void_p, c_int, c_void_p]),
+    "qt_unpack_i2": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
+    "qt_adamw_bf16_sr": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_float, ctypes.c_double,
+                                 ctypes.c_double, c_float, c_float, c_float, c_float, c_int, c_uint64, c_uint64, c_void_p]),
     "qt_selftest_division": (c_int, [c_int, c_float, ctypes.POINTER(ctypes.c_ulonglong)]),
 }
 

@@ -1,0 +1,88 @@
+"""AdamWBF16SR: AdamW with bf16 states, fp32 math and stochastically rounded bf16 weights.
+
+Same constructor, state layout (`step`, `exp_avg`, `exp_avg_sq`) and `lr`-as-tensor convention as the
+reference optimizer (other_optim/bf16_sr.py:6-75); the per-parameter update is one fused sm_100a
+kernel (qt_adamw_bf16_sr) instead of a torch.compile'd Python function, and the 16 random bits come
+from Philox inside the kernel instead of a materialised int32 `random_()` tensor.
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+from torch.optim.optimizer import Optimizer, ParamsT
+
+from gn_kernels import _native as nv
+from gn_kernels.quantize import next_philox_key
+
+
+class AdamWBF16SR(Optimizer):
+    def __init__(
+        self,
+        params: ParamsT,
+        lr: float = 1e-3,
+        betas: tuple[float, float] = (0.9, 0.999),
+        eps: float = 1e-8,
+        weight_decay: float = 1e-2,
+    ) -> None:
+        defaults = dict(lr=torch.as_tensor(lr), betas=betas, eps=eps, weight_decay=weight_decay)
+        super().__init__(params, defaults)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+
+        for group in self.param_groups:
+            lr = group["lr"]
+            if not isinstance(lr, Tensor):
+                raise RuntimeError(
+                    "lr was changed to a non-Tensor object. If you want to update lr, please use "
+                    "optim.param_groups[0]['lr'].fill_(new_lr)"
+                )
+            beta1, beta2 = group["betas"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                state = self.state[p]
+                if len(state) == 0:
+                    state["step"] = torch.tensor(0.0)
+                    state["exp_avg"] = torch.zeros_like(p, dtype=torch.bfloat16)
+                    state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.bfloat16)
+                state["step"] += 1
+                adamw(p, p.grad, state["step"], state["exp_avg"], state["exp_avg_sq"], lr, beta1, beta2,
+                      group["weight_decay"], group["eps"], p.dtype is torch.bfloat16)
+        return loss
+
+
+def _local(t: Tensor) -> Tensor:
+    """The local shard of a DTensor (FSDP2 parameters), or the tensor itself."""
+    to_local = getattr(t, "to_local", None)
+    t = to_local() if callable(to_local) else t
+    inner = getattr(t, "_data", None)  # wrapper subclasses over a plain bf16 tensor
+    return inner if isinstance(inner, Tensor) else t
+
+
+def adamw(p: Tensor, grad: Tensor, step: Tensor, exp_avg: Tensor, exp_avg_sq: Tensor, lr: Tensor, beta1: float,
+          beta2: float, weight_decay: float, eps: float, bf16_sr: bool, *, key: tuple[int, int] | None = None) -> None:
+    """One in-place AdamW step on (p, exp_avg, exp_avg_sq); same arguments as the reference's
+    `adamw` (other_optim/bf16_sr.py:78-90). `key` = (seed, offset) pins the random bits."""
+    p, grad, exp_avg, exp_avg_sq = (_local(t) for t in (p, grad, exp_avg, exp_avg_sq))
+    dev = nv.require_cuda(p, grad, exp_avg, exp_avg_sq)
+    if not (p.is_contiguous() and grad.is_contiguous() and exp_avg.is_contiguous() and exp_avg_sq.is_contiguous()):
+        raise ValueError("adamw: tensors must be contiguous")
+    if exp_avg.dtype is not torch.bfloat16 or exp_avg_sq.dtype is not torch.bfloat16:
+        raise TypeError("adamw: optimizer states are bfloat16")
+    # scalars exactly as the reference forms them: fp32 tensors on the host (bf16_sr.py:91-92,102)
+    step32 = step.detach().to("cpu", torch.float32)
+    bc1 = 1 - beta1**step32
+    bc2 = 1 - beta2**step32
+    sqrt_bc2 = bc2.sqrt()
+    lr32 = lr.detach().to("cpu", torch.float32)
+    seed, offset = key if key is not None else (next_philox_key(dev) if bf16_sr else (0, 0))
+    with torch.cuda.device(dev):
+        nv.check(nv.load().qt_adamw_bf16_sr(
+            p.data_ptr(), nv.code(p.dtype), grad.data_ptr(), nv.code(grad.dtype), exp_avg.data_ptr(), exp_avg_sq.data_ptr(),
+            p.numel(), float(lr32), float(beta1), float(beta2), float(weight_decay), float(eps), float(bc1),
+            float(sqrt_bc2), int(bool(bf16_sr)), seed, offset, nv.stream_ptr(dev)))

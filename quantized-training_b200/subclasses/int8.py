@@ -1,0 +1,207 @@
+"""INT8 absmax quantization and the INT8 weight-only training subclass.
+
+Public surface mirrors the reference (subclasses/int8.py): `quantize_int8`, `Int8QTConfig`,
+`Int8LinearWeight`, `convert_int8_quantized_training`. The quantize step runs on the sm_100a
+kernels (one HBM pass, in-kernel Philox for stochastic rounding); there is no CPU path.
+"""
+from __future__ import annotations
+
+from typing import Literal, NamedTuple
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor, nn
+
+import gn_kernels
+from gn_kernels import scaled_mm
+
+aten = torch.ops.aten
+
+
+def _rows_quantize(t2d: Tensor, stochastic_rounding: bool, eps: float, key=None, col_absmax: Tensor | None = None):
+    """Quantize each ROW of a 2-D tensor; returns contiguous int8 of t2d's shape and scale [rows,1].
+
+    A transposed view (unit stride along dim 0) is served by the transposing column-wise kernel
+    on its base, so `quantize_int8(B.T, dim=1)` never materialises `B.T` in bf16."""
+    if t2d.shape[0] > 1 and t2d.shape[1] > 1 and t2d.stride(0) == 1 and t2d.stride(1) >= t2d.shape[0]:
+        return gn_kernels.quantize_colwise_t(t2d.T, torch.int8, stochastic_rounding, eps=eps, key=key,
+                                             col_absmax_=col_absmax)
+    return gn_kernels.quantize_rowwise(t2d, torch.int8, stochastic_rounding, eps=eps, key=key)
+
+
+@torch.no_grad()
+def quantize_int8(tensor: Tensor, stochastic_rounding: bool = False, *, dim: int = -1, eps: float = 1e-12):
+    """Symmetric absmax INT8 quantization along `dim` (reference: subclasses/int8.py:12-26).
+
+    scale = amax(|x|, dim) / 127 in fp32; x / clip(scale, eps); round-half-even, or floor(x + u)
+    with u ~ U[0,1) when `stochastic_rounding`; clip to [-128, 127]. Returns (int8 tensor shaped
+    like `tensor`, scale with `dim` kept as size 1, in `tensor.dtype`).
+    """
+    if not tensor.is_cuda:
+        raise RuntimeError("quantize_int8 runs on the CUDA kernels only; move the tensor to a B200 first")
+    if tensor.dtype not in (torch.bfloat16, torch.float32):
+        # fp16 and others: quantize from the exact fp32 values, report the scale in the input dtype
+        q, s = quantize_int8(tensor.float(), stochastic_rounding, dim=dim, eps=eps)
+        return q, s.to(tensor.dtype)
+    nd = tensor.ndim
+    if nd == 0:
+        raise ValueError("quantize_int8 needs at least one dimension")
+    dim = dim % nd
+    if nd == 1:
+        q, s = _rows_quantize(tensor.view(1, -1), stochastic_rounding, eps)
+        return q.view(-1), s.view(1)
+    if nd > 2:
+        if dim != nd - 1:
+            raise NotImplementedError("quantize_int8 on >2-D tensors supports the last dim only")
+        flat = tensor.reshape(-1, tensor.shape[-1])
+        q, s = _rows_quantize(flat, stochastic_rounding, eps)
+        return q.view(tensor.shape), s.view(*tensor.shape[:-1], 1)
+    if dim == 1:
+        return _rows_quantize(tensor, stochastic_rounding, eps)
+    # dim == 0: per-column scales; quantize the rows of the transpose and view the result back
+    qt, st = _rows_quantize(tensor.T, stochastic_rounding, eps)
+    return qt.T, st.T
+
+
+class Int8QTConfig(NamedTuple):
+    activation: Literal["none", "int8", "int8_sr"] = "none"
+
+
+class Int8LinearWeight(Tensor):
+    """Weight held as int8 rows + one scale per output row (reference: subclasses/int8.py:33-135).
+
+    Behaves as a tensor of the scale's dtype; `F.linear` on it runs `_Int8Linear`; optimizer
+    updates (`add_`, `addcdiv_`, `copy_`) de-quantize, apply, and re-quantize with stochastic rounding.
+    """
+
+    @staticmethod
+    @torch._dynamo.disable
+    def __new__(cls, int_data: Tensor, scale: Tensor, config: Int8QTConfig):
+        return Tensor._make_wrapper_subclass(cls, int_data.shape, dtype=scale.dtype, device=int_data.device)
+
+    @torch._dynamo.disable
+    def __init__(self, int_data: Tensor, scale: Tensor, config: Int8QTConfig):
+        assert int_data.dtype is torch.int8
+        assert int_data.ndim == 2
+        assert scale.ndim == 2
+        self.int_data = int_data
+        self.scale = scale
+        self.config = config
+
+    def __tensor_flatten__(self):
+        return ["int_data", "scale"], [self.config]
+
+    @classmethod
+    def __tensor_unflatten__(cls, tensor_data_dict, tensor_attributes, outer_size=None, outer_stride=None):
+        return cls(tensor_data_dict["int_data"], tensor_data_dict["scale"], *tensor_attributes)
+
+    @classmethod
+    def from_float(cls, tensor: Tensor, *, config: Int8QTConfig = Int8QTConfig()):
+        int_data, scale = quantize_int8(tensor.detach())
+        out = cls(int_data, scale, config)
+        out.requires_grad_(tensor.requires_grad)
+        return out
+
+    def dequantize(self):
+        return self.int_data * self.scale.view(-1, 1)
+
+    def __repr__(self):
+        return (
+            f"{self.__class__.__name__}(shape={tuple(self.shape)}, config={self.config}, "
+            f"dtype={self.dtype}, device={self.device}, requires_grad={self.requires_grad})"
+        )
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or dict()
+        if func is F.linear:
+            return _Int8Linear.apply(*args, **kwargs)
+        with torch._C.DisableTorchFunctionSubclass():
+            return func(*args, **kwargs)
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args, kwargs):
+        kwargs = kwargs or {}
+        if func in (aten.detach.default, aten.clone.default):
+            w = args[0]
+            return cls(func(w.int_data, *args[1:], **kwargs), func(w.scale, *args[1:], **kwargs), w.config)
+
+        if func is aten._to_copy.default:
+            w = args[0]
+            device, dtype = kwargs.get("device", None), kwargs.get("dtype", None)
+            return cls(w.int_data.to(device=device), w.scale.to(device=device, dtype=dtype), w.config)
+
+        # optimizers build their state with zeros_like: hand them a plain tensor
+        if func is aten.zeros_like.default:
+            w = args[0]
+            return torch.zeros(w.shape, dtype=kwargs.get("dtype", w.dtype), device=kwargs.get("device", w.device))
+
+        if func in (aten.sub.Tensor, aten.mul.Tensor):
+            plain = [a.dequantize() if isinstance(a, cls) else a for a in args]
+            return func(*plain, **kwargs)
+
+        if func is aten.copy_.default:
+            dst, src = args[0], args[1]
+            if isinstance(dst, cls) and isinstance(src, cls):
+                dst.int_data.copy_(src.int_data)
+                dst.scale.copy_(src.scale)
+            elif isinstance(dst, cls):
+                # weight update lands here: re-quantize with stochastic rounding (int8.py:119-122)
+                int_data, scale = quantize_int8(src, stochastic_rounding=True)
+                dst.int_data.copy_(int_data)
+                dst.scale.copy_(scale)
+            else:
+                dst.copy_(src.dequantize())
+            return dst
+
+        # in-place optimizer arithmetic: de-quantize, apply, write back through copy_
+        if func in (aten.addcdiv_.default, aten.add_.Tensor):
+            dst = args[0]
+            return dst.copy_(func(dst.dequantize(), *args[1:], **kwargs))
+
+        raise NotImplementedError(f"{cls.__name__} dispatch: attempting to run {func}, this is not supported")
+
+
+class _Int8Linear(torch.autograd.Function):
+    """F.linear for Int8LinearWeight (reference: subclasses/int8.py:138-180)."""
+
+    @staticmethod
+    def forward(ctx, input: Tensor, weight: Int8LinearWeight, bias: Tensor | None = None):
+        ctx.save_for_backward(input, weight)
+        ctx.bias = bias is not None
+
+        if weight.config.activation == "none":
+            # weight-only: bf16 GEMM on the up-cast int8 weight, then the per-output-row scale
+            out = (input @ weight.int_data.T.to(input.dtype)) * weight.scale.T
+        else:
+            # dynamic activation quantization + INT8 tensor cores
+            batch_dims = input.shape[:-1]
+            x2d = input.reshape(-1, weight.shape[1])
+            x_i8, x_scale = quantize_int8(x2d, weight.config.activation == "int8_sr")
+            out = scaled_mm(x_i8, weight.int_data.T, x_scale, weight.scale.T.contiguous())
+            out = out.view(*batch_dims, -1)
+
+        return out + bias if bias is not None else out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, weight = ctx.saved_tensors
+        grad_input = (grad_output * weight.scale.T) @ weight.int_data.to(grad_output.dtype)
+        grad_output = grad_output.reshape(-1, weight.shape[0])
+        input = input.reshape(-1, weight.shape[1])
+        grad_weight = grad_output.T @ input
+        grad_bias = grad_output.sum(0) if ctx.bias else None
+        return grad_input, grad_weight, grad_bias
+
+
+def convert_int8_quantized_training(module: nn.Module, *, config: Int8QTConfig = Int8QTConfig()):
+    """Swap every nn.Linear weight under `module` for an Int8LinearWeight (int8.py:183-192)."""
+    if isinstance(module, nn.Linear):
+        module.weight = nn.Parameter(
+            Int8LinearWeight.from_float(module.weight, config=config),
+            requires_grad=module.weight.requires_grad,
+        )
+    else:
+        for m in module.children():
+            convert_int8_quantized_training(m, config=config)
+    return module

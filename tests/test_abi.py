@@ -1,0 +1,78 @@
+"""CPU checks of the boundary: the shared library loads and exports every symbol that
+include/qt_b200.h declares, with a ctypes signature on the Python side; argument errors are
+reported through return codes without touching a GPU."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = ROOT / "include" / "qt_b200.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(qt_[a-z0-9_]+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__ as entry
+
+    entry.build()
+    from gn_kernels import _native
+
+    return _native.load()
+
+
+def test_header_declares_the_path():
+    names = declared_symbols()
+    for must in ("qt_quantize_rowwise", "qt_quantize_colwise_t", "qt_int8_mm", "qt_scaled_mm", "qt_tile_scaled_mm",
+                 "qt_last_error"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol(lib):
+    from gn_kernels import _native
+
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared in qt_b200.h but not exported"
+        assert name in _native.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(_native.SIGNATURES) <= set(declared_symbols())
+
+
+def test_version_and_error_strings(lib):
+    assert b"sm_100a" in lib.qt_version()
+    assert isinstance(lib.qt_last_error(), bytes)
+
+
+def test_argument_errors_do_not_need_a_gpu(lib):
+    # bad dtype code
+    rc = lib.qt_quantize_rowwise(None, 99, 4, 4, 4, None, 2, None, 0, 1e-12, 0, 0, 0, None)
+    assert rc == 1 and b"x_dtype" in lib.qt_last_error()
+    # stride smaller than cols
+    rc = lib.qt_quantize_rowwise(None, 0, 4, 8, 4, None, 2, None, 0, 1e-12, 0, 0, 0, None)
+    assert rc == 1 and b"stride" in lib.qt_last_error()
+    # GEMM: mixed operand families
+    rc = lib.qt_scaled_mm(None, 2, 16, 1, None, 3, 1, 16, None, None, 0, 0, None, 16, 16, 16, 16, None)
+    assert rc == 1
+    # GEMM: misaligned pitch
+    buf = ctypes.create_string_buffer(4096)
+    addr = (ctypes.addressof(buf) + 15) & ~15
+    rc = lib.qt_int8_mm(addr, 20, 1, addr, 1, 20, addr, 24, 24, 24, 20, None)
+    assert rc == 1 and b"multiples of 16" in lib.qt_last_error()
+    # unsupported tile shape
+    rc = lib.qt_quantize_tile(addr, 0, 4, 4, 4, 3, 5, addr, 2, addr, 0, 1e-12, None)
+    assert rc == 3
+
+
+def test_python_ops_refuse_cpu_tensors():
+    import torch
+    import gn_kernels
+
+    a = torch.zeros(16, 16, dtype=torch.int8)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        gn_kernels.int8_mm(a, a)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        gn_kernels.quantize_rowwise(torch.zeros(4, 8, dtype=torch.bfloat16))

@@ -1,0 +1,161 @@
+"""GPU parity of the tcgen05 GEMMs: exact int32 accumulators, bit-exact scaled bf16 outputs for
+int8 (the epilogue is deterministic fp32), reference tolerances for fp8 and tile-scaled variants."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import reference_math as om
+from tests.helpers import bits_of, randn_bf16, values_of
+
+pytestmark = pytest.mark.gpu
+
+import gn_kernels  # noqa: E402
+from gn_kernels import _native as nv  # noqa: E402
+
+LAYOUTS = ["A@B.T", "A@B", "A.T@B", "A.T@B.T"]
+
+
+def to_layout(A, B, name):
+    """A [M,K], B [K,N] re-laid-out like the reference benchmark's --a/b_column_major flags
+    (benchmark_mm.py:33-34,91-96)."""
+    a = A.T.contiguous().T if name.startswith("A.T") else A.contiguous()
+    b = B.T.contiguous().T if name.endswith("B.T") else B.contiguous()
+    return a, b
+
+
+def rand_i8(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(-128, 127, shape, dtype=torch.int8, generator=g).cuda()
+
+
+@pytest.mark.parametrize("mnk", [(128, 256, 128), (128, 256, 640), (256, 512, 256), (1024, 1024, 1024), (300, 520, 272),
+                                 (100, 72, 48), (1, 16, 16), (130, 8, 4096), (2048, 32, 64), (17, 1000, 336)])
+@pytest.mark.parametrize("layout", LAYOUTS)
+def test_int8_mm_exact(mnk, layout):
+    M, N, K = mnk
+    A, B = rand_i8((M, K), 1 + M), rand_i8((K, N), 2 + N)
+    A[0, :] = -128
+    B[:, 0] = -128  # the extreme products
+    a, b = to_layout(A, B, layout)
+    out = gn_kernels.int8_mm(a, b)
+    want = om.int8_mm(A.cpu().numpy(), B.cpu().numpy())
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+    assert nv.device_status() == 0
+
+
+def test_int8_mm_odd_shapes_are_padded_by_the_wrapper():
+    for (M, N, K) in [(33, 45, 50), (7, 9, 13), (64, 64, 100)]:
+        A, B = rand_i8((M, K), 5), rand_i8((K, N), 6)
+        out = gn_kernels.int8_mm(A, B)
+        np.testing.assert_array_equal(out.cpu().numpy(), om.int8_mm(A.cpu().numpy(), B.cpu().numpy()))
+        out = gn_kernels.int8_mm(A[:, ::1], B.T.contiguous().T)
+        np.testing.assert_array_equal(out.cpu().numpy(), om.int8_mm(A.cpu().numpy(), B.cpu().numpy()))
+
+
+def test_int8_mm_matches_reference_fixture(golden_dir):
+    g = np.load(golden_dir / "scaled_mm_ref.npz")
+    A, B = torch.from_numpy(g["A"]).cuda(), torch.from_numpy(g["B"]).cuda()
+    np.testing.assert_array_equal(gn_kernels.int8_mm(A, B).cpu().numpy(), g["int_mm"])
+
+
+def test_degenerate_sizes():
+    A = torch.zeros((0, 64), dtype=torch.int8, device="cuda")
+    B = torch.zeros((64, 32), dtype=torch.int8, device="cuda")
+    assert gn_kernels.int8_mm(A, B).shape == (0, 32)
+    A = torch.zeros((16, 0), dtype=torch.int8, device="cuda")
+    B = torch.zeros((0, 32), dtype=torch.int8, device="cuda")
+    out = gn_kernels.int8_mm(A, B)
+    assert out.shape == (16, 32) and int(out.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("mnk", [(1024, 1024, 1024), (300, 520, 272), (128, 264, 128)])
+def test_scaled_mm_int8_bit_exact(mnk, layout):
+    M, N, K = mnk
+    A, B = rand_i8((M, K), 11), rand_i8((K, N), 12)
+    g = torch.Generator().manual_seed(13)
+    sa = (torch.randn(M, 1, generator=g) / 128).bfloat16().cuda()
+    sb = (torch.randn(1, N, generator=g) / 128).bfloat16().cuda()
+    a, b = to_layout(A, B, layout)
+    out = gn_kernels.scaled_mm(a, b, sa, sb)
+    want = om.scaled_mm(A.cpu().numpy(), B.cpu().numpy(), values_of(sa), values_of(sb))
+    np.testing.assert_array_equal(values_of(out), want)
+    assert out.dtype is torch.bfloat16
+    # fp32 scales -> fp32 output (scale dtype decides, triton_mm.py:386)
+    out32 = gn_kernels.scaled_mm(a, b, sa.float(), sb.float())
+    want32 = om.scaled_mm(A.cpu().numpy(), B.cpu().numpy(), values_of(sa), values_of(sb), out_dtype="f32")
+    np.testing.assert_array_equal(out32.cpu().numpy(), want32)
+
+
+def test_scaled_mm_scalar_and_column_vector_scales():
+    M, N, K = 256, 384, 512
+    A, B = rand_i8((M, K), 21), rand_i8((K, N), 22)
+    sa = (torch.rand(M, 1) / 64).bfloat16().cuda()
+    one = torch.tensor(0.0123).bfloat16().cuda()
+    want = om.scaled_mm(A.cpu().numpy(), B.cpu().numpy(), values_of(sa), values_of(one).reshape(1, 1))
+    np.testing.assert_array_equal(values_of(gn_kernels.scaled_mm(A, B, sa, one.view(1, 1))), want)
+    np.testing.assert_array_equal(values_of(gn_kernels.scaled_mm(A, B, sa, one)), want)           # 0-dim (BitNet call site)
+    sb_col = (torch.rand(N, 1) / 64).bfloat16().cuda()                                           # [N,1] (Int8LinearWeight.scale)
+    want = om.scaled_mm(A.cpu().numpy(), B.cpu().numpy(), values_of(sa), values_of(sb_col).reshape(1, -1))
+    np.testing.assert_array_equal(values_of(gn_kernels.scaled_mm(A, B, sa, sb_col)), want)
+
+
+def test_scaled_mm_reference_fixture_and_tolerances(golden_dir):
+    """Inputs drawn like benchmark_mm.py:78-89; acceptance as benchmark_mm.py:113-118."""
+    g = np.load(golden_dir / "scaled_mm_ref.npz")
+    A, B = torch.from_numpy(g["A"]).cuda(), torch.from_numpy(g["B"]).cuda()
+    sA = torch.from_numpy(g["sA"].view(np.int16).copy()).view(torch.bfloat16).cuda()
+    sB = torch.from_numpy(g["sB"].view(np.int16).copy()).view(torch.bfloat16).cuda()
+    out = gn_kernels.scaled_mm(A, B, sA, sB)
+    np.testing.assert_allclose(values_of(out), om.bf16_bits_to_f32(g["rowcol"]), atol=4e-4, rtol=1e-2)
+
+
+def test_config1_dynamic_quantize_plus_gemm(golden_dir):
+    """BASELINE config 1: A ~ N(0,1), B ~ N(0,0.02), 1024^2, seed 2024, A @ B.T row-wise INT8."""
+    torch.manual_seed(2024)
+    A = torch.randn(1024, 1024).bfloat16()
+    B = (torch.randn(1024, 1024) * 0.02).bfloat16()
+    qa, sa = gn_kernels.quantize_rowwise(A.cuda())
+    qb, sb = gn_kernels.quantize_rowwise(B.cuda())
+    acc = gn_kernels.int8_mm(qa, qb.T)
+    out = gn_kernels.scaled_mm(qa, qb.T, sa, sb.T.contiguous())
+    oqa, osa = om.quantize_rowwise(A.float().numpy())
+    oqb, osb = om.quantize_rowwise(B.float().numpy())
+    np.testing.assert_array_equal(qa.cpu().numpy(), oqa)
+    np.testing.assert_array_equal(qb.cpu().numpy(), oqb)
+    np.testing.assert_array_equal(acc.cpu().numpy(), om.int8_mm(oqa, oqb.T))
+    np.testing.assert_array_equal(values_of(out), om.scaled_mm(oqa, oqb.T, osa, osb.T))
+    assert int(qa.min()) >= -127 and int(qa.max()) <= 127
+
+
+@pytest.mark.parametrize("layout", ["A@B.T", "A@B", "A.T@B"])
+def test_scaled_mm_fp8(layout):
+    M, N, K = 512, 768, 1024
+    g = torch.Generator().manual_seed(31)
+    A8 = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn).cuda()
+    B8 = torch.randn(K, N, generator=g).to(torch.float8_e4m3fn).cuda()
+    sa = (torch.randn(M, 1, generator=g) / 128).bfloat16().cuda()
+    sb = (torch.randn(1, N, generator=g) / 128).bfloat16().cuda()
+    a, b = to_layout(A8, B8, layout)
+    out = gn_kernels.scaled_mm(a, b, sa, sb)
+    want = om.scaled_mm(bits_of(A8), bits_of(B8), values_of(sa), values_of(sb), kind="e4m3")
+    # north-star tolerance for scaled bf16 outputs: 1e-2 relative (fp32 accumulation order differs)
+    np.testing.assert_allclose(values_of(out), want, rtol=1e-2, atol=1e-4)
+
+
+def test_full_size_gemm_properties():
+    """8192^3 (the benchmark size): linearity in the row scale, agreement of the three layouts, and
+    a sampled exact check of the int32 accumulators."""
+    S = 8192
+    A, B = rand_i8((S, S), 41), rand_i8((S, S), 42)
+    sa = torch.full((S, 1), 2.0 ** -7, dtype=torch.bfloat16, device="cuda")
+    sb = torch.full((1, S), 2.0 ** -6, dtype=torch.bfloat16, device="cuda")
+    base = gn_kernels.scaled_mm(A, B.T.contiguous().T, sa, sb)
+    acc = gn_kernels.int8_mm(A, B)
+    assert torch.equal(base, (acc.float() * 2.0 ** -13).bfloat16())           # power-of-two scales are exact
+    assert torch.equal(gn_kernels.scaled_mm(A, B, sa * 2, sb), (acc.float() * 2.0 ** -12).bfloat16())
+    assert torch.equal(gn_kernels.int8_mm(A.T.contiguous().T, B), acc)
+    rows = torch.tensor([0, 1, 4095, 8191], device="cuda")
+    want = om.int8_mm(A[rows].cpu().numpy(), B.cpu().numpy())
+    np.testing.assert_array_equal(acc[rows].cpu().numpy(), want)
+    assert nv.device_status() == 0

@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M = N = K")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-warmup-seconds", type=float, default=1.0, help="keep warming up at least this long (0 under a profiler)")
     return ap.parse_args()
 
 
@@ -74,7 +75,7 @@ class ClockSampler:
         try:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "250",
                  "-i", str(self.gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -230,12 +231,30 @@ def main():
         return float(t.item())
 
     # ---- device-resident timing ---------------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        step(A, W)
-    sync_all()
+    # The clock sampler (nvidia-smi) is started first and given time to attach: its start-up stalls
+    # the GPU for milliseconds. Warm-up then runs for at least 0.3 s so the clocks the timed region
+    # sees are the ones the sampler records under load.
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(1.0)
+    sync_all()
+    warm_steps = 0
+    t_warm = time.perf_counter()
+    chunk = max(args.warmup, 3)
+    while True:
+        for _ in range(chunk):
+            step(A, W)
+        warm_steps += chunk
+        torch.cuda.synchronize()
+        more = 1 if (time.perf_counter() - t_warm) < args.min_warmup_seconds else 0
+        if world > 1:  # every rank must run the same number of steps (the step holds a collective)
+            flag = torch.tensor([more], dtype=torch.int32, device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            more = int(flag.item())
+        if not more:
+            break
+    sync_all()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
@@ -245,6 +264,7 @@ def main():
     ms_total = max_over_ranks(start.elapsed_time(stop))
     ms_per_step = ms_total / args.steps
     gemm_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in gemm_events)
+    gemm_ms_median = statistics.median(e0.elapsed_time(e1) for e0, e1 in gemm_events)
     status = _native.device_status()
     if status != 0:
         raise SystemExit(f"a kernel reported a bounded wait that ran out (status {status:#x})")
@@ -295,7 +315,7 @@ def main():
                         "sample": f"3 full passes of the {S}^3 workload after 1 warm-up ({dt:.2f} s each), torch eager quantize + torch._int_mm on the host"}
 
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm_steps,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
         "config": {
@@ -304,7 +324,7 @@ def main():
             "l2": "inputs larger than L2 (2 x 134 MB bf16 in, 2 x 67 MB int8 operands, 134 MB out per step)",
             "value_is": "2*M*N*K * n_gpus / step time; the step includes both quantize kernels",
         },
-        "gemm_only": {"tops": achieved, "ms": gemm_ms},
+        "gemm_only": {"tops": achieved, "ms": gemm_ms, "ms_median": gemm_ms_median},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
                      "frac": achieved / int8_peak, "traffic": traffic,
                      "peak_is": f"2 x {peak_kind} dense bf16 burst ({bf16_peak} TF/s); nominal dense INT8 is {NOMINAL_INT8_DENSE_TOPS} TOPS",

@@ -1,17 +1,22 @@
 // tcgen05 GEMMs for sm_100a: int8 x int8 -> int32 (kind::i8) and fp8 x fp8 -> fp32 (kind::f8f6f4),
-// with raw, row/column-scaled and tile-scaled epilogues.
+// with raw and row/column-scaled epilogues.
 //
-// One persistent CTA per SM, 6 warps:
+// Persistent kernel, one CTA per SM, 6 warps:
 //   warp 0      TMA producer   global -> 128B-swizzled shared-memory stages (cp.async.bulk.tensor)
 //   warp 1      MMA issuer     one elected lane issues tcgen05.mma; accumulators live in TMEM
 //   warps 2..5  epilogue       tcgen05.ld TMEM -> registers -> scale -> global
-// The accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of tile i overlaps
-// the main loop of tile i+1. Stages and accumulators are handed over through mbarriers; every wait
-// is bounded and reports through the device status word instead of spinning forever.
+// Large problems run as CTA PAIRS (2-CTA clusters, tcgen05 cta_group::2): the pair owns a 256 x 256
+// tile, each CTA stages its 128 rows of A and half of B, the leader CTA issues M=256 MMAs for both
+// and each CTA drains its own 128 accumulator rows. Small problems (M <= 128) use one CTA per
+// 128 x 256 tile. The accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of
+// tile i overlaps the main loop of tile i+1. Stages and accumulators are handed over through
+// mbarriers; every wait is bounded and reports through the device status word instead of spinning
+// forever.
 //
 // Operand layouts: both operands may be K-major or MN-major in global memory; MN-major tiles are
 // fetched as [K][128 B of M or N] boxes and described to the tensor core as MN-major, so A@B.T,
-// A@B and A.T@B run without any transpose pass. No TMA multicast is used anywhere.
+// A@B and A.T@B run without any transpose pass. No TMA multicast is used anywhere: every CTA
+// fetches its own tiles (the pair form only redirects the completion bytes to the leader's barrier).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -22,27 +27,43 @@ namespace {
 
 // ---- tile configuration ---------------------------------------------------------------------
 
-constexpr int BM = 128;      // tile rows  (= UMMA M, one TMEM lane per row)
-constexpr int BN = 256;      // tile cols  (= UMMA N, one TMEM column per col)
+constexpr int BM = 128;      // tile rows per CTA (one TMEM lane per row)
+constexpr int BN = 256;      // tile cols (= UMMA N, one TMEM column per col)
 constexpr int BK = 128;      // reduction elements per stage (8-bit => 128 bytes = one swizzle row)
 constexpr int UMMA_K = 32;   // reduction elements per tcgen05.mma for 8-bit operands
-constexpr int STAGES = 4;
-constexpr int A_STAGE_BYTES = BM * BK;                 // 16 KB
-constexpr int B_STAGE_BYTES = BN * BK;                 // 32 KB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int NUM_EPI_THREADS = 128;
 constexpr int TMEM_COLS = 512;                         // 2 accumulators x BN fp32/int32 columns
 constexpr int GROUP_M = 8;                             // rasterisation: 8 row-tiles share B panels in L2
+constexpr int MAX_STAGES = 6;
 
-// shared memory carve-up (offsets from a 1024-byte aligned base)
-constexpr int SMEM_STAGES_OFF = 0;
-constexpr int SMEM_COLSCALE_OFF = STAGES * STAGE_BYTES;             // float [4 epilogue warps][BN]
-constexpr int SMEM_BAR_OFF = SMEM_COLSCALE_OFF + 4 * BN * 4;        // mbarriers
-constexpr int NUM_BARRIERS = 2 * STAGES + 4;
-constexpr int SMEM_TMEMPTR_OFF = SMEM_BAR_OFF + NUM_BARRIERS * 8;
-constexpr int SMEM_ABORT_OFF = SMEM_TMEMPTR_OFF + 4;
-constexpr int SMEM_TOTAL = SMEM_ABORT_OFF + 4 + 1024;               // + alignment slack
+// CG = CTAs per MMA (tcgen05 cta_group). CG == 1: one CTA owns a 128 x 256 tile and stages all of
+// B (4 stages of 48 KB). CG == 2: a pair of CTAs (a 2-CTA cluster) owns a 256 x 256 tile; each CTA
+// stages its 128 rows of A and HALF of B (128 of the 256 columns), the leader issues one M=256
+// MMA for both, and each CTA ends up with its own 128 rows of the accumulator in its own TMEM. Per
+// CTA that is a third less shared-memory and L2->SM traffic for the same math (6 stages of 32 KB).
+template <int CG>
+struct Cfg {
+    // KA = 128-byte K atoms per pipeline stage. The CTA pair stages 256 reduction bytes per
+    // hand-over (8 MMAs per barrier round trip instead of 4): the single MMA-issuing thread spends
+    // a fixed ~250 cycles per hand-over on the barrier wait and tcgen05.commit, which the tensor
+    // pipe only hides when enough MMAs are queued behind it.
+    static constexpr int KA = CG == 2 ? 2 : 1;
+    static constexpr int BKS = BK * KA;                // reduction bytes per stage
+    static constexpr int STAGES = CG == 2 ? 3 : 4;
+    static constexpr int A_ATOM_BYTES = BM * BK;       // one [128 rows][128 B] (or [128 k][128 B]) atom
+    static constexpr int A_STAGE_BYTES = A_ATOM_BYTES * KA;
+    static constexpr int B_ROWS = BN / CG;             // columns of the tile staged by this CTA
+    static constexpr int B_ATOM_BYTES = B_ROWS * BK;
+    static constexpr int B_STAGE_BYTES = B_ATOM_BYTES * KA;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int SMEM_COLSCALE_OFF = STAGES * STAGE_BYTES;      // float [4 epilogue warps][BN]
+    static constexpr int SMEM_BAR_OFF = SMEM_COLSCALE_OFF + 4 * BN * 4; // mbarriers
+    static constexpr int NUM_BARRIERS = 2 * MAX_STAGES + 4;
+    static constexpr int SMEM_TMEMPTR_OFF = SMEM_BAR_OFF + NUM_BARRIERS * 8;
+    static constexpr int SMEM_ABORT_OFF = SMEM_TMEMPTR_OFF + 4;
+    static constexpr int SMEM_TOTAL = SMEM_ABORT_OFF + 4 + 1024;        // + alignment slack
+};
 
 constexpr uint32_t WAIT_LIMIT = 1u << 26;  // polls before a wait gives up (seconds, not minutes)
 
@@ -129,6 +150,58 @@ __device__ __forceinline__ void tcgen05_mma(uint32_t d_tmem, uint64_t a_desc, ui
     }
 }
 
+// ---- cluster / 2-CTA forms -------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared::cta offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on an mbarrier that may live in the peer CTA (shared::cluster address)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA load whose completion bytes are credited to an mbarrier of the CTA pair's leader.
+// No multicast: each CTA fetches its own tile into its own shared memory.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+        : "memory");
+}
+// commit of the pair's MMAs: one arrival on the barrier at this offset in both CTAs
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask) : "memory");
+}
+
+template <int KIND>
+__device__ __forceinline__ void tcgen05_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (KIND == 0) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base lane + t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -198,31 +271,38 @@ __device__ __forceinline__ float load_scale(const void* p, int dtype, int64_t i)
 // ---- the kernel -----------------------------------------------------------------------------
 
 // KIND: 0 int8 (s32 accumulate), 1 fp8 (f32 accumulate). A_MN / B_MN: operand is MN-major in
-// global memory. The fp8 element formats (e4m3 / e5m2 per operand) arrive in `idesc`.
-template <int KIND, int EPI, bool A_MN, bool B_MN>
+// global memory. CG: CTAs per MMA (see Cfg). The fp8 element formats arrive in `idesc`.
+template <int KIND, int EPI, bool A_MN, bool B_MN, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p,
             const uint32_t idesc) {
+    using C = Cfg<CG>;
+    constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
-    float* s_colscale = reinterpret_cast<float*>(smem + SMEM_COLSCALE_OFF);
-    volatile uint32_t* s_tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + SMEM_TMEMPTR_OFF);
-    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + SMEM_ABORT_OFF);
+    float* s_colscale = reinterpret_cast<float*>(smem + C::SMEM_COLSCALE_OFF);
+    volatile uint32_t* s_tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + C::SMEM_TMEMPTR_OFF);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + C::SMEM_ABORT_OFF);
 
-    const uint32_t bar_base = smem_base + SMEM_BAR_OFF;
+    const uint32_t bar_base = smem_base + C::SMEM_BAR_OFF;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-    auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
-    auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+    auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + b); };
+    auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + 2 + b); };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;  // 0 = leader of the pair
+    const bool leader = cta_rank == 0;
 
-    const int tiles_m = (int)((p.M + BM - 1) / BM);
+    // tiles are BM*CG rows x BN columns, one per CTA (CG == 1) or per CTA pair (CG == 2)
+    const int tiles_m = (int)((p.M + BM * CG - 1) / (BM * CG));
     const int tiles_n = (int)((p.N + BN - 1) / BN);
     const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
-    const int num_kb = (int)((p.K + BK - 1) / BK);
+    const int num_kb = (int)((p.K + C::BKS - 1) / C::BKS);
+    const int64_t first_tile = blockIdx.x / CG;
+    const int64_t tile_step = gridDim.x / CG;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -231,92 +311,123 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar(b), 1);
-            mbar_init(tmem_empty_bar(b), NUM_EPI_THREADS);
+            mbar_init(tmem_empty_bar(b), NUM_EPI_THREADS * CG);
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_base + SMEM_TMEMPTR_OFF), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (CG == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_base + C::SMEM_TMEMPTR_OFF), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_base + C::SMEM_TMEMPTR_OFF), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem_ptr;
 
     if (warp == 0) {
-        // ===== TMA producer =====
+        // ===== TMA producer (every CTA fills its own stages) =====
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
             const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-            const int m0 = tc.m * BM, n0 = tc.n * BN;
+            const int m0 = tc.m * (BM * CG) + (int)cta_rank * BM;
+            const int n0 = tc.n * BN + (int)cta_rank * C::B_ROWS;
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = mbar_wait(empty_bar(stage), phase ^ 1u, s_abort, p.status, 0x100 | stage);
                 if (!ok) break;
                 if (lane == 0) {
-                    const uint32_t a_dst = smem_base + SMEM_STAGES_OFF + stage * STAGE_BYTES;
-                    const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-                    const int k0 = kb * BK;
-                    mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-                    if constexpr (A_MN) tma_load_2d(a_dst, &tmap_a, full_bar(stage), m0, k0);
-                    else tma_load_2d(a_dst, &tmap_a, full_bar(stage), k0, m0);
-                    if constexpr (B_MN) {
-                        tma_load_2d(b_dst, &tmap_b, full_bar(stage), n0, k0);
-                        tma_load_2d(b_dst + BK * 128, &tmap_b, full_bar(stage), n0 + 128, k0);
+                    const uint32_t a_dst = smem_base + stage * C::STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + C::A_STAGE_BYTES;
+                    const int k0 = kb * C::BKS;
+                    if constexpr (CG == 2) {
+                        // both CTAs' bytes are credited to the leader's barrier
+                        const uint32_t bar = map_to_cta(full_bar(stage), 0);
+                        if (leader) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
+#pragma unroll
+                        for (int a = 0; a < C::KA; ++a) {
+                            const int ka = k0 + a * BK;
+                            if constexpr (A_MN) tma_load_2d_pair(a_dst + a * C::A_ATOM_BYTES, &tmap_a, bar, m0, ka);
+                            else tma_load_2d_pair(a_dst + a * C::A_ATOM_BYTES, &tmap_a, bar, ka, m0);
+                            if constexpr (B_MN) tma_load_2d_pair(b_dst + a * C::B_ATOM_BYTES, &tmap_b, bar, n0, ka);
+                            else tma_load_2d_pair(b_dst + a * C::B_ATOM_BYTES, &tmap_b, bar, ka, n0);
+                        }
                     } else {
-                        tma_load_2d(b_dst, &tmap_b, full_bar(stage), k0, n0);
+                        mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
+                        if constexpr (A_MN) tma_load_2d(a_dst, &tmap_a, full_bar(stage), m0, k0);
+                        else tma_load_2d(a_dst, &tmap_a, full_bar(stage), k0, m0);
+                        if constexpr (B_MN) {
+                            tma_load_2d(b_dst, &tmap_b, full_bar(stage), n0, k0);
+                            tma_load_2d(b_dst + BK * 128, &tmap_b, full_bar(stage), n0 + 128, k0);
+                        } else {
+                            tma_load_2d(b_dst, &tmap_b, full_bar(stage), k0, n0);
+                        }
                     }
                 }
                 __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
-        // Drain: wait until the MMA warp has released every stage this warp filled, so no TMA
-        // write is still in flight when the CTA exits.
+        // Drain: wait until every stage this warp filled has been released, so no TMA write is
+        // still in flight when the CTA exits.
         for (int s = 0; s < STAGES && ok; ++s) {
             ok = mbar_wait(empty_bar(stage), phase ^ 1u, s_abort, p.status, 0x180 | stage);
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer =====
-        int stage = 0;
-        uint32_t phase = 0;
-        int acc = 0;
-        uint32_t acc_phase = 0;
-        bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, s_abort, p.status, 0x200 | acc);
-            if (!ok) break;
-            tcgen05_fence_after();
-            const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-            for (int kb = 0; kb < num_kb; ++kb) {
-                ok = mbar_wait(full_bar(stage), phase, s_abort, p.status, 0x300 | stage);
+        // ===== MMA issuer (the leader CTA only when CG == 2) =====
+        if (leader) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+                ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, s_abort, p.status, 0x200 | acc);
                 if (!ok) break;
                 tcgen05_fence_after();
-                if (lane == 0) {
-                    const uint32_t a_addr = smem_base + SMEM_STAGES_OFF + stage * STAGE_BYTES;
-                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(full_bar(stage), phase, s_abort, p.status, 0x300 | stage);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    if (lane == 0) {
+                        const uint32_t a_addr = smem_base + stage * C::STAGE_BYTES;
+                        const uint32_t b_addr = a_addr + C::A_STAGE_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // K-major: step 32 bytes inside the 128-byte swizzle row.
-                        // MN-major: step 32 k-rows of 128 bytes.
-                        const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + k * UMMA_K * 128, BK * 128, 1024)
-                                                     : make_smem_desc(a_addr + k * UMMA_K, 16, 1024);
-                        const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + k * UMMA_K * 128, BK * 128, 1024)
-                                                     : make_smem_desc(b_addr + k * UMMA_K, 16, 1024);
-                        tcgen05_mma<KIND>(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < C::BKS / UMMA_K; ++k) {
+                            // K-major: atom (k / 4) of the stage, then 32 bytes inside the 128-byte
+                            // swizzle row. MN-major: the stage is contiguous k-rows of 128 bytes.
+                            constexpr int KPA = BK / UMMA_K;
+                            const uint32_t a_off = A_MN ? k * UMMA_K * 128 : (k / KPA) * C::A_ATOM_BYTES + (k % KPA) * UMMA_K;
+                            const uint32_t b_off = B_MN ? k * UMMA_K * 128 : (k / KPA) * C::B_ATOM_BYTES + (k % KPA) * UMMA_K;
+                            const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + a_off, C::BKS * 128, 1024) : make_smem_desc(a_addr + a_off, 16, 1024);
+                            const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + b_off, C::BKS * 128, 1024) : make_smem_desc(b_addr + b_off, 16, 1024);
+                            if constexpr (CG == 2) tcgen05_mma_pair<KIND>(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+                            else tcgen05_mma<KIND>(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                        // stage reusable (in both CTAs) once these MMAs retire
+                        if constexpr (CG == 2) {
+                            tcgen05_commit_pair(empty_bar(stage));
+                            if (kb == num_kb - 1) tcgen05_commit_pair(tmem_full_bar(acc));
+                        } else {
+                            tcgen05_commit(empty_bar(stage));
+                            if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar(acc));
+                        }
                     }
-                    tcgen05_commit(empty_bar(stage));  // stage reusable once these MMAs retire
-                    if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar(acc));
+                    __syncwarp();
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                __syncwarp();
-                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
             }
-            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
     } else {
         // ===== epilogue =====
@@ -324,9 +435,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const uint32_t leader_empty0 = CG == 2 ? map_to_cta(tmem_empty_bar(0), 0) : 0u;
+        const uint32_t leader_empty1 = CG == 2 ? map_to_cta(tmem_empty_bar(1), 0) : 0u;
+        for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
             const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-            const int64_t m0 = (int64_t)tc.m * BM, n0 = (int64_t)tc.n * BN;
+            const int64_t m0 = (int64_t)tc.m * (BM * CG) + (int64_t)cta_rank * BM, n0 = (int64_t)tc.n * BN;
             const int64_t row = m0 + ew * 32 + lane;
 
             float row_scale = 0.0f;
@@ -397,16 +510,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
             tcgen05_fence_before();
             __syncwarp();
-            mbar_arrive(tmem_empty_bar(acc));
+            // the accumulator belongs to the pair: both CTAs report to the leader's barrier
+            if constexpr (CG == 2) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+            else mbar_arrive(tmem_empty_bar(acc));
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
     }
 
     tcgen05_fence_before();
     __syncthreads();
+    // nobody leaves while the peer may still signal this CTA's barriers or read its shared memory
+    if constexpr (CG == 2) cluster_sync_all();
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if constexpr (CG == 2)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -447,28 +567,59 @@ int make_tmap(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer
     return QT_OK;
 }
 
-template <int KIND, int EPI>
-int launch_layout(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, uint32_t idesc,
-                  int grid, cudaStream_t stream) {
-#define QT_LAUNCH(AMN, BMN)                                                                                        \
-    do {                                                                                                           \
-        auto kfn = gemm_kernel<KIND, EPI, AMN, BMN>;                                                               \
-        static bool attr_set[64] = {false};                                                                        \
-        int dev = 0;                                                                                               \
-        QT_CUDA_CHECK(cudaGetDevice(&dev));                                                                        \
-        if (dev < 0 || dev >= 64 || !attr_set[dev]) {                                                              \
-            QT_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));     \
-            if (dev >= 0 && dev < 64) attr_set[dev] = true;                                                        \
-        }                                                                                                          \
-        kfn<<<grid, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, p, idesc);                                          \
-    } while (0)
-    if (!a_mn && !b_mn) QT_LAUNCH(false, false);
-    else if (!a_mn && b_mn) QT_LAUNCH(false, true);
-    else if (a_mn && b_mn) QT_LAUNCH(true, true);
-    else QT_LAUNCH(true, false);
-#undef QT_LAUNCH
-    QT_CUDA_CHECK(cudaGetLastError());
+// 0 = choose per problem, 1 / 2 = force that many CTAs per MMA (set through qt_set_gemm_cta_group)
+int g_forced_cta_group = 0;
+
+template <int KIND, int EPI, bool A_MN, bool B_MN, int CG>
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, uint32_t idesc, int64_t tiles,
+               cudaStream_t stream) {
+    auto kfn = gemm_kernel<KIND, EPI, A_MN, B_MN, CG>;
+    constexpr int SMEM = Cfg<CG>::SMEM_TOTAL;
+    static bool attr_set[64] = {false};
+    static int max_clusters[64] = {0};
+    int dev = 0;
+    QT_CUDA_CHECK(cudaGetDevice(&dev));
+    const bool cacheable = dev >= 0 && dev < 64;
+    if (!cacheable || !attr_set[dev]) {
+        QT_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        if (cacheable) attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if constexpr (CG == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n_clusters = cacheable ? max_clusters[dev] : 0;
+        if (n_clusters == 0) {
+            cfg.gridDim = dim3((unsigned)(num_sms() / 2 * 2));
+            QT_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n_clusters, kfn, &cfg));
+            if (n_clusters <= 0) return fail(QT_ERR_CUDA, "gemm: no 2-CTA cluster of this kernel fits on the device");
+            if (cacheable) max_clusters[dev] = n_clusters;
+        }
+        const int64_t pairs = tiles < n_clusters ? tiles : n_clusters;
+        cfg.gridDim = dim3((unsigned)(2 * pairs));
+    } else {
+        const int sms = num_sms();
+        cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));
+    }
+    QT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kfn, ta, tb, p, idesc));
     return QT_OK;
+}
+
+template <int KIND, int EPI, int CG>
+int launch_layout(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, uint32_t idesc,
+                  int64_t tiles, cudaStream_t stream) {
+    if (!a_mn && !b_mn) return launch_one<KIND, EPI, false, false, CG>(ta, tb, p, idesc, tiles, stream);
+    if (!a_mn && b_mn) return launch_one<KIND, EPI, false, true, CG>(ta, tb, p, idesc, tiles, stream);
+    if (a_mn && b_mn) return launch_one<KIND, EPI, true, true, CG>(ta, tb, p, idesc, tiles, stream);
+    return launch_one<KIND, EPI, true, false, CG>(ta, tb, p, idesc, tiles, stream);
 }
 
 int fp8_format(int dtype) { return dtype == QT_E4M3 ? 0 : 1; }
@@ -496,25 +647,33 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
     QT_REQUIRE(a_pitch >= (a_mn ? M : K) && b_pitch >= (b_mn ? N : K), "gemm: operand stride smaller than the contiguous extent");
     QT_REQUIRE(p.ldc >= N, "gemm: ldc smaller than N");
 
+    // A CTA pair per 256-row tile pays off once there are at least two row blocks of work per SM pair;
+    // short problems keep the single-CTA form (more, smaller tiles).
+    int cg = g_forced_cta_group;
+    if (cg != 1 && cg != 2) cg = (M > BM) ? 2 : 1;
+    const int b_rows = BN / cg;
+
     CUtensorMap ta, tb;
     if (a_mn) { if (int rc = make_tmap(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)a_pitch, 128, BK)) return rc; }
     else      { if (int rc = make_tmap(&ta, a, (uint64_t)K, (uint64_t)M, (uint64_t)a_pitch, BK, BM)) return rc; }
     if (b_mn) { if (int rc = make_tmap(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)b_pitch, 128, BK)) return rc; }
-    else      { if (int rc = make_tmap(&tb, b, (uint64_t)K, (uint64_t)N, (uint64_t)b_pitch, BK, BN)) return rc; }
+    else      { if (int rc = make_tmap(&tb, b, (uint64_t)K, (uint64_t)N, (uint64_t)b_pitch, BK, (uint32_t)b_rows)) return rc; }
 
     if (int rc = device_status_ptr(&p.status)) return rc;
 
-    const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int sms = num_sms();
-    const int grid = (int)(tiles < sms ? tiles : sms);
-    const uint32_t idesc = is_i8 ? make_idesc(2, 1, 1, a_mn, b_mn, BM, BN)
-                                 : make_idesc(1, fp8_format(a_dtype), fp8_format(b_dtype), a_mn, b_mn, BM, BN);
+    const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + BN - 1) / BN);
+    const uint32_t idesc = is_i8 ? make_idesc(2, 1, 1, a_mn, b_mn, BM * cg, BN)
+                                 : make_idesc(1, fp8_format(a_dtype), fp8_format(b_dtype), a_mn, b_mn, BM * cg, BN);
+#define QT_DISPATCH(KIND, EPI)                                                                     \
+    return cg == 2 ? launch_layout<KIND, EPI, 2>(a_mn, b_mn, ta, tb, p, idesc, tiles, stream)      \
+                   : launch_layout<KIND, EPI, 1>(a_mn, b_mn, ta, tb, p, idesc, tiles, stream)
     if (is_i8) {
-        if (epi == EPI_RAW) return launch_layout<0, EPI_RAW>(a_mn, b_mn, ta, tb, p, idesc, grid, stream);
-        if (epi == EPI_ROWCOL) return launch_layout<0, EPI_ROWCOL>(a_mn, b_mn, ta, tb, p, idesc, grid, stream);
+        if (epi == EPI_RAW) { QT_DISPATCH(0, EPI_RAW); }
+        if (epi == EPI_ROWCOL) { QT_DISPATCH(0, EPI_ROWCOL); }
     } else {
-        if (epi == EPI_ROWCOL) return launch_layout<1, EPI_ROWCOL>(a_mn, b_mn, ta, tb, p, idesc, grid, stream);
+        if (epi == EPI_ROWCOL) { QT_DISPATCH(1, EPI_ROWCOL); }
     }
+#undef QT_DISPATCH
     return fail(QT_ERR_UNSUPPORTED, "gemm: epilogue %d not implemented for this operand type", epi);
 }
 
@@ -523,6 +682,12 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
 }  // namespace qt
 
 using namespace qt;
+
+extern "C" int qt_set_gemm_cta_group(int cta_group) {
+    QT_REQUIRE(cta_group == 0 || cta_group == 1 || cta_group == 2, "set_gemm_cta_group: expected 0 (auto), 1 or 2");
+    g_forced_cta_group = cta_group;
+    return QT_OK;
+}
 
 extern "C" int qt_int8_mm(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, int32_t* c,
                           int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream) {

@@ -181,7 +181,7 @@ def _bitnet_backward(ctx, grad_output, weight_i8):
         grad_input = grad_input.view(*batch_dims, weight_i8.shape[1])
     if ctx.needs_input_grad[1]:
         grad_weight = gy.T @ (input_i8 * row_scale.view(-1, 1))
-    if ctx.needs_input_grad[2]:
+    if len(ctx.needs_input_grad) > 2 and ctx.needs_input_grad[2]:
         grad_bias = gy.sum(0)
     return grad_input, grad_weight, grad_bias
 

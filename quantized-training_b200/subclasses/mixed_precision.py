@@ -198,7 +198,7 @@ class _Int8MixedPrecisionLinear(torch.autograd.Function):
             else:
                 grad_weight = gy.T @ x2d
 
-        if ctx.needs_input_grad[2] and ctx.bias:
+        if len(ctx.needs_input_grad) > 2 and ctx.needs_input_grad[2] and ctx.bias:
             grad_bias = gy.sum(0)
 
         return grad_input, grad_weight, grad_bias
@@ -315,6 +315,6 @@ class _Int8GatheredLinear(torch.autograd.Function):
             else:
                 grad_weight = gy.T @ x2d
 
-        if ctx.needs_input_grad[2] and ctx.bias:
+        if len(ctx.needs_input_grad) > 2 and ctx.needs_input_grad[2] and ctx.bias:
             grad_bias = gy.sum(0)
         return grad_input, grad_weight, grad_bias

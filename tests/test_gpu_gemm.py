@@ -15,6 +15,14 @@ from gn_kernels import _native as nv  # noqa: E402
 LAYOUTS = ["A@B.T", "A@B", "A.T@B", "A.T@B.T"]
 
 
+@pytest.fixture(params=[0, 1, 2], ids=["cg_auto", "cg1", "cg2"])
+def cta_group(request):
+    """Run a test with the GEMM's CTA-pair mode chosen automatically, forced off and forced on."""
+    nv.check(nv.load().qt_set_gemm_cta_group(request.param))
+    yield request.param
+    nv.check(nv.load().qt_set_gemm_cta_group(0))
+
+
 def to_layout(A, B, name):
     """A [M,K], B [K,N] re-laid-out like the reference benchmark's --a/b_column_major flags
     (benchmark_mm.py:33-34,91-96)."""
@@ -31,7 +39,7 @@ def rand_i8(shape, seed):
 @pytest.mark.parametrize("mnk", [(128, 256, 128), (128, 256, 640), (256, 512, 256), (1024, 1024, 1024), (300, 520, 272),
                                  (100, 72, 48), (1, 16, 16), (130, 8, 4096), (2048, 32, 64), (17, 1000, 336)])
 @pytest.mark.parametrize("layout", LAYOUTS)
-def test_int8_mm_exact(mnk, layout):
+def test_int8_mm_exact(mnk, layout, cta_group):
     M, N, K = mnk
     A, B = rand_i8((M, K), 1 + M), rand_i8((K, N), 2 + N)
     A[0, :] = -128
@@ -70,7 +78,7 @@ def test_degenerate_sizes():
 
 @pytest.mark.parametrize("layout", LAYOUTS)
 @pytest.mark.parametrize("mnk", [(1024, 1024, 1024), (300, 520, 272), (128, 264, 128)])
-def test_scaled_mm_int8_bit_exact(mnk, layout):
+def test_scaled_mm_int8_bit_exact(mnk, layout, cta_group):
     M, N, K = mnk
     A, B = rand_i8((M, K), 11), rand_i8((K, N), 12)
     g = torch.Generator().manual_seed(13)
@@ -129,7 +137,7 @@ def test_config1_dynamic_quantize_plus_gemm(golden_dir):
 
 
 @pytest.mark.parametrize("layout", ["A@B.T", "A@B", "A.T@B"])
-def test_scaled_mm_fp8(layout):
+def test_scaled_mm_fp8(layout, cta_group):
     M, N, K = 512, 768, 1024
     g = torch.Generator().manual_seed(31)
     A8 = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn).cuda()

@@ -192,11 +192,11 @@ def test_full_size_properties():
     scale32 = (amax / 127)
     assert torch.equal(s.cpu(), scale32.bfloat16())
     deq_err = (q.float().cpu() * scale32 - x.float().cpu()).abs()
-    assert (deq_err <= 0.5 * scale32 * (1 + 1e-6) + 1e-30).all()
+    assert (deq_err <= 0.5 * scale32 * (1 + 1e-3) + 1e-30).all()
     qt, st = gn_kernels.quantize_colwise_t(x)
     cm = gn_kernels.col_absmax(x)
     assert torch.equal(cm.cpu(), x.float().abs().amax(0).cpu())
     assert torch.equal(st.view(-1).cpu(), (cm.cpu() / 127).bfloat16())
     # idempotence on already-quantized values: quantizing q * scale with the same absmax gives q
     deq_err_t = (qt.float().cpu() * (cm.cpu() / 127).view(-1, 1) - x.float().cpu().T).abs()
-    assert (deq_err_t <= 0.5 * (cm.cpu() / 127).view(-1, 1) * (1 + 1e-6) + 1e-30).all()
+    assert (deq_err_t <= 0.5 * (cm.cpu() / 127).view(-1, 1) * (1 + 1e-3) + 1e-30).all()

@@ -109,6 +109,28 @@ int qt_quantize_colwise_t(const void* x, int x_dtype, int64_t rows, int64_t cols
                           uint64_t offset, void* stream);
 
 /*
+ * qt_col_absmax + qt_quantize_colwise_t in one call that allocates nothing, for hosts that cannot
+ * give this library memory at call time: a serving or training runtime that has already claimed the
+ * whole device for its own pool (a cudaMalloc from a plugin would fail or fragment it), or a caller
+ * inside a region where allocation is forbidden. The per-column absmax that the two-call form keeps
+ * in a caller buffer lives in a fixed 256 KB array inside the library instead, so at most 65536
+ * columns are accepted (more returns QT_ERR_UNSUPPORTED; use the two-call form with your own
+ * buffer). x, qt and scale are still the caller's. No cudaMalloc / cudaFree or allocating library
+ * routine is called.
+ *   - The first call on each device looks up the array's device address (a one-time set-up step):
+ *     make that first call outside any stream capture.
+ *   - Every call on a device shares the one array: calls that may overlap on the GPU (different
+ *     streams) race on it; keep them on one stream or serialise them. The array keeps the previous
+ *     call's maxima between calls; each call clears the columns it uses before reducing into them.
+ * Results are bit-identical to qt_col_absmax followed by qt_quantize_colwise_t.
+ * No counterpart in the reference (its quantize is eager PyTorch and allocates freely).
+ */
+int qt_quantize_colwise_t_noalloc(const void* x, int x_dtype, int64_t rows, int64_t cols,
+                                  int64_t x_row_stride, void* qt, int q_dtype, void* scale,
+                                  int scale_dtype, float eps, int stochastic, uint64_t seed,
+                                  uint64_t offset, void* stream);
+
+/*
  * Tile-wise absmax quantize: one scale per (tile_r x tile_c) tile of x [rows, cols];
  * scale is [ceil(rows/tile_r), ceil(cols/tile_c)] contiguous. tile_r in {1, 128}, tile_c = 128
  * (1x128 activations, 128x128 weights). Round-half-to-even only.

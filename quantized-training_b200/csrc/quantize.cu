@@ -1013,6 +1013,47 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
     return QT_OK;
 }
 
+// ---- allocation-free column-wise quantize ---------------------------------------------------------
+
+// Scratch for qt_quantize_colwise_t_noalloc: the per-column absmax that the two-call form keeps in
+// a caller-allocated buffer. It lives in the library's own image (256 KB on every GPU that loads
+// the library, until the process exits) so the entry point never has to ask anyone for memory.
+constexpr int64_t kNoAllocMaxCols = 65536;
+static __device__ __align__(256) float g_noalloc_col_absmax[kNoAllocMaxCols];
+
+// In host code the array's name is only a handle; the device address has to be looked up, once
+// per device, with that device current.
+static float* g_noalloc_ptr[64] = {nullptr};
+
+static int noalloc_scratch(float** out) {
+    int dev = 0;
+    QT_CUDA_CHECK(cudaGetDevice(&dev));
+    QT_REQUIRE(dev >= 0 && dev < 64, "quantize_colwise_t_noalloc: device index %d out of range", dev);
+    if (!g_noalloc_ptr[dev]) {
+        float* ptr = nullptr;
+        QT_CUDA_CHECK(cudaGetSymbolAddress((void**)&ptr, g_noalloc_col_absmax));
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return QT_OK;
+}
+
+extern "C" int qt_quantize_colwise_t_noalloc(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                                             void* qt_out, int q_dtype, void* scale, int scale_dtype, float eps,
+                                             int stochastic, uint64_t seed, uint64_t offset, void* stream) {
+    if (int rc = check_quant_args(x, x_dtype, rows, cols, x_row_stride, qt_out, q_dtype, scale, scale_dtype)) return rc;
+    if (cols > kNoAllocMaxCols)
+        return fail(QT_ERR_UNSUPPORTED, "quantize_colwise_t_noalloc: %lld columns exceed the built-in scratch of %lld; use "
+                    "qt_col_absmax + qt_quantize_colwise_t with your own buffer", (long long)cols, (long long)kNoAllocMaxCols);
+    if (cols == 0) return QT_OK;
+    float* scratch = nullptr;
+    if (int rc = noalloc_scratch(&scratch)) return rc;
+    // qt_col_absmax clears the columns it is about to use (the array still holds the last call's maxima)
+    if (int rc = qt_col_absmax(x, x_dtype, rows, cols, x_row_stride, scratch, stream)) return rc;
+    return qt_quantize_colwise_t(x, x_dtype, rows, cols, x_row_stride, scratch, qt_out, q_dtype, scale, scale_dtype, eps,
+                                 stochastic, seed, offset, stream);
+}
+
 extern "C" int qt_selftest_division(int q_dtype, float eps, unsigned long long* mismatches_host) {
     QT_REQUIRE(mismatches_host, "selftest_division: null output");
     unsigned long long* d = nullptr;

@@ -39,6 +39,8 @@ SIGNATURES = {
     "qt_col_absmax": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "qt_quantize_colwise_t": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                                       c_int, c_float, c_int, c_uint64, c_uint64, c_void_p]),
+    "qt_quantize_colwise_t_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int,
+                                              c_float, c_int, c_uint64, c_uint64, c_void_p]),
     "qt_quantize_tile": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int, c_void_p,
                                  c_int, c_float, c_void_p]),
     "qt_set_gemm_cta_group": (c_int, [c_int]),

@@ -126,10 +126,13 @@ def philox4x32_10(counter: np.ndarray, offset: int, seed: int) -> np.ndarray:
 
 
 def philox_uniforms(n: int, seed: int, offset: int) -> np.ndarray:
-    """u[i] in [0,1) for linear element index i: word (i % 4) of counter (i // 4), top 24 bits."""
-    n_ctr = (n + 3) // 4
-    words = philox4x32_10(np.arange(n_ctr, dtype=np.uint64), offset, seed).reshape(-1)[:n]
-    return ((words >> np.uint32(8)).astype(np.float32) * np.float32(1.0 / 16777216.0)).astype(np.float32)
+    """The quantize kernels' stochastic-rounding uniforms: element i takes 16 bits of the stream --
+    counter i // 8, word (i % 8) // 2, low half for even i, high half for odd i -- as
+    u = bits * 2^-16 in [0, 1)."""
+    n_ctr = (n + 7) // 8
+    words = philox4x32_10(np.arange(n_ctr, dtype=np.uint64), offset, seed).reshape(-1)
+    halves = np.stack([words & np.uint32(0xFFFF), words >> np.uint32(16)], axis=-1).reshape(-1)[:n]
+    return (halves.astype(np.float32) * np.float32(1.0 / 65536.0)).astype(np.float32)
 
 
 # --------------------------------------------------------------------------------------------

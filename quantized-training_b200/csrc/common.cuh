@@ -62,8 +62,9 @@ inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintp
 
 // ---- Philox4x32-10 --------------------------------------------------------------------------
 // Counter-based generator (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3").
-// Element i of a tensor uses counter (i / 4) and output word (i % 4); the 128-bit counter is
-// {lo32(i/4), hi32(i/4), lo32(offset), hi32(offset)} and the 64-bit key is the seed.
+// The 128-bit counter is {lo32(c), hi32(c), lo32(offset), hi32(offset)} and the 64-bit key is the
+// seed. The quantize kernels give element i 16 bits: counter c = i / 8, word (i % 8) / 2, half i % 2;
+// the optimizer gives element i the low 16 bits of word (i % 4) of counter c = i / 4.
 
 struct Philox4 {
     uint32_t x, y, z, w;
@@ -87,9 +88,6 @@ __host__ __device__ inline Philox4 philox4x32_10(uint64_t ctr, uint64_t offset, 
     }
     return Philox4{c0, c1, c2, c3};
 }
-
-// 24-bit uniform in [0, 1): the same grid torch.rand uses for float32.
-__host__ __device__ inline float u01_from_bits(uint32_t bits) { return (float)(bits >> 8) * (1.0f / 16777216.0f); }
 
 // ---- device numerics ------------------------------------------------------------------------
 

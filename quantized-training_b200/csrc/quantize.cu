@@ -91,15 +91,16 @@ __device__ __forceinline__ void load_vec8(Vec8<XT>& v, const XT* row, int64_t co
 __device__ __forceinline__ float recip_rn(float d) { return __frcp_rn(d); }
 __device__ __forceinline__ float div_rn(float x, float d) { return __fdiv_rn(x, d); }
 
-// Divider by a fixed positive d. EXACT selects div.rn; otherwise the reciprocal sequence.
+// Divider by a fixed positive d. EXACT selects div.rn; otherwise the reciprocal sequence, which
+// needs 1/d to be finite and normal: callers guarantee d >= 1e-30 (eps >= 1e-30 is checked on the
+// host, smaller eps takes the EXACT instantiation).
 template <bool EXACT>
 struct Divider {
     float d, r;
-    bool tiny;  // reciprocal would overflow: use div.rn
-    __device__ __forceinline__ explicit Divider(float d_) : d(d_), r(recip_rn(d_)), tiny(d_ < 1e-30f) {}
-    __device__ __forceinline__ Divider(float d_, float r_) : d(d_), r(r_), tiny(d_ < 1e-30f) {}
+    __device__ __forceinline__ explicit Divider(float d_) : d(d_), r(EXACT ? 0.0f : recip_rn(d_)) {}
+    __device__ __forceinline__ Divider(float d_, float r_) : d(d_), r(r_) {}
     __device__ __forceinline__ float operator()(float x) const {
-        if (EXACT || tiny) {
+        if constexpr (EXACT) {
             return div_rn(x, d);
         } else {
             const float q0 = __fmul_rn(x, r);
@@ -164,29 +165,46 @@ __device__ __forceinline__ uint2 pack8(const float (&v)[8], int q_dtype, bool st
     return out;
 }
 
-// Uniforms for 8 consecutive elements starting at linear index idx.
-__device__ __forceinline__ void uniforms8(float (&u)[8], int64_t idx, uint64_t seed, uint64_t offset) {
-    if ((idx & 3) == 0) {
-        const Philox4 a = philox4x32_10((uint64_t)idx >> 2, offset, seed);
-        const Philox4 b = philox4x32_10(((uint64_t)idx >> 2) + 1, offset, seed);
-        u[0] = u01_from_bits(a.x); u[1] = u01_from_bits(a.y); u[2] = u01_from_bits(a.z); u[3] = u01_from_bits(a.w);
-        u[4] = u01_from_bits(b.x); u[5] = u01_from_bits(b.y); u[6] = u01_from_bits(b.z); u[7] = u01_from_bits(b.w);
-    } else {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint64_t i = (uint64_t)(idx + k);
-            const Philox4 a = philox4x32_10(i >> 2, offset, seed);
-            const uint32_t w = (i & 3) == 0 ? a.x : ((i & 3) == 1 ? a.y : ((i & 3) == 2 ? a.z : a.w));
-            u[k] = u01_from_bits(w);
-        }
-    }
-}
+// Stochastic-rounding uniforms: element i takes 16 bits of the Philox stream -- counter i / 8,
+// word (i % 8) / 2, low half for even i, high half for odd i -- as u = bits * 2^-16 in [0, 1).
+__device__ __forceinline__ float u01_from_half(uint32_t word, int odd) { return (float)((word >> (16 * odd)) & 0xFFFFu) * (1.0f / 65536.0f); }
 
 __device__ __forceinline__ float uniform1(int64_t idx, uint64_t seed, uint64_t offset) {
     const uint64_t i = (uint64_t)idx;
-    const Philox4 a = philox4x32_10(i >> 2, offset, seed);
-    const uint32_t w = (i & 3) == 0 ? a.x : ((i & 3) == 1 ? a.y : ((i & 3) == 2 ? a.z : a.w));
-    return u01_from_bits(w);
+    const Philox4 a = philox4x32_10(i >> 3, offset, seed);
+    const uint32_t sel = (uint32_t)(i >> 1) & 3u;
+    const uint32_t w = sel == 0 ? a.x : (sel == 1 ? a.y : (sel == 2 ? a.z : a.w));
+    return u01_from_half(w, (int)(i & 1));
+}
+
+// Uniforms for 4 consecutive elements starting at idx (one Philox call when they share a counter).
+__device__ __forceinline__ void uniforms4(float (&u)[4], int64_t idx, uint64_t seed, uint64_t offset) {
+    if ((idx & 7) <= 4) {
+        const Philox4 a = philox4x32_10((uint64_t)idx >> 3, offset, seed);
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t e = (uint32_t)(idx & 7) + j;
+            const uint32_t sel = e >> 1;
+            const uint32_t word = sel == 0 ? w[0] : (sel == 1 ? w[1] : (sel == 2 ? w[2] : w[3]));
+            u[j] = u01_from_half(word, (int)(e & 1));
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) u[j] = uniform1(idx + j, seed, offset);
+    }
+}
+
+// Uniforms for 8 consecutive elements starting at linear index idx.
+__device__ __forceinline__ void uniforms8(float (&u)[8], int64_t idx, uint64_t seed, uint64_t offset) {
+    if ((idx & 7) == 0) {
+        const Philox4 a = philox4x32_10((uint64_t)idx >> 3, offset, seed);
+        u[0] = u01_from_half(a.x, 0); u[1] = u01_from_half(a.x, 1); u[2] = u01_from_half(a.y, 0); u[3] = u01_from_half(a.y, 1);
+        u[4] = u01_from_half(a.z, 0); u[5] = u01_from_half(a.z, 1); u[6] = u01_from_half(a.w, 0); u[7] = u01_from_half(a.w, 1);
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) u[k] = uniform1(idx + k, seed, offset);
+    }
 }
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -417,11 +435,20 @@ rowwise_kernel(const RowwiseParams p) {
         const unsigned n_cta = cluster.num_blocks(), rank = cluster.block_rank();
         for (int pair = rank * kThreads + threadIdx.x; pair < PAIRS; pair += n_cta * kThreads) {
             uint32_t m = 0u;
-            for (unsigned c = 0; c < n_cta; ++c) m = max2(m, cluster.map_shared_rank(s_col, c)[pair]);
+            if (n_cta == 8) {
+                // issue the eight remote reads together: each one is a trip across the cluster
+                uint32_t v[8];
+#pragma unroll
+                for (unsigned c = 0; c < 8; ++c) v[c] = cluster.map_shared_rank(s_col, c)[pair];
+#pragma unroll
+                for (unsigned c = 0; c < 8; ++c) m = max2(m, v[c]);
+            } else {
+                for (unsigned c = 0; c < n_cta; ++c) m = max2(m, cluster.map_shared_rank(s_col, c)[pair]);
+            }
             const int64_t c0 = (int64_t)pair * 2;
             // fp32 bit patterns of non-negative values order like unsigned integers
-            if (c0 < p.cols) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c0), m << 16);
-            if (c0 + 1 < p.cols) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c0 + 1), m & 0xFFFF0000u);
+            if (c0 < p.cols && (m & 0xFFFFu)) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c0), m << 16);
+            if (c0 + 1 < p.cols && (m >> 16)) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c0 + 1), m & 0xFFFF0000u);
         }
         cluster.sync();  // nobody leaves while a peer may still read its shared memory
     }
@@ -679,9 +706,8 @@ struct ColwiseParams {
 // transposed tensor) to HBM. x is read once, qt written once.
 constexpr int kTileR = 128, kTileC = 64;
 
-template <typename XT>
+template <typename XT, bool EXACT_DIV>
 __global__ void __launch_bounds__(kThreads, 3) colwise_t_kernel(const ColwiseParams p) {
-    constexpr bool EXACT_DIV = sizeof(XT) != 2;
     __shared__ uint32_t s_tile[kTileC][kTileR / 4 + 1];
     const XT* x = reinterpret_cast<const XT*>(p.x);
     const float qmax = qmax_of(p.q_dtype);
@@ -698,7 +724,7 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_kernel(const ColwisePar
         const float am = (col + k < p.cols) ? p.col_absmax[col + k] : 0.0f;
         const float sc = div_rn(am, qmax);
         dsc[k] = fmaxf(sc, p.eps);
-        rcp[k] = recip_rn(dsc[k]);
+        rcp[k] = EXACT_DIV ? 0.0f : recip_rn(dsc[k]);
         if (blockIdx.y == 0 && rq == 0 && col + k < p.cols) store_scale(p.scale, p.scale_dtype, col + k, sc);
     }
 
@@ -727,16 +753,15 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_kernel(const ColwisePar
                 word = pack4_magic(q[0], q[1], q[2], q[3]);
             } else {
                 word = 0;
+                if (p.q_dtype == QT_I8) {
+                    float u[4];
+                    uniforms4(u, (col + k) * p.rows + r0, p.seed, p.offset);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint32_t b;
-                    if (p.q_dtype == QT_I8) {
-                        const float u = uniform1((col + k) * p.rows + r0 + j, p.seed, p.offset);
-                        b = int8_sr(q[j], u);
-                    } else {
-                        b = quantize_byte(f[j][k] == 0.0f ? f[j][k] : q[j], p.q_dtype, false, 0.0f);
-                    }
-                    word |= b << (8 * j);
+                    for (int j = 0; j < 4; ++j) word |= int8_sr(q[j], u[j]) << (8 * j);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        word |= quantize_byte(f[j][k] == 0.0f ? f[j][k] : q[j], p.q_dtype, false, 0.0f) << (8 * j);
                 }
             }
             s_tile[cg * 8 + k][rq] = word;
@@ -777,9 +802,8 @@ struct TileParams {
 };
 
 // 1 x 128 tiles: 16 lanes per tile, 16 tiles per CTA iteration.
-template <typename XT>
+template <typename XT, bool EXACT_DIV>
 __global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p) {
-    constexpr bool EXACT_DIV = sizeof(XT) != 2;
     const XT* x = reinterpret_cast<const XT*>(p.x);
     const float qmax = qmax_of(p.q_dtype);
     const int64_t tiles_per_row = p.scale_cols;
@@ -814,9 +838,8 @@ __global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p
 }
 
 // 128 x 128 tiles: one CTA per tile; thread (r16, c16) holds 8 vectors (rows r16 + 16 i).
-template <typename XT>
+template <typename XT, bool EXACT_DIV>
 __global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams p) {
-    constexpr bool EXACT_DIV = sizeof(XT) != 2;
     __shared__ float s_red[kThreads / 32];
     const XT* x = reinterpret_cast<const XT*>(p.x);
     const float qmax = qmax_of(p.q_dtype);
@@ -975,8 +998,9 @@ extern "C" int qt_quantize_colwise_t(const void* x, int x_dtype, int64_t rows, i
     if (row_tiles < 1) row_tiles = 1;  // rows == 0 still writes the (zero) scales
     if (row_tiles > 65535) row_tiles = 65535;
     dim3 grid((unsigned)col_tiles, (unsigned)row_tiles);
-    if (x_dtype == QT_BF16) colwise_t_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(p);
-    else colwise_t_kernel<float><<<grid, kThreads, 0, stream>>>(p);
+    if (x_dtype == QT_BF16 && eps >= 1e-30f) colwise_t_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(p);
+    else if (x_dtype == QT_BF16) colwise_t_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(p);
+    else colwise_t_kernel<float, true><<<grid, kThreads, 0, stream>>>(p);
     QT_CUDA_CHECK(cudaGetLastError());
     return QT_OK;
 }
@@ -1000,14 +1024,16 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
         const int64_t want = (n_tiles + 15) / 16;
         const int64_t cap = (int64_t)num_sms() * 16;
         const int grid = (int)(want < cap ? want : cap);
-        if (x_dtype == QT_BF16) tile_1x128_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(p);
-        else tile_1x128_kernel<float><<<grid, kThreads, 0, stream>>>(p);
+        if (x_dtype == QT_BF16 && eps >= 1e-30f) tile_1x128_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(p);
+        else if (x_dtype == QT_BF16) tile_1x128_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(p);
+        else tile_1x128_kernel<float, true><<<grid, kThreads, 0, stream>>>(p);
     } else {
         const int64_t tr = (rows + 127) / 128;
         if (tr > 65535) return fail(QT_ERR_UNSUPPORTED, "quantize_tile: more than 65535 row tiles");
         dim3 grid((unsigned)p.scale_cols, (unsigned)tr);
-        if (x_dtype == QT_BF16) tile_128x128_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(p);
-        else tile_128x128_kernel<float><<<grid, kThreads, 0, stream>>>(p);
+        if (x_dtype == QT_BF16 && eps >= 1e-30f) tile_128x128_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(p);
+        else if (x_dtype == QT_BF16) tile_128x128_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(p);
+        else tile_128x128_kernel<float, true><<<grid, kThreads, 0, stream>>>(p);
     }
     QT_CUDA_CHECK(cudaGetLastError());
     return QT_OK;

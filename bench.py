@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M = N = K")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-clock-sampler", action="store_true", help="do not run nvidia-smi beside the timed region")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0, help="keep warming up at least this long (0 under a profiler)")
     return ap.parse_args()
 
@@ -235,7 +236,7 @@ def main():
     # the GPU for milliseconds. Warm-up then runs for at least 0.3 s so the clocks the timed region
     # sees are the ones the sampler records under load.
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and not args.no_clock_sampler:
         sampler.start()
         time.sleep(1.0)
     sync_all()
@@ -300,13 +301,9 @@ def main():
     hbm_peak, bf16_peak, peak_kind = measured_peaks()
     int8_peak = 2.0 * bf16_peak  # kind::i8 issues at twice the bf16 rate; the driver measures bf16 only
     achieved = flops / (gemm_ms * 1e-3) / 1e12
-    traffic_path = ROOT / "profiles" / "gemm_scaled_int8_traffic.json"
-    traffic = None
-    if traffic_path.exists():
-        try:
-            traffic = json.loads(traffic_path.read_text()).get("dram_bytes_per_launch_8192")
-        except Exception:
-            traffic = None
+    # dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of this kernel, from the ncu
+    # capture summarised in profiles/gemm_scaled_int8_8192.md
+    traffic = 456.2e6 if S == 8192 else None
 
     cpu_baseline = None
     if not args.no_cpu_baseline:
@@ -324,7 +321,7 @@ def main():
             "l2": "inputs larger than L2 (2 x 134 MB bf16 in, 2 x 67 MB int8 operands, 134 MB out per step)",
             "value_is": "2*M*N*K * n_gpus / step time; the step includes both quantize kernels",
         },
-        "gemm_only": {"tops": achieved, "ms": gemm_ms, "ms_median": gemm_ms_median},
+        "gemm_only": {"tops": achieved, "ms": gemm_ms, "ms_median": gemm_ms_median, "ms_max": max(e0.elapsed_time(e1) for e0, e1 in gemm_events)},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
                      "frac": achieved / int8_peak, "traffic": traffic,
                      "peak_is": f"2 x {peak_kind} dense bf16 burst ({bf16_peak} TF/s); nominal dense INT8 is {NOMINAL_INT8_DENSE_TOPS} TOPS",

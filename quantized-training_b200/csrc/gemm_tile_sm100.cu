@@ -1,0 +1,287 @@
+// Tile-scaled GEMM for sm_100a: per block of 128 reduction elements the int8 (or fp8) product is
+// accumulated by tcgen05.mma into a fresh TMEM buffer, then "promoted" on the CUDA cores:
+//     acc[m,n] += fp32(partial[m,n]) * scale_a[m / qm, kb] * scale_b[kb, n / qn]
+// which is the loop of the reference's _tile_scaled_mm_kernel (kernels/gn_kernels/triton_mm.py:314-331).
+//
+// One persistent CTA per SM owns 128 x 128 tiles; 6 warps: TMA producer, MMA issuer, four promotion /
+// epilogue warps that keep the fp32 accumulator (128 values per thread: one row, 128 columns) in
+// registers. TMEM holds four 128-column partial buffers, so the tensor core runs up to four K blocks
+// ahead of the promotion. The promotion (one convert + one fused multiply-add per element per K
+// block) is what bounds this kernel, not the tensor pipe. All waits are bounded.
+#include "tcgen05.cuh"
+
+namespace qt {
+
+namespace {
+
+using namespace tc;
+
+constexpr int TBM = 128, TBN = 128, TBK = 128;
+constexpr int T_UMMA_K = 32;
+constexpr int T_STAGES = 6;
+constexpr int T_A_BYTES = TBM * TBK, T_B_BYTES = TBN * TBK, T_STAGE_BYTES = T_A_BYTES + T_B_BYTES;
+constexpr int T_THREADS = 192;
+constexpr int T_BUFS = 4;                       // TMEM partial buffers of TBN columns
+constexpr int T_TMEM_COLS = T_BUFS * TBN;       // 512
+constexpr int T_SMEM_BAR_OFF = T_STAGES * T_STAGE_BYTES;
+constexpr int T_NUM_BARRIERS = 2 * T_STAGES + 2 * T_BUFS;
+constexpr int T_SMEM_TMEMPTR_OFF = T_SMEM_BAR_OFF + T_NUM_BARRIERS * 8;
+constexpr int T_SMEM_ABORT_OFF = T_SMEM_TMEMPTR_OFF + 4;
+constexpr int T_SMEM_TOTAL = T_SMEM_ABORT_OFF + 4 + 1024;
+
+struct TileGemmParams {
+    int64_t M, N, K;
+    void* c;
+    int64_t ldc;
+    const void* scale_a;
+    const void* scale_b;
+    int64_t sa_s0, sa_s1, sb_s0, sb_s1;
+    int qm, qn;
+    int scale_dtype;
+    int* status;
+};
+
+template <int KIND, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(T_THREADS, 1)
+tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TileGemmParams p,
+                 const uint32_t idesc) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    volatile uint32_t* s_tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + T_SMEM_TMEMPTR_OFF);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + T_SMEM_ABORT_OFF);
+    const uint32_t bar_base = smem_base + T_SMEM_BAR_OFF;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (T_STAGES + s); };
+    auto part_full_bar = [&](int b) { return bar_base + 8u * (2 * T_STAGES + b); };
+    auto part_empty_bar = [&](int b) { return bar_base + 8u * (2 * T_STAGES + T_BUFS + b); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (int)((p.M + TBM - 1) / TBM), tiles_n = (int)((p.N + TBN - 1) / TBN);
+    const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
+    const int num_kb = (int)(p.K / TBK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < T_BUFS; ++b) { mbar_init(part_full_bar(b), 1); mbar_init(part_empty_bar(b), 128); }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_base + T_SMEM_TMEMPTR_OFF), "r"(T_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *s_tmem_ptr;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const TileCoord tc_ = tile_coord(tile, tiles_m, tiles_n);
+            const int m0 = tc_.m * TBM, n0 = tc_.n * TBN;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(empty_bar(stage), phase ^ 1u, s_abort, p.status, 0x500 | stage);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t a_dst = smem_base + stage * T_STAGE_BYTES, b_dst = a_dst + T_A_BYTES;
+                    const int k0 = kb * TBK;
+                    mbar_expect_tx(full_bar(stage), T_STAGE_BYTES);
+                    if constexpr (A_MN) tma_load_2d(a_dst, &tmap_a, full_bar(stage), m0, k0);
+                    else tma_load_2d(a_dst, &tmap_a, full_bar(stage), k0, m0);
+                    if constexpr (B_MN) tma_load_2d(b_dst, &tmap_b, full_bar(stage), n0, k0);
+                    else tma_load_2d(b_dst, &tmap_b, full_bar(stage), k0, n0);
+                }
+                __syncwarp();
+                if (++stage == T_STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+        for (int s = 0; s < T_STAGES && ok; ++s) {
+            ok = mbar_wait(empty_bar(stage), phase ^ 1u, s_abort, p.status, 0x580 | stage);
+            if (++stage == T_STAGES) { stage = 0; phase ^= 1u; }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer: every K block starts a fresh partial (accumulate = 0 on its first MMA) =====
+        int stage = 0, buf = 0;
+        uint32_t phase = 0, buf_phase = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(part_empty_bar(buf), buf_phase ^ 1u, s_abort, p.status, 0x600 | buf);
+                if (!ok) break;
+                ok = mbar_wait(full_bar(stage), phase, s_abort, p.status, 0x700 | stage);
+                if (!ok) break;
+                tcgen05_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_addr = smem_base + stage * T_STAGE_BYTES, b_addr = a_addr + T_A_BYTES;
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(buf * TBN);
+#pragma unroll
+                    for (int k = 0; k < TBK / T_UMMA_K; ++k) {
+                        const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + k * T_UMMA_K * 128, TBK * 128, 1024)
+                                                     : make_smem_desc(a_addr + k * T_UMMA_K, 16, 1024);
+                        const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + k * T_UMMA_K * 128, TBK * 128, 1024)
+                                                     : make_smem_desc(b_addr + k * T_UMMA_K, 16, 1024);
+                        tcgen05_mma<KIND>(d_tmem, a_desc, b_desc, idesc, k != 0 ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty_bar(stage));
+                    tcgen05_commit(part_full_bar(buf));
+                }
+                __syncwarp();
+                if (++stage == T_STAGES) { stage = 0; phase ^= 1u; }
+                if (++buf == T_BUFS) { buf = 0; buf_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ===== promotion + epilogue: thread = one row, 128 fp32 accumulators in registers =====
+        const int ew = warp & 3;
+        int buf = 0;
+        uint32_t buf_phase = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const TileCoord tc_ = tile_coord(tile, tiles_m, tiles_n);
+            const int64_t m0 = (int64_t)tc_.m * TBM, n0 = (int64_t)tc_.n * TBN;
+            const int64_t row = m0 + ew * 32 + lane;
+            const int64_t sa_row = (row < p.M ? row : p.M - 1) / p.qm;
+            const int64_t sb_col = n0 / p.qn;
+            float acc[TBN];
+#pragma unroll
+            for (int j = 0; j < TBN; ++j) acc[j] = 0.0f;
+            // scale of K block 0, then always one block ahead
+            float s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0) * load_scale(p.scale_b, p.scale_dtype, sb_col * p.sb_s1);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const float s = s_next;
+                if (kb + 1 < num_kb)
+                    s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0 + (int64_t)(kb + 1) * p.sa_s1) *
+                             load_scale(p.scale_b, p.scale_dtype, (int64_t)(kb + 1) * p.sb_s0 + sb_col * p.sb_s1);
+                ok = mbar_wait(part_full_bar(buf), buf_phase, s_abort, p.status, 0x800 | buf);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(buf * TBN);
+#pragma unroll
+                for (int c = 0; c < TBN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float x = (KIND == 0) ? (float)(int32_t)r[j] : __uint_as_float(r[j]);
+                        acc[c * 32 + j] = __fmaf_rn(x, s, acc[c * 32 + j]);
+                    }
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                mbar_arrive(part_empty_bar(buf));
+                if (++buf == T_BUFS) { buf = 0; buf_phase ^= 1u; }
+            }
+            if (!ok) break;
+            if (row < p.M) {
+                if (p.scale_dtype == QT_BF16) {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + row * p.ldc + n0;
+                    if (n0 + TBN <= p.N && (p.ldc & 7) == 0) {
+#pragma unroll
+                        for (int j = 0; j < TBN; j += 8)
+                            *reinterpret_cast<uint4*>(dst + j) =
+                                make_uint4(pack_bf16x2(acc[j], acc[j + 1]), pack_bf16x2(acc[j + 2], acc[j + 3]),
+                                           pack_bf16x2(acc[j + 4], acc[j + 5]), pack_bf16x2(acc[j + 6], acc[j + 7]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < TBN; ++j)
+                            if (n0 + j < p.N) dst[j] = __float2bfloat16_rn(acc[j]);
+                    }
+                } else {
+                    float* dst = reinterpret_cast<float*>(p.c) + row * p.ldc + n0;
+#pragma unroll
+                    for (int j = 0; j < TBN; ++j)
+                        if (n0 + j < p.N) dst[j] = acc[j];
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(T_TMEM_COLS) : "memory");
+    }
+}
+
+template <int KIND, bool A_MN, bool B_MN>
+int launch_tile(const CUtensorMap& ta, const CUtensorMap& tb, const TileGemmParams& p, uint32_t idesc, int grid, cudaStream_t stream) {
+    auto kfn = tile_gemm_kernel<KIND, A_MN, B_MN>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    QT_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        QT_CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM_TOTAL));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    kfn<<<grid, T_THREADS, T_SMEM_TOTAL, stream>>>(ta, tb, p, idesc);
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
+template <int KIND>
+int launch_tile_layout(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const TileGemmParams& p, uint32_t idesc,
+                       int grid, cudaStream_t stream) {
+    if (!a_mn && !b_mn) return launch_tile<KIND, false, false>(ta, tb, p, idesc, grid, stream);
+    if (!a_mn && b_mn) return launch_tile<KIND, false, true>(ta, tb, p, idesc, grid, stream);
+    if (a_mn && b_mn) return launch_tile<KIND, true, true>(ta, tb, p, idesc, grid, stream);
+    return launch_tile<KIND, true, false>(ta, tb, p, idesc, grid, stream);
+}
+
+}  // namespace
+
+}  // namespace qt
+
+using namespace qt;
+using namespace qt::tc;
+
+extern "C" int qt_tile_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype,
+                                 int64_t b_sk, int64_t b_sn, const void* scale_a, int64_t sa_s0, int64_t sa_s1,
+                                 const void* scale_b, int64_t sb_s0, int64_t sb_s1, int qm, int qn, int qk, int scale_dtype,
+                                 void* c, int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    QT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "tile_scaled_mm: negative dimension");
+    QT_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "tile_scaled_mm: dimension exceeds 2^31");
+    const bool is_i8 = a_dtype == QT_I8 && b_dtype == QT_I8;
+    const bool is_f8 = (a_dtype == QT_E4M3 || a_dtype == QT_E5M2) && (b_dtype == QT_E4M3 || b_dtype == QT_E5M2);
+    QT_REQUIRE(is_i8 || is_f8, "tile_scaled_mm: operands must both be int8 or both be fp8 (got %d, %d)", a_dtype, b_dtype);
+    QT_REQUIRE(scale_dtype == QT_BF16 || scale_dtype == QT_F32, "tile_scaled_mm: scale_dtype must be QT_BF16 or QT_F32 (got %d)", scale_dtype);
+    if (M == 0 || N == 0) return QT_OK;
+    QT_REQUIRE(a && b && c && scale_a && scale_b, "tile_scaled_mm: null pointer");
+    if (qk != TBK || K % TBK != 0 || K == 0)
+        return fail(QT_ERR_UNSUPPORTED, "tile_scaled_mm: the reduction block must be 128 and K a positive multiple of it (qk=%d, K=%lld)", qk, (long long)K);
+    if (qm < 1 || qn < TBN || qn % TBN != 0)
+        return fail(QT_ERR_UNSUPPORTED, "tile_scaled_mm: qm must be >= 1 and qn a multiple of 128 (qm=%d, qn=%d)", qm, qn);
+    QT_REQUIRE((a_sk == 1) != (a_sm == 1) || M == 1, "tile_scaled_mm: exactly one stride of A must be 1");
+    QT_REQUIRE((b_sk == 1) != (b_sn == 1) || N == 1, "tile_scaled_mm: exactly one stride of B must be 1");
+    const bool a_mn = (a_sk != 1), b_mn = (b_sk != 1);
+    const int64_t a_pitch = a_mn ? a_sk : a_sm, b_pitch = b_mn ? b_sk : b_sn;
+    QT_REQUIRE(aligned_to(a, 16) && aligned_to(b, 16), "tile_scaled_mm: operand base pointers must be 16-byte aligned");
+    QT_REQUIRE(a_pitch % 16 == 0 && b_pitch % 16 == 0, "tile_scaled_mm: the non-unit operand strides must be multiples of 16");
+    QT_REQUIRE(ldc >= N, "tile_scaled_mm: ldc smaller than N");
+
+    CUtensorMap ta, tb;
+    if (a_mn) { if (int rc = make_tmap(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)a_pitch, 128, TBK)) return rc; }
+    else      { if (int rc = make_tmap(&ta, a, (uint64_t)K, (uint64_t)M, (uint64_t)a_pitch, TBK, TBM)) return rc; }
+    if (b_mn) { if (int rc = make_tmap(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)b_pitch, 128, TBK)) return rc; }
+    else      { if (int rc = make_tmap(&tb, b, (uint64_t)K, (uint64_t)N, (uint64_t)b_pitch, TBK, TBN)) return rc; }
+
+    TileGemmParams p = {};
+    p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.scale_a = scale_a; p.scale_b = scale_b;
+    p.sa_s0 = sa_s0; p.sa_s1 = sa_s1; p.sb_s0 = sb_s0; p.sb_s1 = sb_s1; p.qm = qm; p.qn = qn; p.scale_dtype = scale_dtype;
+    if (int rc = device_status_ptr(&p.status)) return rc;
+    const int64_t tiles = ((M + TBM - 1) / TBM) * ((N + TBN - 1) / TBN);
+    const int sms = num_sms();
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    const uint32_t idesc = is_i8 ? make_idesc(2, 1, 1, a_mn, b_mn, TBM, TBN)
+                                 : make_idesc(1, fp8_format(a_dtype), fp8_format(b_dtype), a_mn, b_mn, TBM, TBN);
+    return is_i8 ? launch_tile_layout<0>(a_mn, b_mn, ta, tb, p, idesc, grid, stream)
+                 : launch_tile_layout<1>(a_mn, b_mn, ta, tb, p, idesc, grid, stream);
+}

@@ -12,9 +12,17 @@ char* last_error_buffer() {
 __device__ int g_device_status = 0;
 
 int device_status_ptr(int** out) {
+    static int* cached[64] = {nullptr};
+    int dev = 0;
+    QT_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && cached[dev]) {
+        *out = cached[dev];
+        return QT_OK;
+    }
     void* p = nullptr;
     QT_CUDA_CHECK(cudaGetSymbolAddress(&p, g_device_status));
     *out = reinterpret_cast<int*>(p);
+    if (dev >= 0 && dev < 64) cached[dev] = *out;
     return QT_OK;
 }
 

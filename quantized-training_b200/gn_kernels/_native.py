@@ -96,6 +96,24 @@ def stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def on_device(device: torch.device):
+    """Context manager that makes `device` current for the C call; free when it already is."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
+
+
 def code(dtype: torch.dtype) -> int:
     try:
         return DTYPE_CODE[dtype]

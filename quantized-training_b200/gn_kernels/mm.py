@@ -29,8 +29,11 @@ def _operand(t: Tensor, k_dim: int) -> Tensor:
     return view if k_dim == 1 else view.T
 
 
-def _strides_a(a: Tensor) -> tuple[int, int]:
-    return a.stride(0), a.stride(1)
+def _direct(*tensors: Tensor) -> bool:
+    """Plain CUDA tensors outside torch.compile tracing: call the kernel without the dispatcher."""
+    if torch.compiler.is_compiling():
+        return False
+    return all(type(t) is Tensor and t.is_cuda for t in tensors)
 
 
 lib.define("int8_mm(Tensor A, Tensor B) -> Tensor")
@@ -42,7 +45,7 @@ def int8_mm(A: Tensor, B: Tensor) -> Tensor:
     """int32 C = A @ B for int8 A [M,K], B [K,N], any of the A@B.T / A@B / A.T@B layouts."""
     assert A.dtype is torch.int8 and B.dtype is torch.int8
     assert A.shape[1] == B.shape[0]
-    return lib_ops.int8_mm(A, B)
+    return _int8_mm_cuda(A, B) if _direct(A, B) else lib_ops.int8_mm(A, B)
 
 
 @torch.library.impl(lib, "int8_mm", "Meta")
@@ -51,7 +54,7 @@ def _(a: Tensor, b: Tensor):
 
 
 @torch.library.impl(lib, "int8_mm", "CUDA")
-def _(A: Tensor, B: Tensor):
+def _int8_mm_cuda(A: Tensor, B: Tensor):
     dev = nv.require_cuda(A, B)
     M, K = A.shape
     N = B.shape[1]
@@ -61,7 +64,7 @@ def _(A: Tensor, B: Tensor):
     if K == 0:
         return C.zero_()
     A, B = _operand(A, 1), _operand(B, 0)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_int8_mm(A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1),
                                       C.data_ptr(), C.stride(0), M, N, K, nv.stream_ptr(dev)))
     return C
@@ -89,9 +92,13 @@ def scaled_mm(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor) -> Tensor:
     if scale_A.shape == (A.shape[0], 1) and scale_B.shape in ((1, B.shape[1]), (1, 1)):
         assert scale_A.is_contiguous()
         assert scale_B.is_contiguous()
+        if _direct(A, B, scale_A, scale_B):
+            return _scaled_mm_cuda(A, B, scale_A, scale_B)
         return lib_ops.scaled_mm(A, B, scale_A, scale_B)
 
     assert scale_A.shape[1] == scale_B.shape[0]
+    if _direct(A, B, scale_A, scale_B):
+        return _tile_scaled_mm_cuda(A, B, scale_A, scale_B)
     return lib_ops.tile_scaled_mm(A, B, scale_A, scale_B)
 
 
@@ -107,7 +114,7 @@ def _scale_dtype_ok(scale: Tensor) -> None:
 
 
 @torch.library.impl(lib, "scaled_mm", "CUDA")
-def _(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor):
+def _scaled_mm_cuda(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor):
     dev = nv.require_cuda(A, B, row_scale, col_scale)
     _scale_dtype_ok(row_scale)
     M, K = A.shape
@@ -119,7 +126,7 @@ def _(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor):
         return C.zero_()
     A, B = _operand(A, 1), _operand(B, 0)
     row_scale, col_scale = row_scale.contiguous(), col_scale.contiguous()
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_scaled_mm(
             A.data_ptr(), nv.code(A.dtype), A.stride(0), A.stride(1), B.data_ptr(), nv.code(B.dtype), B.stride(0),
             B.stride(1), row_scale.data_ptr(), col_scale.data_ptr(), int(col_scale.numel() == 1 and N != 1),
@@ -128,7 +135,7 @@ def _(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor):
 
 
 @torch.library.impl(lib, "tile_scaled_mm", "CUDA")
-def _(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor):
+def _tile_scaled_mm_cuda(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor):
     dev = nv.require_cuda(A, B, scale_A, scale_B)
     _scale_dtype_ok(scale_A)
     M, K = A.shape
@@ -140,7 +147,7 @@ def _(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor):
         return C.zero_()
     qm, qk, qn = M // scale_A.shape[0], K // scale_A.shape[1], N // scale_B.shape[1]
     A, B = _operand(A, 1), _operand(B, 0)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_tile_scaled_mm(
             A.data_ptr(), nv.code(A.dtype), A.stride(0), A.stride(1), B.data_ptr(), nv.code(B.dtype), B.stride(0),
             B.stride(1), scale_A.data_ptr(), scale_A.stride(0), scale_A.stride(1), scale_B.data_ptr(), scale_B.stride(0),

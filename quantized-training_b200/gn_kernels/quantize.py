@@ -57,13 +57,13 @@ def _(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
 
 
 @torch.library.impl(lib, "quantize_rowwise", "CUDA")
-def _(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
+def _rowwise_cuda(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
     x = _rows_view(x)
     dev = nv.require_cuda(x)
     rows, cols = x.shape
     q = torch.empty((rows, cols), dtype=out_dtype, device=dev)
     scale = torch.empty((rows, 1), dtype=scale_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_quantize_rowwise(
             x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), q.data_ptr(), nv.code(out_dtype),
             scale.data_ptr(), nv.code(scale_dtype), eps, int(stochastic), seed, offset, nv.stream_ptr(dev)))
@@ -77,14 +77,14 @@ def _(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
 
 
 @torch.library.impl(lib, "quantize_rowwise_colabsmax", "CUDA")
-def _(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
+def _rowwise_colabsmax_cuda(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
     x = _rows_view(x)
     dev = nv.require_cuda(x)
     rows, cols = x.shape
     q = torch.empty((rows, cols), dtype=out_dtype, device=dev)
     scale = torch.empty((rows, 1), dtype=scale_dtype, device=dev)
     colmax = torch.empty((cols,), dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_quantize_rowwise_colabsmax(
             x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), q.data_ptr(), nv.code(out_dtype),
             scale.data_ptr(), nv.code(scale_dtype), colmax.data_ptr(), eps, int(stochastic), seed, offset,
@@ -98,12 +98,12 @@ def _(x):
 
 
 @torch.library.impl(lib, "col_absmax", "CUDA")
-def _(x):
+def _col_absmax_cuda(x):
     x = _rows_view(x)
     dev = nv.require_cuda(x)
     rows, cols = x.shape
     colmax = torch.empty((cols,), dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_col_absmax(x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x),
                                          colmax.data_ptr(), nv.stream_ptr(dev)))
     return colmax
@@ -115,7 +115,7 @@ def _(x, col_absmax, out_dtype, scale_dtype, stochastic, eps, seed, offset):
 
 
 @torch.library.impl(lib, "quantize_colwise_t", "CUDA")
-def _(x, col_absmax, out_dtype, scale_dtype, stochastic, eps, seed, offset):
+def _colwise_t_cuda(x, col_absmax, out_dtype, scale_dtype, stochastic, eps, seed, offset):
     x = _rows_view(x)
     dev = nv.require_cuda(x, col_absmax)
     rows, cols = x.shape
@@ -123,7 +123,7 @@ def _(x, col_absmax, out_dtype, scale_dtype, stochastic, eps, seed, offset):
         raise ValueError("col_absmax must be a contiguous float32 tensor with one entry per column of x")
     qt = torch.empty((cols, rows), dtype=out_dtype, device=dev)
     scale = torch.empty((cols, 1), dtype=scale_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_quantize_colwise_t(
             x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), col_absmax.data_ptr(), qt.data_ptr(),
             nv.code(out_dtype), scale.data_ptr(), nv.code(scale_dtype), eps, int(stochastic), seed, offset,
@@ -138,13 +138,13 @@ def _(x, tile_r, tile_c, out_dtype, scale_dtype, eps):
 
 
 @torch.library.impl(lib, "quantize_tile", "CUDA")
-def _(x, tile_r, tile_c, out_dtype, scale_dtype, eps):
+def _tile_cuda(x, tile_r, tile_c, out_dtype, scale_dtype, eps):
     x = _rows_view(x)
     dev = nv.require_cuda(x)
     rows, cols = x.shape
     q = torch.empty((rows, cols), dtype=out_dtype, device=dev)
     scale = torch.empty((-(-rows // tile_r), -(-cols // tile_c)), dtype=scale_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_quantize_tile(
             x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), tile_r, tile_c, q.data_ptr(),
             nv.code(out_dtype), scale.data_ptr(), nv.code(scale_dtype), eps, nv.stream_ptr(dev)))
@@ -157,6 +157,13 @@ def _key(x: Tensor, stochastic: bool) -> tuple[int, int]:
     return next_philox_key(x.device) if stochastic else (0, 0)
 
 
+def _direct(x: Tensor) -> bool:
+    """True when the kernel can be called without going through the dispatcher: a plain CUDA tensor
+    outside torch.compile tracing. The dispatcher round trip into a Python kernel costs about as much
+    host time as the launch itself."""
+    return type(x) is Tensor and x.is_cuda and not torch.compiler.is_compiling()
+
+
 def quantize_rowwise(x: Tensor, out_dtype: torch.dtype = torch.int8, stochastic_rounding: bool = False, *,
                      eps: float = 1e-12, scale_dtype: torch.dtype | None = None, key: tuple[int, int] | None = None):
     """Per-row absmax quantize of a 2-D tensor: returns (q [R,C], scale [R,1]).
@@ -165,7 +172,8 @@ def quantize_rowwise(x: Tensor, out_dtype: torch.dtype = torch.int8, stochastic_
     (subclasses/int8.py:26). `key` = (seed, offset) pins the stochastic-rounding stream.
     """
     seed, offset = key if key is not None else _key(x, stochastic_rounding)
-    return lib_ops.quantize_rowwise(x, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
+    fn = _rowwise_cuda if _direct(x) else lib_ops.quantize_rowwise
+    return fn(x, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
 
 
 def quantize_rowwise_colabsmax(x: Tensor, out_dtype: torch.dtype = torch.int8, stochastic_rounding: bool = False, *,
@@ -173,12 +181,13 @@ def quantize_rowwise_colabsmax(x: Tensor, out_dtype: torch.dtype = torch.int8, s
                                key: tuple[int, int] | None = None):
     """quantize_rowwise plus the per-column |x| maximum ([C] float32) from the same pass over x."""
     seed, offset = key if key is not None else _key(x, stochastic_rounding)
-    return lib_ops.quantize_rowwise_colabsmax(x, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
+    fn = _rowwise_colabsmax_cuda if _direct(x) else lib_ops.quantize_rowwise_colabsmax
+    return fn(x, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
 
 
 def col_absmax(x: Tensor) -> Tensor:
     """Per-column |x| maximum of a 2-D tensor, float32 [C]."""
-    return lib_ops.col_absmax(x)
+    return _col_absmax_cuda(x) if _direct(x) else lib_ops.col_absmax(x)
 
 
 def quantize_colwise_t(x: Tensor, out_dtype: torch.dtype = torch.int8, stochastic_rounding: bool = False, *,
@@ -187,12 +196,14 @@ def quantize_colwise_t(x: Tensor, out_dtype: torch.dtype = torch.int8, stochasti
     """Per-column absmax quantize with the transpose materialised: returns (q [C,R], scale [C,1]),
     equal to quantizing `x.T` row-wise and calling `.contiguous()` (subclasses/mixed_precision.py:102-105)."""
     if col_absmax_ is None:
-        col_absmax_ = lib_ops.col_absmax(x)
+        col_absmax_ = col_absmax(x)
     seed, offset = key if key is not None else _key(x, stochastic_rounding)
-    return lib_ops.quantize_colwise_t(x, col_absmax_, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
+    fn = _colwise_t_cuda if _direct(x) else lib_ops.quantize_colwise_t
+    return fn(x, col_absmax_, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
 
 
 def quantize_tile(x: Tensor, tile_shape: tuple[int, int], out_dtype: torch.dtype = torch.int8, *, eps: float = 1e-12,
                   scale_dtype: torch.dtype | None = None):
     """Per-tile absmax quantize (tiles 1x128 or 128x128): returns (q [R,C], scale [R/tr, C/tc])."""
-    return lib_ops.quantize_tile(x, tile_shape[0], tile_shape[1], out_dtype, scale_dtype or x.dtype, eps)
+    fn = _tile_cuda if _direct(x) else lib_ops.quantize_tile
+    return fn(x, tile_shape[0], tile_shape[1], out_dtype, scale_dtype or x.dtype, eps)

@@ -81,7 +81,7 @@ def adamw(p: Tensor, grad: Tensor, step: Tensor, exp_avg: Tensor, exp_avg_sq: Te
     sqrt_bc2 = bc2.sqrt()
     lr32 = lr.detach().to("cpu", torch.float32)
     seed, offset = key if key is not None else (next_philox_key(dev) if bf16_sr else (0, 0))
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_adamw_bf16_sr(
             p.data_ptr(), nv.code(p.dtype), grad.data_ptr(), nv.code(grad.dtype), exp_avg.data_ptr(), exp_avg_sq.data_ptr(),
             p.numel(), float(lr32), float(beta1), float(beta2), float(weight_decay), float(eps), float(bc1),

@@ -50,7 +50,7 @@ def get_bitnet_scale(x: Tensor) -> Tensor:
     if x.numel() == 0:
         return out.fill_(float("nan"))
     workspace = torch.empty(1024, dtype=torch.float64, device=dev)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_abs_mean(x.data_ptr(), nv.code(x.dtype), x.numel(), out.data_ptr(), workspace.data_ptr(),
                                        workspace.numel() * 8, nv.stream_ptr(dev)))
     return out
@@ -67,7 +67,7 @@ def _ternarize(w: Tensor, scale: Tensor, eps: float, pack: bool) -> Tensor:
         out = torch.empty((w.shape[0], w.shape[1] // 4), dtype=torch.int8, device=dev)
     else:
         out = torch.empty(w.shape, dtype=torch.int8, device=dev)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_bitnet_quantize_weight(w.data_ptr(), nv.code(w.dtype), w.numel(), scale.data_ptr(), eps,
                                                      out.data_ptr(), int(pack), nv.stream_ptr(dev)))
     return out
@@ -93,7 +93,7 @@ def _unpack_i2_in_i8(x: Tensor) -> Tensor:
     dev = nv.require_cuda(x)
     x = x.contiguous()
     out = torch.empty((x.shape[0], x.shape[1] * 4), dtype=torch.int8, device=dev)
-    with torch.cuda.device(dev):
+    with nv.on_device(dev):
         nv.check(nv.load().qt_unpack_i2(x.data_ptr(), x.numel(), out.data_ptr(), nv.stream_ptr(dev)))
     return out
 

@@ -167,3 +167,47 @@ def test_full_size_gemm_properties():
     want = om.int8_mm(A[rows].cpu().numpy(), B.cpu().numpy())
     np.testing.assert_array_equal(acc[rows].cpu().numpy(), want)
     assert nv.device_status() == 0
+
+
+@pytest.mark.parametrize("layout", ["A@B.T", "A@B", "A.T@B"])
+@pytest.mark.parametrize("tiles", [(1, 128), (128, 128)])
+def test_tile_scaled_mm_int8(layout, tiles):
+    """DeepSeek-style 1x128 activation / 128x128 weight tiles (benchmark_mm.py:87-89), and 128x128 on
+    both sides; acceptance as benchmark_mm.py:119-121 (atol 1e-4, rtol 1e-2) against the oracle."""
+    M, N, K = 384, 512, 640
+    qm = tiles[0]
+    A, B = rand_i8((M, K), 51), rand_i8((K, N), 52)
+    g = torch.Generator().manual_seed(53)
+    sa = (torch.randn(M // qm, K // 128, generator=g) / 128).bfloat16().cuda()
+    sb = (torch.randn(K // 128, N // 128, generator=g) / 128).bfloat16().cuda()
+    a, b = to_layout(A, B, layout)
+    out = gn_kernels.scaled_mm(a, b, sa, sb)
+    want = om.tile_scaled_mm(A.cpu().numpy(), B.cpu().numpy(), values_of(sa), values_of(sb))
+    np.testing.assert_allclose(values_of(out), want, atol=1e-4, rtol=1e-2)
+    assert out.dtype is torch.bfloat16 and nv.device_status() == 0
+    # column-major scale tensors (the benchmark re-lays them out with the operands) are read by stride
+    out2 = gn_kernels.scaled_mm(a, b, sa.T.contiguous().T, sb.T.contiguous().T)
+    assert torch.equal(out, out2)
+
+
+def test_tile_scaled_mm_reference_fixture_and_fp8(golden_dir):
+    g = np.load(golden_dir / "scaled_mm_ref.npz")
+
+    def bf(a):
+        return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).cuda()
+
+    A, B = torch.from_numpy(g["A"]).cuda(), torch.from_numpy(g["B"]).cuda()
+    out = gn_kernels.scaled_mm(A, B, bf(g["tsA"]), bf(g["tsB"]))
+    np.testing.assert_allclose(values_of(out), om.bf16_bits_to_f32(g["tile"]), atol=1e-4, rtol=1e-2)
+    A8 = torch.from_numpy(g["A8"]).cuda().view(torch.float8_e4m3fn)
+    B8 = torch.from_numpy(g["B8"]).cuda().view(torch.float8_e4m3fn)
+    out8 = gn_kernels.scaled_mm(A8, B8, bf(g["tsA"]), bf(g["tsB"]))
+    np.testing.assert_allclose(values_of(out8), om.bf16_bits_to_f32(g["f8_tile"]), rtol=1.6e-2, atol=2e-5)
+
+
+def test_tile_scaled_mm_rejects_unsupported_blocks():
+    A, B = rand_i8((128, 256), 1), rand_i8((256, 128), 2)
+    sa = torch.ones((128, 4), dtype=torch.bfloat16, device="cuda")   # qk = 64
+    sb = torch.ones((4, 1), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="reduction block must be 128"):
+        gn_kernels.scaled_mm(A, B, sa, sb)

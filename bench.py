@@ -47,6 +47,10 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M = N = K")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "train-470m", "train-1b"],
+                    help="gemm: the headline quantize + scaled GEMM step; train-*: one INT8 mixed-precision Llama step (tok/s)")
+    ap.add_argument("--quantize", default="mixed_precision", choices=["mixed_precision", "none", "int8_quantized_training", "bitnet"],
+                    help="train-* workloads: which weight subclass the decoder's Linear layers get (none = bf16 baseline)")
     ap.add_argument("--no-clock-sampler", action="store_true", help="do not run nvidia-smi beside the timed region")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0, help="keep warming up at least this long (0 under a profiler)")
     return ap.parse_args()
@@ -160,6 +164,82 @@ def run_reference(args, rank: int):
     print(json.dumps(line), flush=True)
 
 
+LLAMA_SHAPES = {
+    # the reference's shipped config (mini_llamas/Llama-2-470m/config.json:5-10) and the 1.1B shape of BASELINE.json
+    "train-470m": dict(hidden_size=1024, intermediate_size=4096, num_hidden_layers=24, num_attention_heads=16,
+                       num_key_value_heads=16),
+    "train-1b": dict(hidden_size=2048, intermediate_size=5632, num_hidden_layers=22, num_attention_heads=32,
+                     num_key_value_heads=4),
+}
+
+
+def run_train(args, rank, local_rank, world):
+    """Secondary workload: one INT8 mixed-precision training step of a random-init Llama-style decoder
+    (forward, grad-input and grad-weight GEMMs all row-wise INT8; LM head in bf16; AdamWBF16SR), batch
+    16 x 2048 random tokens per GPU, tok/s as the reference computes it (llm_pretrain.py:229-234).
+    Data parallel over ranks with DDP-style gradient all-reduce when launched with torchrun."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from train_utils import get_optimizer, quantize_model
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    bs, seq = 16, 2048
+    torch.manual_seed(2024)
+    cfg = LlamaConfig(vocab_size=32000, max_position_embeddings=seq, attn_implementation="sdpa", tie_word_embeddings=False,
+                      **LLAMA_SHAPES[args.workload])
+    with torch.device(dev):
+        model = LlamaForCausalLM(cfg).bfloat16()
+    quantize_model(model.model, None if args.quantize == "none" else args.quantize)
+    if world > 1:
+        model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
+    optim = get_optimizer("other_optim.AdamWBF16SR", model, lr=1e-4, weight_decay=0.01)
+    torch.manual_seed(2024 + rank)
+    tokens = torch.randint(0, 32000, (bs, seq + 1), device=dev)
+
+    def step():
+        logits = model(input_ids=tokens[:, :-1]).logits.float()
+        loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), tokens[:, 1:].reshape(-1))
+        loss.backward()
+        optim.step()
+        optim.zero_grad(set_to_none=True)
+        return loss
+
+    for _ in range(max(args.warmup, 3)):
+        loss = step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    if rank == 0:
+        n_params = sum(p.numel() for p in model.parameters())
+        print(json.dumps({
+            "metric": "int8_mixed_precision_train_tok_per_s", "value": world * bs * seq * args.steps / (ms * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: Llama-style decoder, {n_params / 1e6:.0f}M params, quantize={args.quantize} "
+                                   f"(LM head bf16), AdamWBF16SR, batch {bs} x {seq} random tokens per GPU",
+                       "parallelism": f"dp{world}"},
+            "loss": float(loss.detach()), "max_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -168,6 +248,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload != "gemm":
+        run_train(args, rank, local_rank, world)
         return
 
     if not torch.cuda.is_available():

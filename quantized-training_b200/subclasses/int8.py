@@ -18,15 +18,63 @@ from gn_kernels import scaled_mm
 aten = torch.ops.aten
 
 
-def _rows_quantize(t2d: Tensor, stochastic_rounding: bool, eps: float, key=None, col_absmax: Tensor | None = None):
+class _QuantCache:
+    """Remembers the last few round-to-nearest quantizations so a tensor that feeds several Linear
+    layers (the hidden state into q/k/v, or into gate/up) is quantized once, not once per layer.
+
+    An entry is valid only for the very same tensor object state: same storage address, shape, strides
+    and version counter. The entry keeps a reference to its source tensor, so the storage cannot be
+    freed and handed to another tensor while the entry lives; an in-place write bumps the version.
+    Stochastic rounding is never cached (every use must draw fresh noise)."""
+
+    SLOTS = 4
+
+    def __init__(self):
+        self.entries: list[tuple[tuple, Tensor, tuple]] = []
+
+    @staticmethod
+    def key(t: Tensor, eps: float):
+        return (t.data_ptr(), t._version, tuple(t.shape), tuple(t.stride()), t.dtype, eps)
+
+    def get(self, t: Tensor, eps: float):
+        k = self.key(t, eps)
+        for kk, _src, out in self.entries:
+            if kk == k:
+                return out
+        return None
+
+    def put(self, t: Tensor, eps: float, out: tuple):
+        self.entries.append((self.key(t, eps), t, out))
+        if len(self.entries) > self.SLOTS:
+            self.entries.pop(0)
+
+    def clear(self):
+        self.entries.clear()
+
+
+_quant_cache = _QuantCache()
+
+
+def _rows_quantize(t2d: Tensor, stochastic_rounding: bool, eps: float, key=None, col_absmax: Tensor | None = None,
+                   cache: bool = False):
     """Quantize each ROW of a 2-D tensor; returns contiguous int8 of t2d's shape and scale [rows,1].
 
     A transposed view (unit stride along dim 0) is served by the transposing column-wise kernel
-    on its base, so `quantize_int8(B.T, dim=1)` never materialises `B.T` in bf16."""
+    on its base, so `quantize_int8(B.T, dim=1)` never materialises `B.T` in bf16. `cache=True` lets
+    repeated round-to-nearest requests for the same activation reuse the first result."""
+    use_cache = cache and not stochastic_rounding and not torch.compiler.is_compiling()
+    if use_cache:
+        hit = _quant_cache.get(t2d, eps)
+        if hit is not None:
+            return hit
     if t2d.shape[0] > 1 and t2d.shape[1] > 1 and t2d.stride(0) == 1 and t2d.stride(1) >= t2d.shape[0]:
-        return gn_kernels.quantize_colwise_t(t2d.T, torch.int8, stochastic_rounding, eps=eps, key=key,
-                                             col_absmax_=col_absmax)
-    return gn_kernels.quantize_rowwise(t2d, torch.int8, stochastic_rounding, eps=eps, key=key)
+        out = gn_kernels.quantize_colwise_t(t2d.T, torch.int8, stochastic_rounding, eps=eps, key=key,
+                                            col_absmax_=col_absmax)
+    else:
+        out = gn_kernels.quantize_rowwise(t2d, torch.int8, stochastic_rounding, eps=eps, key=key)
+    if use_cache:
+        _quant_cache.put(t2d, eps, out)
+    return out
 
 
 @torch.no_grad()

@@ -126,11 +126,11 @@ class MixedPrecisionLinearWeight(Tensor):
 
 
 def _dynamic_int8_mm(A: Tensor, B: Tensor, sr: bool, *, a_col_absmax: Tensor | None = None,
-                     b_col_absmax: Tensor | None = None) -> Tensor:
+                     b_col_absmax: Tensor | None = None, cache_a: bool = False) -> Tensor:
     """bf16 A [M,K] @ B [K,N] through INT8: rows of A and columns of B get absmax scales
     (reference: mixed_precision.py:100-108). Either operand may be a transposed view; the optional
     absmax tensors are precomputed per-column maxima of the operand's BASE (row-major) tensor."""
-    A_i8, row_scale = _rows_quantize(A, sr, 1e-12, col_absmax=a_col_absmax)
+    A_i8, row_scale = _rows_quantize(A, sr, 1e-12, col_absmax=a_col_absmax, cache=cache_a)
     Bt_i8, col_scale = _rows_quantize(B.T, sr, 1e-12, col_absmax=b_col_absmax)
     return scaled_mm(A_i8, Bt_i8.T, row_scale, col_scale.view(1, -1))
 
@@ -153,7 +153,8 @@ class _Int8MixedPrecisionLinear(torch.autograd.Function):
         if cfg.output:
             batch_dims = input.shape[:-1]
             x2d = input.reshape(-1, weight.shape[1])
-            out = _dynamic_mm(x2d, weight._data.T, cfg.stochastic_rounding, cfg.dtype)
+            # the same hidden state usually feeds several projections: quantize it once
+            out = _dynamic_mm(x2d, weight._data.T, cfg.stochastic_rounding, cfg.dtype, cache_a=True)
             out = out.view(*batch_dims, weight.shape[0])
         else:
             out = input @ weight._data.T
@@ -194,7 +195,7 @@ class _Int8MixedPrecisionLinear(torch.autograd.Function):
 
         if ctx.needs_input_grad[1]:
             if cfg.grad_weight:
-                grad_weight = _dynamic_mm(x2d.T, gy, sr, cfg.dtype, b_col_absmax=gy_colmax).T
+                grad_weight = _dynamic_mm(x2d.T, gy, sr, cfg.dtype, b_col_absmax=gy_colmax, cache_a=True).T
             else:
                 grad_weight = gy.T @ x2d
 

@@ -271,3 +271,36 @@ def test_optimizer_class_trains_a_converted_model():
         loss = F.mse_loss(model(x).float(), target.float())
         loss.backward()
         opt.step()
+
+
+def test_activation_quantization_cache_is_exact_and_invalidates():
+    """A hidden state feeding several projections is quantized once; the cached result must be the
+    same bytes, and an in-place update or a new tensor at the same address must miss."""
+    from subclasses.int8 import _quant_cache, _rows_quantize
+
+    _quant_cache.clear()
+    x = randn_bf16((256, 512), seed=12)
+    q1, s1 = _rows_quantize(x, False, 1e-12, cache=True)
+    q2, s2 = _rows_quantize(x, False, 1e-12, cache=True)
+    assert q2 is q1 and s2 is s1                                  # hit
+    x.mul_(2)                                                      # version bump -> miss, fresh values
+    q3, s3 = _rows_quantize(x, False, 1e-12, cache=True)
+    assert q3 is not q1 and torch.equal(q3, q1) and not torch.equal(s3, s1)
+    qt1, _ = _rows_quantize(x.T, False, 1e-12, cache=True)         # transposed view is its own entry
+    qt2, _ = _rows_quantize(x.T, False, 1e-12, cache=True)
+    assert qt2 is qt1 and qt1.shape == (512, 256)
+    qs1, _ = _rows_quantize(x, True, 1e-12, cache=True)            # stochastic rounding is never cached
+    qs2, _ = _rows_quantize(x, True, 1e-12, cache=True)
+    assert qs1 is not qs2
+    # three projections of one input: identical to three independent computations
+    lins = [torch.nn.Linear(512, 128, bias=False).bfloat16().cuda() for _ in range(3)]
+    for lin in lins:
+        convert_mixed_precision(lin)
+    _quant_cache.clear()
+    with_cache = [lin(x) for lin in lins]
+    outs = []
+    for lin in lins:
+        _quant_cache.clear()
+        outs.append(lin(x))
+    for a, b in zip(with_cache, outs):
+        assert torch.equal(a, b)

@@ -17,6 +17,7 @@ baseline of the same path on the host cores, clocks sampled during the timed reg
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -51,6 +52,7 @@ def parse_args():
                     help="gemm: the headline quantize + scaled GEMM step; train-*: one INT8 mixed-precision Llama step (tok/s)")
     ap.add_argument("--quantize", default="mixed_precision", choices=["mixed_precision", "none", "int8_quantized_training", "bitnet"],
                     help="train-* workloads: which weight subclass the decoder's Linear layers get (none = bf16 baseline)")
+    ap.add_argument("--sm-margin", type=int, default=8, help="SMs the GEMM leaves to the concurrent all-gather when --gpus > 1")
     ap.add_argument("--no-clock-sampler", action="store_true", help="do not run nvidia-smi beside the timed region")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0, help="keep warming up at least this long (0 under a profiler)")
     return ap.parse_args()
@@ -65,18 +67,63 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason sampler running beside the timed region."""
+    """Samples SM clock, power and throttle reasons of one GPU beside the timed region, through NVML
+    in a background thread (the same fields `nvidia-smi --query-gpu=clocks.sm,...` prints; reading
+    only). Falls back to an nvidia-smi subprocess when the NVML binding is missing."""
 
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, interval_s: float = 0.05):
         self.gpu_index = gpu_index
+        self.interval_s = interval_s
+        self.samples = []          # (sm_mhz, reasons bitmask)
+        self.sm_max = None
+        self.thread = None
+        self.stop_flag = None
         self.proc = None
         self.file = None
 
     def start(self):
+        try:
+            import threading
+
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.gpu_index
+            if visible:
+                try:
+                    index = int(visible.split(",")[self.gpu_index])
+                except (ValueError, IndexError):
+                    index = self.gpu_index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self.stop_flag = threading.Event()
+
+            def loop():
+                while not self.stop_flag.is_set():
+                    try:
+                        mhz = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                        try:
+                            mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                        except Exception:
+                            mask = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                        self.samples.append((mhz, mask))
+                    except Exception:
+                        pass
+                    self.stop_flag.wait(self.interval_s)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.thread = None
+            self._start_smi()
+
+    def _start_smi(self):
         try:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
@@ -85,8 +132,23 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def mark(self):
+        """Samples taken from now on count as 'under load'."""
+        self.samples.clear()
+
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        out = {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            if self.samples:
+                out["sm_mhz"] = statistics.median(m for m, _ in self.samples)
+                out["samples"] = len(self.samples)
+                mask = 0
+                for _, r in self.samples:
+                    mask |= r
+                out["reasons"] = sorted(name for bit, name in self.REASONS.items() if mask & bit)
+            return out
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -260,6 +322,9 @@ def main():
     from gn_kernels import _native
 
     _native.load()
+    if world > 1:
+        # leave a few SMs to the all-gather that runs beside the persistent GEMM
+        _native.check(_native.load().qt_set_gemm_sm_margin(args.sm_margin))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -279,19 +344,47 @@ def main():
     W = W_host.to(dev)
     out_host = torch.empty((S, S), dtype=torch.bfloat16).pin_memory()
 
-    wq_full = torch.empty((S, S), dtype=torch.int8, device=dev)
-    ws_full = torch.empty((S, 1), dtype=torch.bfloat16, device=dev)
+    # Gathered weight, double-buffered: with more than one GPU the quantize + all-gather of the NEXT
+    # step's weight runs on a side stream under the current step's activation quantize and GEMM (the
+    # prefetch FSDP2 does for the next layer), so every step still holds exactly one shard quantize,
+    # one all-gather, one activation quantize and one GEMM.
+    wq_full = [torch.empty((S, S), dtype=torch.int8, device=dev) for _ in range(2)]
+    ws_full = [torch.empty((S, 1), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    gathered = [torch.cuda.Event() for _ in range(2)]   # buffer b holds a complete gathered weight
+    consumed = [torch.cuda.Event() for _ in range(2)]   # the GEMM that read buffer b has finished
+    state = {"next": 0, "primed": False}
     gemm_events = []
 
+    def prefetch_weight(w_dev):
+        """Quantize this rank's weight rows and all-gather them into the next buffer (side stream)."""
+        b = state["next"]
+        comm_stream.wait_stream(torch.cuda.current_stream(dev))   # w_dev is ready
+        comm_stream.wait_event(consumed[b])
+        with torch.cuda.stream(comm_stream):
+            wq, ws = gn_kernels.quantize_rowwise(w_dev)
+            dist.all_gather_into_tensor(wq_full[b], wq)
+            dist.all_gather_into_tensor(ws_full[b], ws)
+            wq.record_stream(comm_stream)
+            ws.record_stream(comm_stream)
+            gathered[b].record(comm_stream)
+        state["next"] = 1 - b
+        return b
+
     def step(a_dev, w_dev, record_gemm=False):
-        wq, ws = gn_kernels.quantize_rowwise(w_dev)
         if world > 1:
-            dist.all_gather_into_tensor(wq_full, wq)
-            dist.all_gather_into_tensor(ws_full, ws)
-            wq_all, ws_all = wq_full, ws_full
+            if not state["primed"]:
+                state["ready"] = prefetch_weight(w_dev)
+                state["primed"] = True
+            b = state["ready"]
+            state["ready"] = prefetch_weight(w_dev)     # next step's weight, overlapped with this step
+            aq, as_ = gn_kernels.quantize_rowwise(a_dev)
+            torch.cuda.current_stream(dev).wait_event(gathered[b])
+            wq_all, ws_all = wq_full[b], ws_full[b]
         else:
-            wq_all, ws_all = wq, ws
-        aq, as_ = gn_kernels.quantize_rowwise(a_dev)
+            b = -1
+            wq_all, ws_all = gn_kernels.quantize_rowwise(w_dev)
+            aq, as_ = gn_kernels.quantize_rowwise(a_dev)
         if record_gemm:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -299,6 +392,8 @@ def main():
         if record_gemm:
             e1.record()
             gemm_events.append((e0, e1))
+        if b >= 0:
+            consumed[b].record()
         return out
 
     def sync_all():
@@ -321,7 +416,7 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0 and not args.no_clock_sampler:
         sampler.start()
-        time.sleep(1.0)
+        time.sleep(0.2)
     sync_all()
     warm_steps = 0
     t_warm = time.perf_counter()
@@ -331,6 +426,8 @@ def main():
             step(A, W)
         warm_steps += chunk
         torch.cuda.synchronize()
+        if warm_steps == chunk:
+            sampler.mark()          # from here on the GPU is under this workload's load
         more = 1 if (time.perf_counter() - t_warm) < args.min_warmup_seconds else 0
         if world > 1:  # every rank must run the same number of steps (the step holds a collective)
             flag = torch.tensor([more], dtype=torch.int32, device=dev)
@@ -339,12 +436,15 @@ def main():
         if not more:
             break
     sync_all()
+    gc.collect()
+    gc.disable()   # a collector pause between two launches would be charged to the step
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
         out = step(A, W, record_gemm=True)
     stop.record()
     sync_all()
+    gc.enable()
     ms_total = max_over_ranks(start.elapsed_time(stop))
     ms_per_step = ms_total / args.steps
     gemm_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in gemm_events)
@@ -400,7 +500,7 @@ def main():
         "dtype": "int8", "data": "synthetic",
         "config": {
             "workload": f"rowwise dynamic INT8 quantize (activation + weight shard) + scaled INT8 GEMM A@B.T, M=N=K={S} per GPU, bf16 in/out",
-            "weight_all_gather": "int8 rows + bf16 scales over NCCL" if world > 1 else "none (1 GPU)",
+            "weight_all_gather": "int8 rows + bf16 scales over NCCL, prefetched one step ahead on a side stream" if world > 1 else "none (1 GPU)",
             "l2": "inputs larger than L2 (2 x 134 MB bf16 in, 2 x 67 MB int8 operands, 134 MB out per step)",
             "value_is": "2*M*N*K * n_gpus / step time; the step includes both quantize kernels",
         },

@@ -162,6 +162,14 @@ int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_t cols, int
 int qt_set_gemm_cta_group(int cta_group);
 
 /*
+ * Number of SMs the persistent GEMM grids leave unused (default 0), so that a kernel which has to
+ * run at the same time -- an NCCL collective prefetching the next weight -- finds free SMs instead
+ * of queueing behind a grid that holds every SM until it finishes. Process-wide.
+ * No counterpart in the reference (it leaves overlap to FSDP2's streams and Triton's non-persistent grids).
+ */
+int qt_set_gemm_sm_margin(int sms);
+
+/*
  * C(int32) = A(int8) @ B(int8), exact.
  * replaces: gn_kernels int8_mm, kernels/gn_kernels/triton_mm.py:112-128 (_matmul_kernel :53-109).
  */

@@ -344,6 +344,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
 // 0 = choose per problem, 1 / 2 = force that many CTAs per MMA (set through qt_set_gemm_cta_group)
 int g_forced_cta_group = 0;
+// SMs the persistent GEMM grids leave free for kernels that must run beside them (collectives)
+int g_sm_margin = 0;
 
 template <int KIND, int EPI, bool A_MN, bool B_MN, int CG>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, uint32_t idesc, int64_t tiles,
@@ -378,10 +380,13 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
             if (n_clusters <= 0) return fail(QT_ERR_CUDA, "gemm: no 2-CTA cluster of this kernel fits on the device");
             if (cacheable) max_clusters[dev] = n_clusters;
         }
-        const int64_t pairs = tiles < n_clusters ? tiles : n_clusters;
+        int usable = n_clusters - (g_sm_margin + 1) / 2;
+        if (usable < 1) usable = 1;
+        const int64_t pairs = tiles < usable ? tiles : usable;
         cfg.gridDim = dim3((unsigned)(2 * pairs));
     } else {
-        const int sms = num_sms();
+        int sms = num_sms() - g_sm_margin;
+        if (sms < 1) sms = 1;
         cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));
     }
     QT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kfn, ta, tb, p, idesc));
@@ -455,6 +460,12 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
 }  // namespace qt
 
 using namespace qt;
+
+extern "C" int qt_set_gemm_sm_margin(int sms) {
+    QT_REQUIRE(sms >= 0 && sms < 128, "set_gemm_sm_margin: expected 0..127 (got %d)", sms);
+    g_sm_margin = sms;
+    return QT_OK;
+}
 
 extern "C" int qt_set_gemm_cta_group(int cta_group) {
     QT_REQUIRE(cta_group == 0 || cta_group == 1 || cta_group == 2, "set_gemm_cta_group: expected 0 (auto), 1 or 2");

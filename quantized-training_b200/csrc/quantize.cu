@@ -306,13 +306,15 @@ __device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider<f
 // The next row's loads are issued before the current row is reduced and quantized (register double
 // buffer), which keeps HBM requests in flight through the reduction and the stores. With COLABS
 // each thread also keeps the running |x| maximum of its columns (packed bf16 pairs) over all rows
-// the CTA visits; the CTA folds those into one atomic max per column at the end.
+// the CTA visits; at the end the CTA folds its sub-rows in shared memory, a pair of CTAs (a 2-CTA
+// cluster) folds through distributed shared memory, and one atomic max per column per pair goes out.
 template <int TPR, int VPT, bool COLABS, bool SR>
-__global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (COLABS || SR ? 3 : 4) : (VPT <= 8 ? 2 : 1)))
+__global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1)))
 rowwise_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;  // rows per CTA per iteration
     constexpr int WPR = TPR / 32;        // warps per row
-    constexpr bool PREFETCH = VPT <= 4;
+    // the column-maxima variant spends its registers on the maxima instead of a second row buffer
+    constexpr bool PREFETCH = VPT <= 4 && !COLABS;
     __shared__ float s_red[kThreads / 32];
     __shared__ uint32_t s_col[COLABS ? TPR * VPT * 4 : 1];  // packed bf16 pairs, one per two columns
 
@@ -435,13 +437,10 @@ rowwise_kernel(const RowwiseParams p) {
         const unsigned n_cta = cluster.num_blocks(), rank = cluster.block_rank();
         for (int pair = rank * kThreads + threadIdx.x; pair < PAIRS; pair += n_cta * kThreads) {
             uint32_t m = 0u;
-            if (n_cta == 8) {
-                // issue the eight remote reads together: each one is a trip across the cluster
-                uint32_t v[8];
-#pragma unroll
-                for (unsigned c = 0; c < 8; ++c) v[c] = cluster.map_shared_rank(s_col, c)[pair];
-#pragma unroll
-                for (unsigned c = 0; c < 8; ++c) m = max2(m, v[c]);
+            if (n_cta == 2) {
+                // issue both reads together: the remote one is a trip across the cluster
+                const uint32_t v0 = cluster.map_shared_rank(s_col, 0)[pair], v1 = cluster.map_shared_rank(s_col, 1)[pair];
+                m = max2(v0, v1);
             } else {
                 for (unsigned c = 0; c < n_cta; ++c) m = max2(m, cluster.map_shared_rank(s_col, c)[pair]);
             }
@@ -491,18 +490,21 @@ __global__ void __launch_bounds__(kThreads) rowwise_generic_kernel(const Rowwise
     }
 }
 
-constexpr int kClusterSize = 8;  // CTAs per cluster in the column-absmax variant (portable maximum)
+// CTAs per cluster in the column-absmax variant. Pairs halve the column atomics at no cost; clusters
+// of 4 or 8 constrain CTA placement enough to slow the streaming loop by a quarter (measured).
+constexpr int kClusterSize = 2;
 
 template <int TPR, int VPT, bool COLABS, bool SR>
 int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
     constexpr int RPC = kThreads / TPR;
-    constexpr int CTAS_PER_SM = (VPT <= 4 ? (COLABS || SR ? 3 : 4) : (VPT <= 8 ? 2 : 1));
+    constexpr int CTAS_PER_SM = (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1));
     const int64_t want = (p.rows + RPC - 1) / RPC;
     const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
     int64_t grid = want < cap ? want : cap;
     auto kfn = rowwise_kernel<TPR, VPT, COLABS, SR>;
     if constexpr (COLABS) {
-        grid = (grid + kClusterSize - 1) / kClusterSize * kClusterSize;
+        constexpr int csize = kClusterSize;
+        grid = (grid + csize - 1) / csize * csize;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)grid);
         cfg.blockDim = dim3(kThreads);
@@ -510,7 +512,7 @@ int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = kClusterSize;
+        attr[0].val.clusterDim.x = csize;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
@@ -690,6 +692,7 @@ __global__ void __launch_bounds__(kThreads) col_absmax_kernel(const XT* __restri
 struct ColwiseParams {
     const void* x;
     int64_t rows, cols, stride;
+    int64_t tiles_per_cta;  // consecutive 128-row tiles handled by one CTA
     const float* col_absmax;
     uint8_t* qt;
     void* scale;
@@ -728,14 +731,26 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_kernel(const ColwisePar
         if (blockIdx.y == 0 && rq == 0 && col + k < p.cols) store_scale(p.scale, p.scale_dtype, col + k, sc);
     }
 
-    for (int64_t rb = blockIdx.y; rb * kTileR < p.rows; rb += gridDim.y) {
+    // A CTA walks `tiles_per_cta` consecutive row tiles of its column strip, so the 128-byte output
+    // segments of one transposed row are written back to back, and the next tile's loads are in
+    // flight while the current one is quantized (register double buffer).
+    auto load_tile = [&](Vec8<XT> (&v)[4], int64_t rb) {
         const int64_t r0 = rb * kTileR + rq * 4;
-        Vec8<XT> v[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             if (r0 + j < p.rows && col < p.cols) load_vec8<XT>(v[j], x + (r0 + j) * p.stride, col, p.cols, p.vec_load != 0);
             else v[j].zero();
         }
+    };
+    const int64_t rb_begin = (int64_t)blockIdx.y * p.tiles_per_cta;
+    int64_t rb_end = rb_begin + p.tiles_per_cta;
+    const int64_t row_tiles = (p.rows + kTileR - 1) / kTileR;
+    if (rb_end > row_tiles) rb_end = row_tiles;
+    Vec8<XT> v[4], vn[4];
+    if (rb_begin < rb_end) load_tile(v, rb_begin);
+    for (int64_t rb = rb_begin; rb < rb_end; ++rb) {
+        const int64_t r0 = rb * kTileR + rq * 4;
+        if (rb + 1 < rb_end) load_tile(vn, rb + 1);
         float f[4][8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) v[j].unpack(f[j]);
@@ -785,6 +800,8 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_kernel(const ColwisePar
             }
         }
         __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = vn[j];
     }
 }
 
@@ -801,39 +818,69 @@ struct TileParams {
     int vec_load, vec_store;
 };
 
-// 1 x 128 tiles: 16 lanes per tile, 16 tiles per CTA iteration.
+// 1 x 128 tiles: 16 lanes own one tile (8 elements each). `tpr` threads (a power of two, 16..256)
+// span a row chunk of tpr*8 columns, the CTA's other threads take further rows; a work item is
+// 4 such row groups, so four 16-byte loads are in flight per thread and the next item's loads are
+// issued before the current one is reduced and quantized.
 template <typename XT, bool EXACT_DIV>
-__global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p) {
+__global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p, int tpr_log2) {
+    constexpr int ROWS = 4;
     const XT* x = reinterpret_cast<const XT*>(p.x);
     const float qmax = qmax_of(p.q_dtype);
-    const int64_t tiles_per_row = p.scale_cols;
-    const int64_t n_tiles = p.rows * tiles_per_row;
     const int l16 = threadIdx.x & 15;
     const float zero_u[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    // all 16 lanes of a group follow the same trip count so the shuffles stay converged
-    for (int64_t tbase = (int64_t)blockIdx.x * (kThreads / 16); tbase < n_tiles; tbase += (int64_t)gridDim.x * (kThreads / 16)) {
-        const int64_t tile = tbase + (threadIdx.x >> 4);
-        const bool valid = tile < n_tiles;
-        const int64_t row = valid ? tile / tiles_per_row : 0;
-        const int64_t col = (valid ? tile % tiles_per_row : 0) * 128 + l16 * 8;
-        Vec8<XT> v;
-        if (valid && col < p.cols) load_vec8<XT>(v, x + row * p.stride, col, p.cols, p.vec_load != 0);
-        else v.zero();
-        float f[8];
-        v.unpack(f);
-        float amax = 0.0f;
+    const int tpr = 1 << tpr_log2;
+    const int rpp = kThreads >> tpr_log2;            // rows per pass
+    const int sub = threadIdx.x >> tpr_log2, t = threadIdx.x & (tpr - 1);
+    const int64_t chunks = (p.cols + tpr * 8 - 1) / (tpr * 8);
+    const int64_t row_blocks = (p.rows + ROWS * rpp - 1) / (ROWS * rpp);
+    const int64_t items = row_blocks * chunks;
+
+    auto load_item = [&](Vec8<XT> (&v)[ROWS], int64_t item) {
+        const int64_t rblk = item / chunks, chunk = item - rblk * chunks;
+        const int64_t col = (chunk * tpr + t) * 8;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-        const float sc = __fdiv_rn(amax, qmax);
-        const Divider<EXACT_DIV> div(fmaxf(sc, p.eps));
-        if (valid && l16 == 0) store_scale(p.scale, p.scale_dtype, tile, sc);
-        if (valid && col < p.cols) {
-            divide8(f, div, p.q_dtype != QT_I8);
-            const uint2 bytes = pack8(f, p.q_dtype, false, zero_u);
-            store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
+        for (int j = 0; j < ROWS; ++j) {
+            const int64_t row = (rblk * ROWS + j) * rpp + sub;
+            if (row < p.rows && col < p.cols) load_vec8<XT>(v[j], x + row * p.stride, col, p.cols, p.vec_load != 0);
+            else v[j].zero();
         }
+    };
+
+    Vec8<XT> v[ROWS], vn[ROWS];
+    int64_t item = blockIdx.x;
+    if (item < items) load_item(v, item);
+    for (; item < items; item += gridDim.x) {
+        if (item + gridDim.x < items) load_item(vn, item + gridDim.x);
+        const int64_t rblk = item / chunks, chunk = item - rblk * chunks;
+        const int64_t col = (chunk * tpr + t) * 8;
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            const int64_t row = (rblk * ROWS + j) * rpp + sub;
+            float f[8];
+            v[j].unpack(f);
+            float amax = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
+            // all 16 lanes of a tile take part (out-of-range lanes hold zeros)
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+            const float sc = div_rn(amax, qmax);
+            const Divider<EXACT_DIV> div(fmaxf(sc, p.eps));
+            if (row < p.rows && col < p.cols) {
+                if (l16 == 0) store_scale(p.scale, p.scale_dtype, row * p.scale_cols + (col >> 7), sc);
+                uint2 bytes;
+                if constexpr (sizeof(XT) == 2 && !EXACT_DIV) {
+                    bytes = quantize_vec8<false>(v[j].raw, div, p.q_dtype, 0, 0, 0);
+                } else {
+                    divide8(f, div, p.q_dtype != QT_I8);
+                    bytes = pack8(f, p.q_dtype, false, zero_u);
+                }
+                store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) v[j] = vn[j];
     }
 }
 
@@ -875,10 +922,15 @@ __global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams
     for (int i = 0; i < 8; ++i) {
         const int64_t row = tile_r * 128 + r16 + 16 * i;
         if (row < p.rows && col < p.cols) {
-            float f[8];
-            v[i].unpack(f);
-            divide8(f, div, p.q_dtype != QT_I8);
-            const uint2 bytes = pack8(f, p.q_dtype, false, zero_u);
+            uint2 bytes;
+            if constexpr (sizeof(XT) == 2 && !EXACT_DIV) {
+                bytes = quantize_vec8<false>(v[i].raw, div, p.q_dtype, 0, 0, 0);
+            } else {
+                float f[8];
+                v[i].unpack(f);
+                divide8(f, div, p.q_dtype != QT_I8);
+                bytes = pack8(f, p.q_dtype, false, zero_u);
+            }
             store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
         }
     }
@@ -996,8 +1048,14 @@ extern "C" int qt_quantize_colwise_t(const void* x, int x_dtype, int64_t rows, i
     const int64_t col_tiles = (cols + kTileC - 1) / kTileC;
     int64_t row_tiles = (rows + kTileR - 1) / kTileR;
     if (row_tiles < 1) row_tiles = 1;  // rows == 0 still writes the (zero) scales
-    if (row_tiles > 65535) row_tiles = 65535;
-    dim3 grid((unsigned)col_tiles, (unsigned)row_tiles);
+    // enough CTAs for ~6 per SM, each walking up to 16 consecutive row tiles
+    int64_t per_cta = (row_tiles * col_tiles) / ((int64_t)num_sms() * 6);
+    if (per_cta < 1) per_cta = 1;
+    if (per_cta > 16) per_cta = 16;
+    int64_t groups = (row_tiles + per_cta - 1) / per_cta;
+    while (groups > 65535) { per_cta *= 2; groups = (row_tiles + per_cta - 1) / per_cta; }
+    p.tiles_per_cta = per_cta;
+    dim3 grid((unsigned)col_tiles, (unsigned)groups);
     if (x_dtype == QT_BF16 && eps >= 1e-30f) colwise_t_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(p);
     else if (x_dtype == QT_BF16) colwise_t_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(p);
     else colwise_t_kernel<float, true><<<grid, kThreads, 0, stream>>>(p);
@@ -1020,13 +1078,15 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
     p.vec_load = aligned_to(x, 16) && ((x_row_stride * esz) % 16 == 0);
     p.vec_store = aligned_to(q, 8) && (cols % 8 == 0);
     if (tile_r == 1) {
-        const int64_t n_tiles = rows * p.scale_cols;
-        const int64_t want = (n_tiles + 15) / 16;
-        const int64_t cap = (int64_t)num_sms() * 16;
-        const int grid = (int)(want < cap ? want : cap);
-        if (x_dtype == QT_BF16 && eps >= 1e-30f) tile_1x128_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(p);
-        else if (x_dtype == QT_BF16) tile_1x128_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(p);
-        else tile_1x128_kernel<float, true><<<grid, kThreads, 0, stream>>>(p);
+        int tpr_log2 = 4;  // at least one 16-lane tile group per row
+        while (tpr_log2 < 8 && ((int64_t)8 << tpr_log2) < cols) ++tpr_log2;
+        const int tpr = 1 << tpr_log2, rpp = kThreads / tpr;
+        const int64_t items = ((rows + 4 * rpp - 1) / (4 * rpp)) * ((cols + tpr * 8 - 1) / (tpr * 8));
+        const int64_t cap = (int64_t)num_sms() * 6;
+        const int grid = (int)(items < cap ? items : cap);
+        if (x_dtype == QT_BF16 && eps >= 1e-30f) tile_1x128_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(p, tpr_log2);
+        else if (x_dtype == QT_BF16) tile_1x128_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(p, tpr_log2);
+        else tile_1x128_kernel<float, true><<<grid, kThreads, 0, stream>>>(p, tpr_log2);
     } else {
         const int64_t tr = (rows + 127) / 128;
         if (tr > 65535) return fail(QT_ERR_UNSUPPORTED, "quantize_tile: more than 65535 row tiles");

@@ -244,6 +244,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     } else {
         // ===== epilogue =====
         const int ew = warp & 3;  // TMEM lane quarter this warp may read
+        // every row start and every 32-column chunk is 32-byte aligned: full-sector stores
+        const int esz = (EPI == EPI_RAW || p.scale_dtype == QT_F32) ? 4 : 2;
+        const bool wide32 = ((reinterpret_cast<uintptr_t>(p.c) & 31) == 0) && (((p.ldc * esz) & 31) == 0);
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -271,17 +274,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tcgen05_fence_after();
 
             const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(t_row + c * 32, r);
-                tmem_ld_wait();
+            // scale + store one 32-column chunk held in registers
+            auto emit = [&](const uint32_t (&r)[32], int c) {
                 const int64_t n = n0 + c * 32;
                 if (row < p.M && n < p.N) {
                     if constexpr (EPI == EPI_RAW) {
                         // int32 (or fp32 bit pattern) straight out
                         uint32_t* dst = reinterpret_cast<uint32_t*>(p.c) + row * p.ldc + n;
-                        if (n + 32 <= p.N && (p.ldc & 3) == 0) {
+                        if (n + 32 <= p.N && wide32) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8)
+                                st_global_v8(dst + j, r[j], r[j + 1], r[j + 2], r[j + 3], r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
+                        } else if (n + 32 <= p.N && (p.ldc & 3) == 0) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4)
                                 *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
@@ -298,7 +302,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         }
                         if (p.scale_dtype == QT_BF16) {
                             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + row * p.ldc + n;
-                            if (n + 32 <= p.N && (p.ldc & 7) == 0) {
+                            if (n + 32 <= p.N && wide32) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 16)
+                                    st_global_v8(dst + j, pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                                                 pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]),
+                                                 pack_bf16x2(v[j + 8], v[j + 9]), pack_bf16x2(v[j + 10], v[j + 11]),
+                                                 pack_bf16x2(v[j + 12], v[j + 13]), pack_bf16x2(v[j + 14], v[j + 15]));
+                            } else if (n + 32 <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
                                 for (int j = 0; j < 32; j += 8)
                                     *reinterpret_cast<uint4*>(dst + j) =
@@ -319,6 +330,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         }
                     }
                 }
+            };
+            // two register buffers: the TMEM load of chunk c+1 is in flight while chunk c is stored
+            uint32_t ra[32], rb[32];
+            tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c += 2) {
+                tmem_ld_wait();
+                tmem_ld_32x32(t_row + (c + 1) * 32, rb);
+                emit(ra, c);
+                tmem_ld_wait();
+                if (c + 2 < BN / 32) tmem_ld_32x32(t_row + (c + 2) * 32, ra);
+                emit(rb, c + 1);
             }
             tcgen05_fence_before();
             __syncwarp();

@@ -50,6 +50,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gemm", choices=["gemm", "train-470m", "train-1b"],
                     help="gemm: the headline quantize + scaled GEMM step; train-*: one INT8 mixed-precision Llama step (tok/s)")
+    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp"], help="train-* workloads with --gpus > 1: DDP, or FSDP2 with the INT8 weight all-gather")
     ap.add_argument("--quantize", default="mixed_precision", choices=["mixed_precision", "none", "int8_quantized_training", "bitnet"],
                     help="train-* workloads: which weight subclass the decoder's Linear layers get (none = bf16 baseline)")
     ap.add_argument("--sm-margin", type=int, default=8, help="SMs the GEMM leaves to the concurrent all-gather when --gpus > 1")
@@ -256,7 +257,13 @@ def run_train(args, rank, local_rank, world):
     with torch.device(dev):
         model = LlamaForCausalLM(cfg).bfloat16()
     quantize_model(model.model, None if args.quantize == "none" else args.quantize)
-    if world > 1:
+    if world > 1 and args.parallel == "fsdp":
+        from torch.distributed.fsdp import fully_shard
+
+        for layer in model.model.layers:   # per decoder layer, then the root (llm_pretrain.py:134-139)
+            fully_shard(layer)
+        fully_shard(model)
+    elif world > 1:
         model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
     optim = get_optimizer("other_optim.AdamWBF16SR", model, lr=1e-4, weight_decay=0.01)
     torch.manual_seed(2024 + rank)
@@ -295,7 +302,7 @@ def run_train(args, rank, local_rank, world):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": f"{args.workload}: Llama-style decoder, {n_params / 1e6:.0f}M params, quantize={args.quantize} "
                                    f"(LM head bf16), AdamWBF16SR, batch {bs} x {seq} random tokens per GPU",
-                       "parallelism": f"dp{world}"},
+                       "parallelism": (f"fsdp{world}" if (world > 1 and args.parallel == "fsdp") else f"dp{world}")},
             "loss": float(loss.detach()), "max_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
         }), flush=True)
     if world > 1:

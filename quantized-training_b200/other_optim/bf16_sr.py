@@ -56,6 +56,26 @@ class AdamWBF16SR(Optimizer):
         return loss
 
 
+_bc_cache: dict[tuple[float, float, float], tuple[float, float]] = {}
+
+
+def _bias_corrections(step: float, beta1: float, beta2: float) -> tuple[float, float]:
+    """(1 - beta1^step, sqrt(1 - beta2^step)) formed exactly as the reference does -- fp32 tensor
+    arithmetic on the host (bf16_sr.py:91-92,102) -- and remembered per step value, since every
+    parameter of a step shares them."""
+    k = (step, beta1, beta2)
+    hit = _bc_cache.get(k)
+    if hit is None:
+        if len(_bc_cache) > 64:
+            _bc_cache.clear()
+        step32 = torch.tensor(step, dtype=torch.float32)
+        bc1 = 1 - beta1**step32
+        bc2 = 1 - beta2**step32
+        hit = (float(bc1), float(bc2.sqrt()))
+        _bc_cache[k] = hit
+    return hit
+
+
 def _local(t: Tensor) -> Tensor:
     """The local shard of a DTensor (FSDP2 parameters), or the tensor itself."""
     to_local = getattr(t, "to_local", None)
@@ -74,15 +94,11 @@ def adamw(p: Tensor, grad: Tensor, step: Tensor, exp_avg: Tensor, exp_avg_sq: Te
         raise ValueError("adamw: tensors must be contiguous")
     if exp_avg.dtype is not torch.bfloat16 or exp_avg_sq.dtype is not torch.bfloat16:
         raise TypeError("adamw: optimizer states are bfloat16")
-    # scalars exactly as the reference forms them: fp32 tensors on the host (bf16_sr.py:91-92,102)
-    step32 = step.detach().to("cpu", torch.float32)
-    bc1 = 1 - beta1**step32
-    bc2 = 1 - beta2**step32
-    sqrt_bc2 = bc2.sqrt()
-    lr32 = lr.detach().to("cpu", torch.float32)
+    bc1, sqrt_bc2 = _bias_corrections(float(step), beta1, beta2)
+    lr32 = float(lr) if lr.device.type == "cpu" else float(lr.detach().to("cpu", torch.float32))
     seed, offset = key if key is not None else (next_philox_key(dev) if bf16_sr else (0, 0))
     with nv.on_device(dev):
         nv.check(nv.load().qt_adamw_bf16_sr(
             p.data_ptr(), nv.code(p.dtype), grad.data_ptr(), nv.code(grad.dtype), exp_avg.data_ptr(), exp_avg_sq.data_ptr(),
-            p.numel(), float(lr32), float(beta1), float(beta2), float(weight_decay), float(eps), float(bc1),
-            float(sqrt_bc2), int(bool(bf16_sr)), seed, offset, nv.stream_ptr(dev)))
+            p.numel(), lr32, float(beta1), float(beta2), float(weight_decay), float(eps), bc1,
+            sqrt_bc2, int(bool(bf16_sr)), seed, offset, nv.stream_ptr(dev)))

@@ -189,6 +189,26 @@ int qt_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const v
                  int64_t K, void* stream);
 
 /*
+ * Split-K forms. When the output is small and the reduction long (the grad-weight GEMMs: a
+ * [hidden, hidden] result reduced over tens of thousands of tokens) there are too few output tiles
+ * to occupy the GPU; given a workspace, these variants let several CTA pairs share one tile, each
+ * reducing a slice of K into a raw partial plane, and a finishing kernel sums the planes and applies
+ * the epilogue. int8 results stay bit-identical (integer partials add exactly); fp8 partials add in
+ * fp32. qt_gemm_workspace_bytes returns the bytes the library would like for (M, N, K): 0 means no
+ * split would be used. A null, misaligned (32 bytes) or too-small workspace falls back to the
+ * unsplit kernel. The workspace contents are undefined afterwards.
+ * No counterpart in the reference (Triton's kernels there never split K).
+ */
+int64_t qt_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int qt_int8_mm_ws(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn,
+                  int32_t* c, int64_t ldc, int64_t M, int64_t N, int64_t K, void* workspace,
+                  int64_t workspace_bytes, void* stream);
+int qt_scaled_mm_ws(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype,
+                    int64_t b_sk, int64_t b_sn, const void* scale_a, const void* scale_b,
+                    int scale_b_is_scalar, int scale_dtype, void* c, int64_t ldc, int64_t M, int64_t N,
+                    int64_t K, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * Tile-scaled GEMM: for each block kb of qk reduction elements
  *   acc[m,n] += fp32(A[m,kb] @ B[kb,n]) * scale_a[m/qm, kb] * scale_b[kb, n/qn]
  * scale_a: [ceil(M/qm), K/qk] with strides (sa_s0, sa_s1); scale_b: [K/qk, ceil(N/qn)] with strides

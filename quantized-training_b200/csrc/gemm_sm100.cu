@@ -78,6 +78,12 @@ struct GemmParams {
     int64_t sa_s0, sa_s1, sb_s0, sb_s1;
     int qm, qn;
     int* status;
+    // split-K: `splits` CTAs (or CTA pairs) share one output tile, each reducing `kb_per_split` stages
+    // and writing raw partial accumulators to ws[split][M][N] (int32 / fp32 bits); a finishing kernel
+    // sums them and applies the epilogue. splits == 1: no workspace, epilogue in this kernel.
+    int splits;
+    int kb_per_split;
+    uint32_t* ws;
 };
 
 // ---- the kernel -----------------------------------------------------------------------------
@@ -115,6 +121,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int num_kb = (int)((p.K + C::BKS - 1) / C::BKS);
     const int64_t first_tile = blockIdx.x / CG;
     const int64_t tile_step = gridDim.x / CG;
+    const int64_t num_work = num_tiles * p.splits;  // a work item is (tile, K split)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -123,7 +130,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar(b), 1);
-            mbar_init(tmem_empty_bar(b), NUM_EPI_THREADS * CG);
+            mbar_init(tmem_empty_bar(b), (NUM_EPI_THREADS / 32) * CG);  // one arrival per epilogue warp
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -149,11 +156,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        for (int64_t work = first_tile; work < num_work && ok; work += tile_step) {
+            const int64_t tile = work / p.splits;
+            const int split = (int)(work - tile * p.splits);
+            const int kb_begin = split * p.kb_per_split;
+            const int kb_end = (kb_begin + p.kb_per_split < num_kb) ? kb_begin + p.kb_per_split : num_kb;
             const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
             const int m0 = tc.m * (BM * CG) + (int)cta_rank * BM;
             const int n0 = tc.n * BN + (int)cta_rank * C::B_ROWS;
-            for (int kb = 0; kb < num_kb; ++kb) {
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
                 ok = mbar_wait(empty_bar(stage), phase ^ 1u, s_abort, p.status, 0x100 | stage);
                 if (!ok) break;
                 if (lane == 0) {
@@ -202,12 +213,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+            for (int64_t work = first_tile; work < num_work && ok; work += tile_step) {
+                const int split = (int)(work % p.splits);
+                const int kb_begin = split * p.kb_per_split;
+                const int kb_end = (kb_begin + p.kb_per_split < num_kb) ? kb_begin + p.kb_per_split : num_kb;
                 ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, s_abort, p.status, 0x200 | acc);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     ok = mbar_wait(full_bar(stage), phase, s_abort, p.status, 0x300 | stage);
                     if (!ok) break;
                     tcgen05_fence_after();
@@ -223,16 +237,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                             const uint32_t b_off = B_MN ? k * UMMA_K * 128 : (k / KPA) * C::B_ATOM_BYTES + (k % KPA) * UMMA_K;
                             const uint64_t a_desc = A_MN ? make_smem_desc(a_addr + a_off, C::BKS * 128, 1024) : make_smem_desc(a_addr + a_off, 16, 1024);
                             const uint64_t b_desc = B_MN ? make_smem_desc(b_addr + b_off, C::BKS * 128, 1024) : make_smem_desc(b_addr + b_off, 16, 1024);
-                            if constexpr (CG == 2) tcgen05_mma_pair<KIND>(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
-                            else tcgen05_mma<KIND>(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+                            if constexpr (CG == 2) tcgen05_mma_pair<KIND>(d_tmem, a_desc, b_desc, idesc, (kb > kb_begin || k != 0) ? 1u : 0u);
+                            else tcgen05_mma<KIND>(d_tmem, a_desc, b_desc, idesc, (kb > kb_begin || k != 0) ? 1u : 0u);
                         }
                         // stage reusable (in both CTAs) once these MMAs retire
                         if constexpr (CG == 2) {
                             tcgen05_commit_pair(empty_bar(stage));
-                            if (kb == num_kb - 1) tcgen05_commit_pair(tmem_full_bar(acc));
+                            if (kb == kb_end - 1) tcgen05_commit_pair(tmem_full_bar(acc));
                         } else {
                             tcgen05_commit(empty_bar(stage));
-                            if (kb == num_kb - 1) tcgen05_commit(tmem_full_bar(acc));
+                            if (kb == kb_end - 1) tcgen05_commit(tmem_full_bar(acc));
                         }
                     }
                     __syncwarp();
@@ -252,10 +266,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         bool ok = true;
         const uint32_t leader_empty0 = CG == 2 ? map_to_cta(tmem_empty_bar(0), 0) : 0u;
         const uint32_t leader_empty1 = CG == 2 ? map_to_cta(tmem_empty_bar(1), 0) : 0u;
-        for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        for (int64_t work = first_tile; work < num_work && ok; work += tile_step) {
+            const int64_t tile = work / p.splits;
+            const int split = (int)(work - tile * p.splits);
             const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
             const int64_t m0 = (int64_t)tc.m * (BM * CG) + (int64_t)cta_rank * BM, n0 = (int64_t)tc.n * BN;
             const int64_t row = m0 + ew * 32 + lane;
+            // split-K partials go out raw, one [M][N] plane per split
+            uint32_t* ws_row = (p.splits > 1 && row < p.M) ? p.ws + ((int64_t)split * p.M + row) * p.N : nullptr;
 
             float row_scale = 0.0f;
             float* cs_warp = s_colscale + (warp - 2) * BN;  // private to this warp: no cross-warp barrier
@@ -277,7 +295,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             // scale + store one 32-column chunk held in registers
             auto emit = [&](const uint32_t (&r)[32], int c) {
                 const int64_t n = n0 + c * 32;
-                if (row < p.M && n < p.N) {
+                if (ws_row != nullptr) {
+                    if (n < p.N) {
+                        uint32_t* dst = ws_row + n;
+                        if (n + 32 <= p.N && (p.N & 7) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8)
+                                st_global_v8(dst + j, r[j], r[j + 1], r[j + 2], r[j + 3], r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
+                        } else {
+                            for (int j = 0; j < 32 && n + j < p.N; ++j) dst[j] = r[j];
+                        }
+                    }
+                } else if (row < p.M && n < p.N) {
                     if constexpr (EPI == EPI_RAW) {
                         // int32 (or fp32 bit pattern) straight out
                         uint32_t* dst = reinterpret_cast<uint32_t*>(p.c) + row * p.ldc + n;
@@ -346,8 +375,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tcgen05_fence_before();
             __syncwarp();
             // the accumulator belongs to the pair: both CTAs report to the leader's barrier
-            if constexpr (CG == 2) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
-            else mbar_arrive(tmem_empty_bar(acc));
+            if (lane == 0) {
+                if constexpr (CG == 2) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+                else mbar_arrive(tmem_empty_bar(acc));
+            }
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
     }
@@ -425,8 +456,72 @@ int launch_layout(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap
     return launch_one<KIND, EPI, true, false, CG>(ta, tb, p, idesc, tiles, stream);
 }
 
+// Sums the split-K partial planes and applies the epilogue. Integer partials add exactly, so the
+// result is bit-identical to the unsplit kernel; fp8 partials add in fp32 in split order.
+template <int KIND, int EPI>
+__global__ void __launch_bounds__(256) splitk_finish_kernel(const GemmParams p) {
+    const int64_t total = p.M * p.N;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        const int64_t row = i / p.N, col = i - row * p.N;
+        float v;
+        int32_t isum = 0;
+        if constexpr (KIND == 0) {
+            for (int s = 0; s < p.splits; ++s) isum += (int32_t)p.ws[(int64_t)s * total + i];
+            v = (float)isum;
+        } else {
+            float fsum = 0.0f;
+            for (int s = 0; s < p.splits; ++s) fsum = __fadd_rn(fsum, __uint_as_float(p.ws[(int64_t)s * total + i]));
+            v = fsum;
+        }
+        if constexpr (EPI == EPI_RAW) {
+            reinterpret_cast<uint32_t*>(p.c)[row * p.ldc + col] = (KIND == 0) ? (uint32_t)isum : __float_as_uint(v);
+        } else {
+            const float rs = load_scale(p.scale_a, p.scale_dtype, row);
+            const float cs = load_scale(p.scale_b, p.scale_dtype, p.scale_b_is_scalar ? 0 : col);
+            const float o = __fmul_rn(__fmul_rn(v, rs), cs);
+            if (p.scale_dtype == QT_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[row * p.ldc + col] = __float2bfloat16_rn(o);
+            else reinterpret_cast<float*>(p.c)[row * p.ldc + col] = o;
+        }
+    }
+}
+
+template <int KIND, int EPI>
+int launch_finish(const GemmParams& p, cudaStream_t stream) {
+    const int64_t total = p.M * p.N;
+    const int64_t want = (total + 255) / 256;
+    const int64_t cap = (int64_t)num_sms() * 8;
+    splitk_finish_kernel<KIND, EPI><<<(unsigned)(want < cap ? want : cap), 256, 0, stream>>>(p);
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
+// Split K when the output has too few tiles to occupy the machine (the grad-weight GEMMs: a small
+// [K_out, N] result reduced over tens of thousands of tokens). Every split keeps at least 4 stages.
+void choose_splits(int64_t M, int64_t N, int64_t K, int cg, int* splits, int* kb_per_split) {
+    const int bks = cg == 2 ? Cfg<2>::BKS : Cfg<1>::BKS;
+    const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + BN - 1) / BN);
+    const int num_kb = (int)((K + bks - 1) / bks);
+    const int units = cg == 2 ? num_sms() / 2 : num_sms();
+    *splits = 1;
+    *kb_per_split = num_kb;
+    if (tiles * 2 > units || num_kb < 8) return;
+    int64_t s = units / tiles;
+    if (s > num_kb / 4) s = num_kb / 4;
+    if (s > 32) s = 32;
+    if (s < 2) return;
+    const int per = (int)((num_kb + s - 1) / s);
+    *kb_per_split = per;
+    *splits = (num_kb + per - 1) / per;
+}
+
+int pick_cta_group(int64_t M) {
+    int cg = g_forced_cta_group;
+    if (cg != 1 && cg != 2) cg = (M > BM) ? 2 : 1;
+    return cg;
+}
+
 int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype, int64_t b_sk,
-                  int64_t b_sn, GemmParams p, void* stream_) {
+                  int64_t b_sn, GemmParams p, void* workspace, int64_t workspace_bytes, void* stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     const int64_t M = p.M, N = p.N, K = p.K;
     QT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative dimension");
@@ -450,9 +545,23 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
 
     // A CTA pair per 256-row tile pays off once there are at least two row blocks of work per SM pair;
     // short problems keep the single-CTA form (more, smaller tiles).
-    int cg = g_forced_cta_group;
-    if (cg != 1 && cg != 2) cg = (M > BM) ? 2 : 1;
+    const int cg = pick_cta_group(M);
     const int b_rows = BN / cg;
+    p.splits = 1;
+    p.ws = nullptr;
+    {
+        const int bks = cg == 2 ? Cfg<2>::BKS : Cfg<1>::BKS;
+        p.kb_per_split = (int)((K + bks - 1) / bks);
+    }
+    if (workspace != nullptr) {
+        int splits = 1, per = 0;
+        choose_splits(M, N, K, cg, &splits, &per);
+        if (splits > 1 && workspace_bytes >= (int64_t)splits * M * N * 4 && aligned_to(workspace, 32)) {
+            p.splits = splits;
+            p.kb_per_split = per;
+            p.ws = reinterpret_cast<uint32_t*>(workspace);
+        }
+    }
 
     CUtensorMap ta, tb;
     if (a_mn) { if (int rc = make_tmap(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)a_pitch, 128, BK)) return rc; }
@@ -462,12 +571,16 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
 
     if (int rc = device_status_ptr(&p.status)) return rc;
 
-    const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + BN - 1) / BN);
+    const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + BN - 1) / BN) * p.splits;  // work items
     const uint32_t idesc = is_i8 ? make_idesc(2, 1, 1, a_mn, b_mn, BM * cg, BN)
                                  : make_idesc(1, fp8_format(a_dtype), fp8_format(b_dtype), a_mn, b_mn, BM * cg, BN);
-#define QT_DISPATCH(KIND, EPI)                                                                     \
-    return cg == 2 ? launch_layout<KIND, EPI, 2>(a_mn, b_mn, ta, tb, p, idesc, tiles, stream)      \
-                   : launch_layout<KIND, EPI, 1>(a_mn, b_mn, ta, tb, p, idesc, tiles, stream)
+#define QT_DISPATCH(KIND, EPI)                                                                               \
+    do {                                                                                                     \
+        const int rc_ = cg == 2 ? launch_layout<KIND, EPI, 2>(a_mn, b_mn, ta, tb, p, idesc, tiles, stream)   \
+                                : launch_layout<KIND, EPI, 1>(a_mn, b_mn, ta, tb, p, idesc, tiles, stream);  \
+        if (rc_ != QT_OK || p.splits == 1) return rc_;                                                       \
+        return launch_finish<KIND, EPI>(p, stream);                                                          \
+    } while (0)
     if (is_i8) {
         if (epi == EPI_RAW) { QT_DISPATCH(0, EPI_RAW); }
         if (epi == EPI_ROWCOL) { QT_DISPATCH(0, EPI_ROWCOL); }
@@ -496,20 +609,40 @@ extern "C" int qt_set_gemm_cta_group(int cta_group) {
     return QT_OK;
 }
 
-extern "C" int qt_int8_mm(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, int32_t* c,
-                          int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream) {
-    GemmParams p = {};
-    p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc;
-    return gemm_dispatch(EPI_RAW, a, QT_I8, a_sm, a_sk, b, QT_I8, b_sk, b_sn, p, stream);
+extern "C" int64_t qt_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    int splits = 1, per = 0;
+    choose_splits(M, N, K, pick_cta_group(M), &splits, &per);
+    return splits > 1 ? (int64_t)splits * M * N * 4 : 0;
 }
 
-extern "C" int qt_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype, int64_t b_sk,
-                            int64_t b_sn, const void* scale_a, const void* scale_b, int scale_b_is_scalar, int scale_dtype,
-                            void* c, int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream) {
+extern "C" int qt_int8_mm_ws(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, int32_t* c,
+                             int64_t ldc, int64_t M, int64_t N, int64_t K, void* workspace, int64_t workspace_bytes, void* stream) {
+    GemmParams p = {};
+    p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc;
+    return gemm_dispatch(EPI_RAW, a, QT_I8, a_sm, a_sk, b, QT_I8, b_sk, b_sn, p, workspace, workspace_bytes, stream);
+}
+
+extern "C" int qt_int8_mm(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, int32_t* c,
+                          int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream) {
+    return qt_int8_mm_ws(a, a_sm, a_sk, b, b_sk, b_sn, c, ldc, M, N, K, nullptr, 0, stream);
+}
+
+extern "C" int qt_scaled_mm_ws(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype, int64_t b_sk,
+                               int64_t b_sn, const void* scale_a, const void* scale_b, int scale_b_is_scalar, int scale_dtype,
+                               void* c, int64_t ldc, int64_t M, int64_t N, int64_t K, void* workspace, int64_t workspace_bytes,
+                               void* stream) {
     QT_REQUIRE(scale_dtype == QT_BF16 || scale_dtype == QT_F32, "scaled_mm: scale_dtype must be QT_BF16 or QT_F32 (got %d)", scale_dtype);
     QT_REQUIRE((scale_a && scale_b) || M == 0 || N == 0, "scaled_mm: null scale pointer");
     GemmParams p = {};
     p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc;
     p.scale_a = scale_a; p.scale_b = scale_b; p.scale_b_is_scalar = scale_b_is_scalar; p.scale_dtype = scale_dtype;
-    return gemm_dispatch(EPI_ROWCOL, a, a_dtype, a_sm, a_sk, b, b_dtype, b_sk, b_sn, p, stream);
+    return gemm_dispatch(EPI_ROWCOL, a, a_dtype, a_sm, a_sk, b, b_dtype, b_sk, b_sn, p, workspace, workspace_bytes, stream);
+}
+
+extern "C" int qt_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype, int64_t b_sk,
+                            int64_t b_sn, const void* scale_a, const void* scale_b, int scale_b_is_scalar, int scale_dtype,
+                            void* c, int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream) {
+    return qt_scaled_mm_ws(a, a_dtype, a_sm, a_sk, b, b_dtype, b_sk, b_sn, scale_a, scale_b, scale_b_is_scalar, scale_dtype, c,
+                           ldc, M, N, K, nullptr, 0, stream);
 }

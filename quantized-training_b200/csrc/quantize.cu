@@ -119,13 +119,12 @@ __device__ __forceinline__ uint32_t int8_rne(float v) {
     return __float_as_uint(__fadd_rn(v, kRoundMagic)) & 0xFFu;
 }
 
-// int8 from floor(v + u), clamp [-128, 127].
+// int8 from floor(v + u), clamp [-128, 127]. Adding 1.5 * 2^23 with round-toward-minus-infinity
+// leaves floor(w) in the low mantissa bits.
 __device__ __forceinline__ uint32_t int8_sr(float v, float u) {
     float w = __fadd_rn(v, u);
     w = fminf(fmaxf(w, -128.0f), 127.5f);
-    float r = __fsub_rn(__fadd_rn(w, kRoundMagic), kRoundMagic);  // nearest integer
-    if (r > w) r -= 1.0f;                                          // -> floor
-    return __float_as_uint(__fadd_rn(r, kRoundMagic)) & 0xFFu;
+    return __float_as_uint(__fadd_rd(w, kRoundMagic)) & 0xFFu;
 }
 
 // f[k] <- f[k] / d for 8 values. The reciprocal sequence returns +0 for -0; fp8 keeps the sign of
@@ -274,11 +273,10 @@ __device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider<f
         if constexpr (SR) {
             float u[8];
             uniforms8(u, idx, seed, offset);
-            uint32_t b[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) b[k] = int8_sr(v[k], u[k]);
-            out.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
-            out.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+            for (int k = 0; k < 8; ++k) v[k] = __fadd_rd(fminf(fmaxf(__fadd_rn(v[k], u[k]), -128.0f), 127.5f), kRoundMagic);
+            out.x = pack4_magic(v[0], v[1], v[2], v[3]);
+            out.y = pack4_magic(v[4], v[5], v[6], v[7]);
         } else {
 #pragma unroll
             for (int k = 0; k < 8; ++k) v[k] = __fadd_rn(v[k], kRoundMagic);

@@ -211,3 +211,28 @@ def test_tile_scaled_mm_rejects_unsupported_blocks():
     sb = torch.ones((4, 1), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError, match="reduction block must be 128"):
         gn_kernels.scaled_mm(A, B, sa, sb)
+
+
+@pytest.mark.parametrize("mnk", [(1024, 1024, 32768), (256, 256, 8192), (2048, 256, 16384), (300, 520, 12288), (128, 256, 8192)])
+@pytest.mark.parametrize("layout", ["A@B.T", "A.T@B"])
+def test_split_k_is_bit_exact(mnk, layout, cta_group):
+    """Small outputs with long reductions (grad-weight shapes) split K across CTAs; integer partials
+    add exactly, so int32 and scaled bf16 results equal the oracle bit for bit."""
+    M, N, K = mnk
+    assert nv.load().qt_gemm_workspace_bytes(M, N, K) >= 0
+    A, B = rand_i8((M, K), 61), rand_i8((K, N), 62)
+    g = torch.Generator().manual_seed(63)
+    sa = (torch.randn(M, 1, generator=g) / 128).bfloat16().cuda()
+    sb = (torch.randn(1, N, generator=g) / 128).bfloat16().cuda()
+    a, b = to_layout(A, B, layout)
+    acc = om.int8_mm(A.cpu().numpy(), B.cpu().numpy())
+    np.testing.assert_array_equal(gn_kernels.int8_mm(a, b).cpu().numpy(), acc)
+    want = om.round_to_bf16(((acc.astype(np.float32) * values_of(sa)).astype(np.float32) * values_of(sb)).astype(np.float32))
+    np.testing.assert_array_equal(values_of(gn_kernels.scaled_mm(a, b, sa, sb)), want)
+    assert nv.device_status() == 0
+
+
+def test_split_k_is_used_for_grad_weight_shapes():
+    assert nv.load().qt_gemm_workspace_bytes(1024, 1024, 32768) > 0
+    assert nv.load().qt_gemm_workspace_bytes(8192, 8192, 8192) == 0
+    assert nv.load().qt_gemm_workspace_bytes(32768, 1024, 1024) == 0

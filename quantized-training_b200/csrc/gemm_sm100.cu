@@ -1,10 +1,10 @@
 // tcgen05 GEMMs for sm_100a: int8 x int8 -> int32 (kind::i8) and fp8 x fp8 -> fp32 (kind::f8f6f4),
 // with raw and row/column-scaled epilogues.
 //
-// Persistent kernel, one CTA per SM, 6 warps:
+// Persistent kernel, one CTA per SM, 10 warps:
 //   warp 0      TMA producer   global -> 128B-swizzled shared-memory stages (cp.async.bulk.tensor)
 //   warp 1      MMA issuer     one elected lane issues tcgen05.mma; accumulators live in TMEM
-//   warps 2..5  epilogue       tcgen05.ld TMEM -> registers -> scale -> global
+//   warps 2..9  epilogue       tcgen05.ld TMEM -> registers -> scale -> global (two warps per lane quarter)
 // Large problems run as CTA PAIRS (2-CTA clusters, tcgen05 cta_group::2): the pair owns a 256 x 256
 // tile, each CTA stages its 128 rows of A and half of B, the leader CTA issues M=256 MMAs for both
 // and each CTA drains its own 128 accumulator rows. Small problems (M <= 128) use one CTA per
@@ -31,8 +31,9 @@ constexpr int BM = 128;      // tile rows per CTA (one TMEM lane per row)
 constexpr int BN = 256;      // tile cols (= UMMA N, one TMEM column per col)
 constexpr int BK = 128;      // reduction elements per stage (8-bit => 128 bytes = one swizzle row)
 constexpr int UMMA_K = 32;   // reduction elements per tcgen05.mma for 8-bit operands
-constexpr int NUM_THREADS = 192;
-constexpr int NUM_EPI_THREADS = 128;
+constexpr int NUM_EPI_WARPS = 8;                       // two warps per TMEM lane quarter, 128 columns each
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;   // + TMA producer warp + MMA issuer warp
+constexpr int NUM_EPI_THREADS = 32 * NUM_EPI_WARPS;
 constexpr int TMEM_COLS = 512;                         // 2 accumulators x BN fp32/int32 columns
 constexpr int MAX_STAGES = 6;
 
@@ -56,8 +57,8 @@ struct Cfg {
     static constexpr int B_ATOM_BYTES = B_ROWS * BK;
     static constexpr int B_STAGE_BYTES = B_ATOM_BYTES * KA;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int SMEM_COLSCALE_OFF = STAGES * STAGE_BYTES;      // float [4 epilogue warps][BN]
-    static constexpr int SMEM_BAR_OFF = SMEM_COLSCALE_OFF + 4 * BN * 4; // mbarriers
+    static constexpr int SMEM_COLSCALE_OFF = STAGES * STAGE_BYTES;      // float [epilogue warps][BN / 2]
+    static constexpr int SMEM_BAR_OFF = SMEM_COLSCALE_OFF + NUM_EPI_WARPS * (BN / 2) * 4; // mbarriers
     static constexpr int NUM_BARRIERS = 2 * MAX_STAGES + 4;
     static constexpr int SMEM_TMEMPTR_OFF = SMEM_BAR_OFF + NUM_BARRIERS * 8;
     static constexpr int SMEM_ABORT_OFF = SMEM_TMEMPTR_OFF + 4;
@@ -130,7 +131,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar(b), 1);
-            mbar_init(tmem_empty_bar(b), (NUM_EPI_THREADS / 32) * CG);  // one arrival per epilogue warp
+            mbar_init(tmem_empty_bar(b), NUM_EPI_WARPS * CG);  // one arrival per epilogue warp
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -257,7 +258,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
     } else {
         // ===== epilogue =====
-        const int ew = warp & 3;  // TMEM lane quarter this warp may read
+        const int ew = warp & 3;              // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;     // which 128 of the tile's 256 columns this warp drains
+        constexpr int HALF_N = BN / 2;
         // every row start and every 32-column chunk is 32-byte aligned: full-sector stores
         const int esz = (EPI == EPI_RAW || p.scale_dtype == QT_F32) ? 4 : 2;
         const bool wide32 = ((reinterpret_cast<uintptr_t>(p.c) & 31) == 0) && (((p.ldc * esz) & 31) == 0);
@@ -276,11 +279,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t* ws_row = (p.splits > 1 && row < p.M) ? p.ws + ((int64_t)split * p.M + row) * p.N : nullptr;
 
             float row_scale = 0.0f;
-            float* cs_warp = s_colscale + (warp - 2) * BN;  // private to this warp: no cross-warp barrier
+            float* cs_warp = s_colscale + (warp - 2) * HALF_N;  // private to this warp: no cross-warp barrier
             if constexpr (EPI == EPI_ROWCOL) {
                 // stage this tile's column scales as fp32
-                for (int j = lane; j < BN; j += 32) {
-                    const int64_t n = n0 + j;
+                for (int j = lane; j < HALF_N; j += 32) {
+                    const int64_t n = n0 + half * HALF_N + j;
                     cs_warp[j] = (n < p.N) ? load_scale(p.scale_b, p.scale_dtype, p.scale_b_is_scalar ? 0 : n) : 0.0f;
                 }
                 if (row < p.M) row_scale = load_scale(p.scale_a, p.scale_dtype, row);
@@ -291,10 +294,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (!ok) break;
             tcgen05_fence_after();
 
-            const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * BN);
+            const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * BN + half * HALF_N);
             // scale + store one 32-column chunk held in registers
             auto emit = [&](const uint32_t (&r)[32], int c) {
-                const int64_t n = n0 + c * 32;
+                const int64_t n = n0 + half * HALF_N + c * 32;
                 if (ws_row != nullptr) {
                     if (n < p.N) {
                         uint32_t* dst = ws_row + n;
@@ -364,12 +367,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t ra[32], rb[32];
             tmem_ld_32x32(t_row, ra);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c += 2) {
+            for (int c = 0; c < HALF_N / 32; c += 2) {
                 tmem_ld_wait();
                 tmem_ld_32x32(t_row + (c + 1) * 32, rb);
                 emit(ra, c);
                 tmem_ld_wait();
-                if (c + 2 < BN / 32) tmem_ld_32x32(t_row + (c + 2) * 32, ra);
+                if (c + 2 < HALF_N / 32) tmem_ld_32x32(t_row + (c + 2) * 32, ra);
                 emit(rb, c + 1);
             }
             tcgen05_fence_before();
@@ -514,9 +517,12 @@ void choose_splits(int64_t M, int64_t N, int64_t K, int cg, int* splits, int* kb
     *splits = (num_kb + per - 1) / per;
 }
 
-int pick_cta_group(int64_t M) {
+// CTA pairs pay off when the reduction is long enough to amortise the per-tile hand-overs across the
+// pair (measured: better from K = 2048 up, slightly worse at K = 1024) and there is more than one row
+// block.
+int pick_cta_group(int64_t M, int64_t K) {
     int cg = g_forced_cta_group;
-    if (cg != 1 && cg != 2) cg = (M > BM) ? 2 : 1;
+    if (cg != 1 && cg != 2) cg = (M > BM && K > 1024) ? 2 : 1;
     return cg;
 }
 
@@ -545,7 +551,7 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
 
     // A CTA pair per 256-row tile pays off once there are at least two row blocks of work per SM pair;
     // short problems keep the single-CTA form (more, smaller tiles).
-    const int cg = pick_cta_group(M);
+    const int cg = pick_cta_group(M, K);
     const int b_rows = BN / cg;
     p.splits = 1;
     p.ws = nullptr;
@@ -612,7 +618,7 @@ extern "C" int qt_set_gemm_cta_group(int cta_group) {
 extern "C" int64_t qt_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     int splits = 1, per = 0;
-    choose_splits(M, N, K, pick_cta_group(M), &splits, &per);
+    choose_splits(M, N, K, pick_cta_group(M, K), &splits, &per);
     return splits > 1 ? (int64_t)splits * M * N * 4 : 0;
 }
 

@@ -445,6 +445,11 @@ def main():
     sync_all()
     gc.collect()
     gc.disable()   # a collector pause between two launches would be charged to the step
+    # The barrier + synchronize above leave the GPU idle for milliseconds; two more untimed steps put it
+    # back under load so the first timed step does not pay the ramp-up.
+    for _ in range(2):
+        step(A, W)
+    warm_steps += 2
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):

@@ -333,21 +333,15 @@ rowwise_kernel(const RowwiseParams p) {
         __syncthreads();
     }
 
+    // the host only takes this kernel when cols is a multiple of 8 and q is 8-byte aligned, so every
+    // vector is either wholly inside the row or wholly outside it
     auto load_row = [&](uint4 (&v)[VPT], int64_t row) {
         const bool valid = row < p.rows;
         const __nv_bfloat16* xrow = x + (valid ? row : 0) * p.stride;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const int64_t col = ((int64_t)i * TPR + t) * 8;
-            if (valid && col + 8 <= p.cols) {
-                v[i] = *reinterpret_cast<const uint4*>(xrow + col);
-            } else if (valid && col < p.cols) {
-                Vec8<__nv_bfloat16> tmp;
-                load_vec8<__nv_bfloat16>(tmp, xrow, col, p.cols, false);
-                v[i] = tmp.raw;
-            } else {
-                v[i] = make_uint4(0, 0, 0, 0);
-            }
+            const int col = (i * TPR + t) * 8;
+            v[i] = (valid && col < p.cols) ? *reinterpret_cast<const uint4*>(xrow + col) : make_uint4(0, 0, 0, 0);
         }
     };
 
@@ -387,13 +381,13 @@ rowwise_kernel(const RowwiseParams p) {
         const Divider<false> div(fmaxf(scale, p.eps));
         if (valid && t == 0) store_scale(p.scale, p.scale_dtype, row, scale);
 
+        uint8_t* qrow = p.q + row * p.cols;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const int64_t col = ((int64_t)i * TPR + t) * 8;
+            const int col = (i * TPR + t) * 8;
             if (valid && col < p.cols) {
-                const int64_t idx = row * p.cols + col;
-                const uint2 bytes = quantize_vec8<SR>(cur[i], div, p.q_dtype, idx, p.seed, p.offset);
-                store_bytes8(p.q, idx, p.cols - col, bytes, p.vec_store != 0);
+                const uint2 bytes = quantize_vec8<SR>(cur[i], div, p.q_dtype, SR ? row * p.cols + col : 0, p.seed, p.offset);
+                *reinterpret_cast<uint2*>(qrow + col) = bytes;
             }
         }
 
@@ -546,11 +540,11 @@ int launch_rowwise_generic(const RowwiseParams& p, cudaStream_t stream) {
     return QT_OK;
 }
 
-// Fast path: bf16 rows, 16-byte aligned, that fit the register-resident kernel, with a positive
+// Fast path: bf16 rows, 16-byte aligned, a multiple of 8 columns, that fit the register-resident kernel, with a positive
 // eps (the unclamped rounding relies on max(scale, eps) not being denormal). Everything else --
 // fp32 input, odd alignment, very wide rows -- takes the generic two-pass kernel.
 int launch_rowwise(const RowwiseParams& p, int x_dtype, bool colabs, cudaStream_t stream) {
-    const bool fast = x_dtype == QT_BF16 && p.vec_load && p.eps >= 1e-30f && p.cols <= (colabs ? 16384 : 32768);
+    const bool fast = x_dtype == QT_BF16 && p.vec_load && p.vec_store && p.eps >= 1e-30f && p.cols <= (colabs ? 16384 : 32768);
     if (fast) {
         if (colabs) return p.stochastic ? launch_rowwise_bf16<true, true>(p, stream) : launch_rowwise_bf16<true, false>(p, stream);
         return p.stochastic ? launch_rowwise_bf16<false, true>(p, stream) : launch_rowwise_bf16<false, false>(p, stream);

@@ -192,6 +192,12 @@ def cpu_reference_step(A, B):
 def time_cpu_path(size: int, steps: int, warmup: int):
     """Time the reference's CPU form of the path (torch eager quantize + torch._int_mm + scale) with
     all host threads. Returns (TOPS, threads, seconds per step)."""
+    # use every host core (torchrun pins OMP_NUM_THREADS=1 in its workers)
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores))
     torch.manual_seed(2024)
     A = torch.randn(size, size).bfloat16()
     B = (torch.randn(size, size) * 0.02).bfloat16()
@@ -538,7 +544,7 @@ def main():
     traffic = 456.2e6 if S == 8192 else None
 
     cpu_baseline = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:
         tops, threads, dt = time_cpu_path(S, 3 if S >= 8192 else 5, 1)
         cpu_baseline = {"value": tops, "unit": UNIT, "cores": threads, "kind": "port",
                         "sample": f"3 full passes of the {S}^3 workload after 1 warm-up ({dt:.2f} s each), torch eager quantize + torch._int_mm on the host"}

@@ -541,7 +541,7 @@ def main():
     achieved = flops / (gemm_ms * 1e-3) / 1e12
     # dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of this kernel, from the ncu
     # capture summarised in profiles/gemm_scaled_int8_8192.md
-    traffic = 456.2e6 if S == 8192 else None
+    traffic = 461.3e6 if S == 8192 else None
 
     cpu_baseline = None
     if not args.no_cpu_baseline and world == 1:

@@ -3,10 +3,10 @@
 //     acc[m,n] += fp32(partial[m,n]) * scale_a[m / qm, kb] * scale_b[kb, n / qn]
 // which is the loop of the reference's _tile_scaled_mm_kernel (kernels/gn_kernels/triton_mm.py:314-331).
 //
-// One persistent CTA per SM owns 128 x 128 tiles; 6 warps: TMA producer, MMA issuer, four promotion /
-// epilogue warps that keep the fp32 accumulator (128 values per thread: one row, 128 columns) in
-// registers. TMEM holds four 128-column partial buffers, so the tensor core runs up to four K blocks
-// ahead of the promotion. The promotion (one convert + one fused multiply-add per element per K
+// One persistent CTA per SM owns 128 x 256 tiles; 10 warps: TMA producer, MMA issuer, eight promotion /
+// epilogue warps that keep the fp32 accumulator (128 values per thread: one row, 128 columns, i.e. one
+// scale block of B) in registers. TMEM holds two 256-column partial buffers, so the tensor core works
+// on the next K block while the current one is promoted. The promotion (one convert + one fused multiply-add per element per K
 // block) is what bounds this kernel, not the tensor pipe. All waits are bounded.
 #include "tcgen05.cuh"
 
@@ -16,12 +16,13 @@ namespace {
 
 using namespace tc;
 
-constexpr int TBM = 128, TBN = 128, TBK = 128;
+constexpr int TBM = 128, TBN = 256, TBK = 128;
 constexpr int T_UMMA_K = 32;
-constexpr int T_STAGES = 6;
+constexpr int T_STAGES = 4;
 constexpr int T_A_BYTES = TBM * TBK, T_B_BYTES = TBN * TBK, T_STAGE_BYTES = T_A_BYTES + T_B_BYTES;
-constexpr int T_THREADS = 192;
-constexpr int T_BUFS = 4;                       // TMEM partial buffers of TBN columns
+constexpr int T_EPI_WARPS = 8;                   // two promotion warps per TMEM lane quarter, 128 columns each
+constexpr int T_THREADS = 64 + 32 * T_EPI_WARPS;
+constexpr int T_BUFS = 2;                       // TMEM partial buffers of TBN columns
 constexpr int T_TMEM_COLS = T_BUFS * TBN;       // 512
 constexpr int T_SMEM_BAR_OFF = T_STAGES * T_STAGE_BYTES;
 constexpr int T_NUM_BARRIERS = 2 * T_STAGES + 2 * T_BUFS;
@@ -63,7 +64,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < T_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < T_BUFS; ++b) { mbar_init(part_full_bar(b), 1); mbar_init(part_empty_bar(b), 128); }
+        for (int b = 0; b < T_BUFS; ++b) { mbar_init(part_full_bar(b), 1); mbar_init(part_empty_bar(b), T_EPI_WARPS); }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -94,8 +95,12 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     mbar_expect_tx(full_bar(stage), T_STAGE_BYTES);
                     if constexpr (A_MN) tma_load_2d(a_dst, &tmap_a, full_bar(stage), m0, k0);
                     else tma_load_2d(a_dst, &tmap_a, full_bar(stage), k0, m0);
-                    if constexpr (B_MN) tma_load_2d(b_dst, &tmap_b, full_bar(stage), n0, k0);
-                    else tma_load_2d(b_dst, &tmap_b, full_bar(stage), k0, n0);
+                    if constexpr (B_MN) {
+                        tma_load_2d(b_dst, &tmap_b, full_bar(stage), n0, k0);
+                        tma_load_2d(b_dst + TBK * 128, &tmap_b, full_bar(stage), n0 + 128, k0);
+                    } else {
+                        tma_load_2d(b_dst, &tmap_b, full_bar(stage), k0, n0);
+                    }
                 }
                 __syncwarp();
                 if (++stage == T_STAGES) { stage = 0; phase ^= 1u; }
@@ -137,8 +142,10 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
         }
     } else {
-        // ===== promotion + epilogue: thread = one row, 128 fp32 accumulators in registers =====
+        // ===== promotion + epilogue: thread = one row x 64 columns, fp32 accumulators in registers =====
         const int ew = warp & 3;
+        const int half = (warp - 2) >> 2;
+        constexpr int HN = TBN / 2;
         int buf = 0;
         uint32_t buf_phase = 0;
         bool ok = true;
@@ -147,10 +154,10 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int64_t m0 = (int64_t)tc_.m * TBM, n0 = (int64_t)tc_.n * TBN;
             const int64_t row = m0 + ew * 32 + lane;
             const int64_t sa_row = (row < p.M ? row : p.M - 1) / p.qm;
-            const int64_t sb_col = n0 / p.qn;
-            float acc[TBN];
+            const int64_t sb_col = (n0 + half * HN < p.N ? n0 + half * HN : n0) / p.qn;
+            float acc[HN];
 #pragma unroll
-            for (int j = 0; j < TBN; ++j) acc[j] = 0.0f;
+            for (int j = 0; j < HN; ++j) acc[j] = 0.0f;
             // scale of K block 0, then always one block ahead
             float s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0) * load_scale(p.scale_b, p.scale_dtype, sb_col * p.sb_s1);
             for (int kb = 0; kb < num_kb; ++kb) {
@@ -161,43 +168,57 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 ok = mbar_wait(part_full_bar(buf), buf_phase, s_abort, p.status, 0x800 | buf);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(buf * TBN);
+                const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(buf * TBN + half * HN);
+                // 16-column chunks through two register buffers: the next TMEM load is in flight while
+                // the current chunk is promoted. For int8 the partial of one 128-element K block is below
+                // 2^22 in magnitude, so adding it to the bit pattern of 1.5 * 2^23 and subtracting that
+                // constant converts it exactly without the (slower) integer-to-float instruction.
+                auto promote = [&](const uint32_t (&r)[16], int c) {
 #pragma unroll
-                for (int c = 0; c < TBN / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(t_row + c * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float x = (KIND == 0) ? (float)(int32_t)r[j] : __uint_as_float(r[j]);
-                        acc[c * 32 + j] = __fmaf_rn(x, s, acc[c * 32 + j]);
+                    for (int j = 0; j < 16; ++j) {
+                        float x;
+                        if constexpr (KIND == 0) x = __fsub_rn(__uint_as_float(r[j] + 0x4B400000u), 12582912.0f);
+                        else x = __uint_as_float(r[j]);
+                        acc[c * 16 + j] = __fmaf_rn(x, s, acc[c * 16 + j]);
                     }
+                };
+                uint32_t ra[16], rb[16];
+                tmem_ld_32x16(t_row, ra);
+#pragma unroll
+                for (int c = 0; c < HN / 16; c += 2) {
+                    tmem_ld_wait();
+                    tmem_ld_32x16(t_row + (c + 1) * 16, rb);
+                    promote(ra, c);
+                    tmem_ld_wait();
+                    if (c + 2 < HN / 16) tmem_ld_32x16(t_row + (c + 2) * 16, ra);
+                    promote(rb, c + 1);
                 }
                 tcgen05_fence_before();
                 __syncwarp();
-                mbar_arrive(part_empty_bar(buf));
+                if (lane == 0) mbar_arrive(part_empty_bar(buf));
                 if (++buf == T_BUFS) { buf = 0; buf_phase ^= 1u; }
             }
             if (!ok) break;
             if (row < p.M) {
+                const int64_t nh = n0 + half * HN;
                 if (p.scale_dtype == QT_BF16) {
-                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + row * p.ldc + n0;
-                    if (n0 + TBN <= p.N && (p.ldc & 7) == 0) {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + row * p.ldc + nh;
+                    if (nh + HN <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
-                        for (int j = 0; j < TBN; j += 8)
+                        for (int j = 0; j < HN; j += 8)
                             *reinterpret_cast<uint4*>(dst + j) =
                                 make_uint4(pack_bf16x2(acc[j], acc[j + 1]), pack_bf16x2(acc[j + 2], acc[j + 3]),
                                            pack_bf16x2(acc[j + 4], acc[j + 5]), pack_bf16x2(acc[j + 6], acc[j + 7]));
                     } else {
 #pragma unroll
-                        for (int j = 0; j < TBN; ++j)
-                            if (n0 + j < p.N) dst[j] = __float2bfloat16_rn(acc[j]);
+                        for (int j = 0; j < HN; ++j)
+                            if (nh + j < p.N) dst[j] = __float2bfloat16_rn(acc[j]);
                     }
                 } else {
-                    float* dst = reinterpret_cast<float*>(p.c) + row * p.ldc + n0;
+                    float* dst = reinterpret_cast<float*>(p.c) + row * p.ldc + nh;
 #pragma unroll
-                    for (int j = 0; j < TBN; ++j)
-                        if (n0 + j < p.N) dst[j] = acc[j];
+                    for (int j = 0; j < HN; ++j)
+                        if (nh + j < p.N) dst[j] = acc[j];
                 }
             }
         }
@@ -257,7 +278,7 @@ extern "C" int qt_tile_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64
     QT_REQUIRE(a && b && c && scale_a && scale_b, "tile_scaled_mm: null pointer");
     if (qk != TBK || K % TBK != 0 || K == 0)
         return fail(QT_ERR_UNSUPPORTED, "tile_scaled_mm: the reduction block must be 128 and K a positive multiple of it (qk=%d, K=%lld)", qk, (long long)K);
-    if (qm < 1 || qn < TBN || qn % TBN != 0)
+    if (qm < 1 || qn < 128 || qn % 128 != 0)
         return fail(QT_ERR_UNSUPPORTED, "tile_scaled_mm: qm must be >= 1 and qn a multiple of 128 (qm=%d, qn=%d)", qm, qn);
     QT_REQUIRE((a_sk == 1) != (a_sm == 1) || M == 1, "tile_scaled_mm: exactly one stride of A must be 1");
     QT_REQUIRE((b_sk == 1) != (b_sn == 1) || N == 1, "tile_scaled_mm: exactly one stride of B must be 1");

@@ -268,6 +268,20 @@ int qt_adamw_bf16_sr(void* p, int p_dtype, const void* grad, int grad_dtype, voi
                      float sqrt_bias_correction2, int stochastic, uint64_t seed, uint64_t offset,
                      void* stream);
 
+/*
+ * The same update for n_tensors parameter tensors in as few launches as possible (a launch covers up
+ * to 48 tensors / 320 blocks of 32768 elements). p, grad, exp_avg, exp_avg_sq and numel are HOST
+ * arrays of n_tensors device pointers / lengths; all tensors share the dtypes and the scalars (the
+ * reference steps every parameter of a group with the same hyper-parameters, other_optim/
+ * bf16_sr.py:37-74, and launches one compiled kernel per parameter). Tensor t gets exactly the result
+ * of qt_adamw_bf16_sr(..., seed, offset + t, ...). Tensors of length 0 are skipped.
+ */
+int qt_adamw_bf16_sr_multi(int n_tensors, void* const* p, const void* const* grad, void* const* exp_avg,
+                           void* const* exp_avg_sq, const int64_t* numel, int p_dtype, int grad_dtype,
+                           float lr, double beta1, double beta2, float weight_decay, float eps,
+                           float bias_correction1, float sqrt_bias_correction2, int stochastic,
+                           uint64_t seed, uint64_t offset, void* stream);
+
 /* ---- self-tests ------------------------------------------------------------------------------ */
 
 /*

@@ -53,12 +53,12 @@ __device__ __forceinline__ uint32_t sr_bf16_bits(float x, uint32_t rand16) {
     return (__float_as_uint(x) + (rand16 & 0xFFFFu)) >> 16;
 }
 
+// Elements [4q, 4q+4) of one tensor (fewer at the tail). The tensor's pointers and length are in `a`.
 template <typename PT, typename GT>
-__global__ void __launch_bounds__(kThreads) adamw_kernel(const AdamParams a) {
+__device__ __forceinline__ void adam_quad(const AdamParams& a, int64_t q) {
     PT* p = reinterpret_cast<PT*>(a.p);
     const GT* g = reinterpret_cast<const GT*>(a.g);
-    const int64_t n4 = (a.n + 3) / 4;
-    for (int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x; q < n4; q += (int64_t)gridDim.x * kThreads) {
+    {
         const int64_t i0 = q * 4;
         Philox4 r = {0, 0, 0, 0};
         if (a.stochastic) r = philox4x32_10((uint64_t)q, a.offset, a.seed);
@@ -130,6 +130,45 @@ __global__ void __launch_bounds__(kThreads) adamw_kernel(const AdamParams a) {
     }
 }
 
+template <typename PT, typename GT>
+__global__ void __launch_bounds__(kThreads) adamw_kernel(const AdamParams a) {
+    const int64_t n4 = (a.n + 3) / 4;
+    for (int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x; q < n4; q += (int64_t)gridDim.x * kThreads)
+        adam_quad<PT, GT>(a, q);
+}
+
+// ---- multi-tensor form: one launch updates many parameter tensors ---------------------------------
+// A launch carries a table of up to kMaxTensors tensors and kMaxBlocks blocks; block b updates chunk
+// block_chunk[b] (kChunk elements) of tensor block_tensor[b]. Tensor t draws its random bits with
+// Philox offset `offset + t`, i.e. exactly what a single-tensor call with that offset draws.
+
+constexpr int kMaxTensors = 48;
+constexpr int kMaxBlocks = 320;
+constexpr int kChunk = 32768;   // elements per block (458 KB of traffic for bf16 p and g)
+
+struct MultiTable {
+    void* p[kMaxTensors];
+    const void* g[kMaxTensors];
+    __nv_bfloat16* m[kMaxTensors];
+    __nv_bfloat16* v[kMaxTensors];
+    int64_t numel[kMaxTensors];
+    uint32_t tensor_index[kMaxTensors];
+    int32_t block_chunk[kMaxBlocks];
+    uint8_t block_tensor[kMaxBlocks];
+};
+
+template <typename PT, typename GT>
+__global__ void __launch_bounds__(kThreads) adamw_multi_kernel(const __grid_constant__ MultiTable tab, const AdamParams proto) {
+    const int t = tab.block_tensor[blockIdx.x];
+    AdamParams a = proto;
+    a.p = tab.p[t]; a.g = tab.g[t]; a.m = tab.m[t]; a.v = tab.v[t]; a.n = tab.numel[t];
+    a.offset = proto.offset + tab.tensor_index[t];
+    const int64_t q_begin = (int64_t)tab.block_chunk[blockIdx.x] * (kChunk / 4);
+    const int64_t n4 = (a.n + 3) / 4;
+    const int64_t q_end = q_begin + kChunk / 4 < n4 ? q_begin + kChunk / 4 : n4;
+    for (int64_t q = q_begin + threadIdx.x; q < q_end; q += kThreads) adam_quad<PT, GT>(a, q);
+}
+
 }  // namespace
 
 }  // namespace qt
@@ -166,4 +205,59 @@ extern "C" int qt_adamw_bf16_sr(void* p, int p_dtype, const void* grad, int grad
     else adamw_kernel<float, float><<<grid, kThreads, 0, stream>>>(a);
     QT_CUDA_CHECK(cudaGetLastError());
     return QT_OK;
+}
+
+extern "C" int qt_adamw_bf16_sr_multi(int n_tensors, void* const* p, const void* const* grad, void* const* exp_avg,
+                                      void* const* exp_avg_sq, const int64_t* numel, int p_dtype, int grad_dtype, float lr,
+                                      double beta1, double beta2, float weight_decay, float eps, float bias_correction1,
+                                      float sqrt_bias_correction2, int stochastic, uint64_t seed, uint64_t offset,
+                                      void* stream_) {
+    QT_REQUIRE(n_tensors >= 0, "adamw_multi: negative tensor count");
+    QT_REQUIRE(p_dtype == QT_BF16 || p_dtype == QT_F32, "adamw_multi: parameter dtype must be QT_BF16 or QT_F32 (got %d)", p_dtype);
+    QT_REQUIRE(grad_dtype == QT_BF16 || grad_dtype == QT_F32, "adamw_multi: gradient dtype must be QT_BF16 or QT_F32 (got %d)", grad_dtype);
+    QT_REQUIRE(!stochastic || p_dtype == QT_BF16, "adamw_multi: stochastic rounding applies to bf16 parameters only");
+    if (n_tensors == 0) return QT_OK;
+    QT_REQUIRE(p && grad && exp_avg && exp_avg_sq && numel, "adamw_multi: null table");
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    AdamParams a = {};
+    a.lr = lr; a.lr_wd = lr * weight_decay;
+    a.w1 = (float)(1.0 - beta1); a.w2 = (float)(1.0 - beta2);
+    a.bc1 = bias_correction1; a.sqrt_bc2 = sqrt_bias_correction2; a.eps = eps;
+    a.stochastic = stochastic; a.seed = seed; a.offset = offset;
+
+    MultiTable tab;
+    int nt = 0, nb = 0;
+    auto flush = [&]() -> int {
+        if (nb == 0) { nt = 0; return QT_OK; }
+        if (p_dtype == QT_BF16 && grad_dtype == QT_BF16) adamw_multi_kernel<__nv_bfloat16, __nv_bfloat16><<<nb, kThreads, 0, stream>>>(tab, a);
+        else if (p_dtype == QT_BF16) adamw_multi_kernel<__nv_bfloat16, float><<<nb, kThreads, 0, stream>>>(tab, a);
+        else if (grad_dtype == QT_BF16) adamw_multi_kernel<float, __nv_bfloat16><<<nb, kThreads, 0, stream>>>(tab, a);
+        else adamw_multi_kernel<float, float><<<nb, kThreads, 0, stream>>>(tab, a);
+        QT_CUDA_CHECK(cudaGetLastError());
+        nt = 0; nb = 0;
+        return QT_OK;
+    };
+    for (int t = 0; t < n_tensors; ++t) {
+        QT_REQUIRE(numel[t] >= 0, "adamw_multi: negative numel for tensor %d", t);
+        if (numel[t] == 0) continue;
+        QT_REQUIRE(p[t] && grad[t] && exp_avg[t] && exp_avg_sq[t], "adamw_multi: null pointer for tensor %d", t);
+        QT_REQUIRE(aligned_to(p[t], 16) && aligned_to(grad[t], 16) && aligned_to(exp_avg[t], 8) && aligned_to(exp_avg_sq[t], 8),
+                   "adamw_multi: tensor %d must be 16-byte aligned", t);
+        const int64_t chunks = (numel[t] + kChunk - 1) / kChunk;
+        int64_t c = 0;
+        while (c < chunks) {
+            if (nt == kMaxTensors || nb == kMaxBlocks) { if (int rc = flush()) return rc; }
+            // (re-)enter this tensor into the current table
+            const int slot = nt++;
+            tab.p[slot] = p[t]; tab.g[slot] = grad[t];
+            tab.m[slot] = reinterpret_cast<__nv_bfloat16*>(exp_avg[t]); tab.v[slot] = reinterpret_cast<__nv_bfloat16*>(exp_avg_sq[t]);
+            tab.numel[slot] = numel[t]; tab.tensor_index[slot] = (uint32_t)t;
+            while (c < chunks && nb < kMaxBlocks) {
+                tab.block_tensor[nb] = (uint8_t)slot;
+                tab.block_chunk[nb] = (int32_t)c;
+                ++nb; ++c;
+            }
+        }
+    }
+    return flush();
 }

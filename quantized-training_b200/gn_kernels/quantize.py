@@ -6,6 +6,7 @@ exist so the quantize step is one HBM pass instead of a chain of eager / inducto
 from __future__ import annotations
 
 import itertools
+import threading
 
 import torch
 from torch import Tensor
@@ -15,6 +16,7 @@ from ._lib import lib, lib_ops
 
 _F8 = (torch.float8_e4m3fn, torch.float8_e5m2)
 _philox_calls = itertools.count(1)
+_philox_lock = threading.Lock()
 
 
 def next_philox_key(device: torch.device) -> tuple[int, int]:
@@ -22,7 +24,19 @@ def next_philox_key(device: torch.device) -> tuple[int, int]:
     that device, the offset counts launches in this process, so runs are reproducible."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     seed = torch.cuda.default_generators[idx].initial_seed() & 0xFFFFFFFFFFFFFFFF
-    return seed, next(_philox_calls)
+    with _philox_lock:
+        return seed, next(_philox_calls)
+
+
+def reserve_philox_keys(device: torch.device, n: int) -> tuple[int, int]:
+    """(seed, first offset) of `n` consecutive launch offsets, for one call that stands for n launches."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    seed = torch.cuda.default_generators[idx].initial_seed() & 0xFFFFFFFFFFFFFFFF
+    with _philox_lock:
+        first = next(_philox_calls)
+        for _ in range(n - 1):
+            next(_philox_calls)
+    return seed, first
 
 
 def _rows_view(x: Tensor) -> Tensor:

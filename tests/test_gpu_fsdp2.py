@@ -24,7 +24,7 @@ def _build(seed=0):
     ).bfloat16()
 
 
-def _worker(rank: int, world: int, port: int, out_path: str):
+def _worker(rank: int, world: int, port: int, out_path: str, mode: str = "int8_mp"):
     import sys
     from pathlib import Path
 
@@ -33,34 +33,35 @@ def _worker(rank: int, world: int, port: int, out_path: str):
     import torch.distributed as dist
     from torch.distributed.fsdp import fully_shard
 
-    from subclasses import MixedPrecisionConfig, convert_mixed_precision
-    from subclasses.mixed_precision import Int8RowScaledLinearWeight
+    from subclasses import MixedPrecisionConfig, convert_bitnet, convert_mixed_precision
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         model = _build().cuda()
-        convert_mixed_precision(model, config=MixedPrecisionConfig())
+        if mode == "bitnet":
+            convert_bitnet(model)
+        else:
+            convert_mixed_precision(model, config=MixedPrecisionConfig())
         for layer in (model[0], model[2]):
             fully_shard(layer)
         fully_shard(model)
         g = torch.Generator().manual_seed(100)              # same batch on both ranks: grads must agree
         x = torch.randn(64, 256, generator=g).bfloat16().cuda().requires_grad_()
-        seen = []
-        hook = model[2].register_forward_pre_hook(lambda m, a: seen.append(type(m.weight.data if not hasattr(m.weight, "_local_tensor") else m.weight._local_tensor)))
         y = model(x)
         gathered_types = []
         for layer in (model[0], model[2]):
             state = layer._get_fsdp_state()
             for fp in state._fsdp_param_group.fsdp_params:
                 gathered_types.append([t.dtype for t in fp.all_gather_outputs])
+        gathered_shapes = [[tuple(t.shape) for t in fp.all_gather_outputs]
+                           for layer in (model[0], model[2]) for fp in layer._get_fsdp_state()._fsdp_param_group.fsdp_params]
         y.float().square().mean().backward()
-        hook.remove()
         grads = [p.grad.full_tensor().float().cpu() if hasattr(p.grad, "full_tensor") else p.grad.float().cpu() for p in model.parameters()]
         if rank == 0:
             torch.save({"y": y.detach().float().cpu(), "gx": x.grad.float().cpu(), "grads": grads,
-                        "gathered": [[str(d) for d in ds] for ds in gathered_types]}, out_path)
+                        "gathered": [[str(d) for d in ds] for ds in gathered_types], "gathered_shapes": gathered_shapes}, out_path)
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -90,3 +91,34 @@ def test_fsdp2_int8_all_gather_matches_unsharded(tmp_path):
         assert (a - b).norm() / b.norm() < 2e-2
     # grad_input uses the gathered int8 weight (scale folded into dY): within quantization error
     assert (got["gx"] - x.grad.float().cpu()).norm() / x.grad.float().norm().cpu() < 3e-2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fsdp2_bitnet_2bit_all_gather_matches_unsharded(tmp_path):
+    """BitNet weights cross NVLink as packed 2-bit ternaries (4 per byte); the tensor-wide abs-mean is
+    the average of the two equal-size shards' abs-means, equal to the unsharded one up to fp32 rounding,
+    so the forward agrees within a few weights flipping between ternary levels."""
+    import torch.multiprocessing as mp
+
+    from subclasses import convert_bitnet
+
+    out_path = str(tmp_path / "fsdp_bitnet.pt")
+    mp.spawn(_worker, args=(2, _free_port(), out_path, "bitnet"), nprocs=2, join=True)
+    got = torch.load(out_path)
+    assert all(ds == ["torch.int8"] for ds in got["gathered"]), got["gathered"]
+    # 512x256 and 384x512 weights, four ternaries per byte
+    assert sorted(int(torch.tensor(s[0]).prod()) for s in got["gathered_shapes"]) == sorted([512 * 256 // 4, 384 * 512 // 4])
+
+    model = _build().cuda()
+    convert_bitnet(model)
+    g = torch.Generator().manual_seed(100)
+    x = torch.randn(64, 256, generator=g).bfloat16().cuda().requires_grad_()
+    y = model(x)
+    y.float().square().mean().backward()
+    yr = y.detach().float().cpu()
+    assert (got["y"] - yr).norm() / yr.norm() < 2e-2
+    for a, p in zip(got["grads"], model.parameters()):
+        b = p.grad.float().cpu()
+        assert (a - b).norm() / b.norm() < 3e-2
+    gx = x.grad.float().cpu()
+    assert (got["gx"] - gx).norm() / gx.norm() < 3e-2

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 import gn_kernels  # noqa: E402
 from other_optim import AdamWBF16SR  # noqa: E402
-from other_optim.bf16_sr import adamw  # noqa: E402
+from other_optim.bf16_sr import adamw, adamw_multi  # noqa: E402
 from subclasses import (  # noqa: E402
     BitNetTrainingLinearWeight,
     Int8LinearWeight,
@@ -247,6 +247,29 @@ def test_adamw_stochastic_rounding_is_unbiased():
     # the fp32 update is 1 - 1e-3 (Adam's first step moves by lr); bf16 spacing near 1 is 2^-7 below
     assert abs(mean - (1 - 1e-3)) < 2e-5
     assert len(torch.unique(outs[0])) == 2
+
+
+@pytest.mark.parametrize("p_dtype,g_dtype,sr", [(torch.bfloat16, torch.bfloat16, True), (torch.bfloat16, torch.float32, True),
+                                                (torch.float32, torch.bfloat16, False), (torch.float32, torch.float32, False)])
+def test_adamw_multi_equals_per_tensor_calls(p_dtype, g_dtype, sr):
+    # sizes around the kernel's chunk (32768 elements) and table limits (48 tensors, 320 blocks per launch),
+    # ragged tails, an empty tensor
+    sizes = [1, 3, 4, 7, 0, 32768, 32769, 65536 + 5, 1000, 4096 * 4096 + 8] + [257 + 4 * i for i in range(60)]
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    mk = lambda n, dt, scale=1.0: (torch.randn(n, device="cuda", generator=gen) * scale).to(dt)  # noqa: E731
+    ps = [mk(n, p_dtype) for n in sizes]
+    gs = [mk(n, g_dtype, 0.1) for n in sizes]
+    ms = [mk(n, torch.bfloat16, 0.01) for n in sizes]
+    vs = [mk(n, torch.bfloat16, 0.01).abs() for n in sizes]
+    one = [[t.clone() for t in ts] for ts in (ps, ms, vs)]
+    hyper = (torch.tensor(2e-3), 0.9, 0.95, 0.1, 1e-8, sr)
+    adamw_multi(ps, gs, 3.0, ms, vs, *hyper, key=(77, 1000))
+    for t, (p, g, m, v) in enumerate(zip(one[0], gs, one[1], one[2])):
+        if p.numel():
+            adamw(p, g, torch.tensor(3.0), m, v, *hyper, key=(77, 1000 + t))
+    for got, want in zip(ps + ms + vs, one[0] + one[1] + one[2]):
+        assert torch.equal(got, want)
+    assert not torch.equal(ps[5], mk(sizes[5], p_dtype))  # the update did something
 
 
 def test_optimizer_class_trains_a_converted_model():

@@ -269,6 +269,23 @@ int qt_adamw_bf16_sr(void* p, int p_dtype, const void* grad, int grad_dtype, voi
                      void* stream);
 
 /*
+ * In-place optimizer update of an INT8 weight [rows, cols] with bf16 per-row scales [rows]: what the
+ * reference does in three eager steps -- de-quantize, add_/addcdiv_, re-quantize row-wise with
+ * stochastic rounding and copy back (subclasses/int8.py:114-133) -- in one pass that reads q, scale and
+ * the operands once and overwrites q and scale:
+ *   w = bf16(float(q) * scale[row])
+ *   mode 0: y = bf16(w + value * t1)              (add_(t1, alpha=value))
+ *   mode 1: y = bf16(w + value * (t1 / t2))       (addcdiv_(t1, t2, value=value))
+ *   q, scale <- stochastic row-wise INT8 quantization of y, random bits of (seed, offset) exactly as
+ *   qt_quantize_rowwise draws them for a contiguous [rows, cols] tensor.
+ * t1, t2: contiguous bf16 [rows, cols] (t2 unused in mode 0). Needs cols % 8 == 0, cols <= 32768,
+ * q 8-byte and t1/t2 16-byte aligned: otherwise QT_ERR_UNSUPPORTED and the caller runs the three steps.
+ */
+int qt_int8_weight_update(void* q, void* scale, int64_t rows, int64_t cols, int mode, const void* t1,
+                          const void* t2, float value, float eps, uint64_t seed, uint64_t offset,
+                          void* stream);
+
+/*
  * The same update for n_tensors parameter tensors in as few launches as possible (a launch covers up
  * to 48 tensors / 320 blocks of 32768 elements). p, grad, exp_avg, exp_avg_sq and numel are HOST
  * arrays of n_tensors device pointers / lengths; all tensors share the dtypes and the scalars (the

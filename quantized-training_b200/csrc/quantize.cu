@@ -236,6 +236,11 @@ struct RowwiseParams {
     int stochastic;
     uint64_t seed, offset;
     int vec_load, vec_store;
+    // in-place weight update (UPD != 0): the row is not read from x but formed from the int8 weight
+    // itself, its scale and one or two bf16 operand tensors
+    const __nv_bfloat16* t1;
+    const __nv_bfloat16* t2;
+    float value;
 };
 
 // ---- packed bf16 helpers -----------------------------------------------------------------------
@@ -299,6 +304,34 @@ __device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider<f
     return out;
 }
 
+// Eight updated bf16 weights, packed like eight loaded bf16 values. The arithmetic is the eager
+// sequence on a bf16 weight, every step in fp32 and rounded to bf16 where eager materialises a tensor:
+//   w = bf16(float(q) * s)                          de-quantize (int8 tensor * bf16 scale)
+//   y = bf16(w + value * t1)            UPD == 1    add_(t1, alpha=value)
+//   y = bf16(w + value * (t1 / t2))     UPD == 2    addcdiv_(t1, t2, value=value)
+// with the multiply-add fused, as the compiled element-wise kernels of the framework do.
+template <int UPD>
+__device__ __forceinline__ uint4 updated_vec8(uint2 qb, float s, const uint4& a, const uint4& b, float value) {
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+    const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t qw = k < 2 ? qb.x : qb.y;
+        const int q0 = (int)(int8_t)((qw >> (16 * (k & 1))) & 0xFFu);
+        const int q1 = (int)(int8_t)((qw >> (16 * (k & 1) + 8)) & 0xFFu);
+        const float w0 = __bfloat162float(__float2bfloat16_rn(__fmul_rn((float)q0, s)));
+        const float w1 = __bfloat162float(__float2bfloat16_rn(__fmul_rn((float)q1, s)));
+        float t0 = __uint_as_float(aw[k] << 16), t1 = __uint_as_float(aw[k] & 0xFFFF0000u);
+        if constexpr (UPD == 2) {
+            t0 = __fdiv_rn(t0, __uint_as_float(bw[k] << 16));
+            t1 = __fdiv_rn(t1, __uint_as_float(bw[k] & 0xFFFF0000u));
+        }
+        out[k] = as_u32(__floats2bfloat162_rn(__fmaf_rn(value, t0, w0), __fmaf_rn(value, t1, w1)));
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
 // Row-wise kernel for bf16 rows that fit in registers. TPR threads cooperate on one row, each
 // holding VPT 16-byte vectors, so a row of up to TPR*VPT*8 columns is read from HBM exactly once.
 // The next row's loads are issued before the current row is reduced and quantized (register double
@@ -306,7 +339,10 @@ __device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider<f
 // each thread also keeps the running |x| maximum of its columns (packed bf16 pairs) over all rows
 // the CTA visits; at the end the CTA folds its sub-rows in shared memory, a pair of CTAs (a 2-CTA
 // cluster) folds through distributed shared memory, and one atomic max per column per pair goes out.
-template <int TPR, int VPT, bool COLABS, bool SR>
+// With UPD != 0 the kernel re-quantizes an int8 weight in place: the "row" is the updated weight formed
+// by updated_vec8 from q, scale and the operand tensors; q and scale are then overwritten (each row
+// is complete in registers before its bytes are stored, and a prefetched row is a different row).
+template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0>
 __global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1)))
 rowwise_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;  // rows per CTA per iteration
@@ -337,11 +373,29 @@ rowwise_kernel(const RowwiseParams p) {
     // vector is either wholly inside the row or wholly outside it
     auto load_row = [&](uint4 (&v)[VPT], int64_t row) {
         const bool valid = row < p.rows;
-        const __nv_bfloat16* xrow = x + (valid ? row : 0) * p.stride;
+        if constexpr (UPD == 0) {
+            const __nv_bfloat16* xrow = x + (valid ? row : 0) * p.stride;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int col = (i * TPR + t) * 8;
-            v[i] = (valid && col < p.cols) ? *reinterpret_cast<const uint4*>(xrow + col) : make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < VPT; ++i) {
+                const int col = (i * TPR + t) * 8;
+                v[i] = (valid && col < p.cols) ? *reinterpret_cast<const uint4*>(xrow + col) : make_uint4(0, 0, 0, 0);
+            }
+        } else {
+            const int64_t r = valid ? row : 0;
+            const float s = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.scale)[r]);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int col = (i * TPR + t) * 8;
+                if (valid && col < p.cols) {
+                    const int64_t at = r * p.cols + col;
+                    const uint2 qb = *reinterpret_cast<const uint2*>(p.q + at);
+                    const uint4 a = *reinterpret_cast<const uint4*>(p.t1 + at);
+                    const uint4 b = UPD == 2 ? *reinterpret_cast<const uint4*>(p.t2 + at) : make_uint4(0, 0, 0, 0);
+                    v[i] = updated_vec8<UPD>(qb, s, a, b, p.value);
+                } else {
+                    v[i] = make_uint4(0, 0, 0, 0);
+                }
+            }
         }
     };
 
@@ -486,14 +540,14 @@ __global__ void __launch_bounds__(kThreads) rowwise_generic_kernel(const Rowwise
 // of 4 or 8 constrain CTA placement enough to slow the streaming loop by a quarter (measured).
 constexpr int kClusterSize = 2;
 
-template <int TPR, int VPT, bool COLABS, bool SR>
+template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0>
 int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
     constexpr int RPC = kThreads / TPR;
     constexpr int CTAS_PER_SM = (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1));
     const int64_t want = (p.rows + RPC - 1) / RPC;
     const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
     int64_t grid = want < cap ? want : cap;
-    auto kfn = rowwise_kernel<TPR, VPT, COLABS, SR>;
+    auto kfn = rowwise_kernel<TPR, VPT, COLABS, SR, UPD>;
     if constexpr (COLABS) {
         constexpr int csize = kClusterSize;
         grid = (grid + csize - 1) / csize * csize;
@@ -517,17 +571,17 @@ int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
     return QT_OK;
 }
 
-template <bool COLABS, bool SR>
+template <bool COLABS, bool SR, int UPD = 0>
 int launch_rowwise_bf16(const RowwiseParams& p, cudaStream_t stream) {
     const int64_t c = p.cols;
-    if (c <= 256) return launch_rowwise_cfg<32, 1, COLABS, SR>(p, stream);
-    if (c <= 512) return launch_rowwise_cfg<32, 2, COLABS, SR>(p, stream);
-    if (c <= 1024) return launch_rowwise_cfg<32, 4, COLABS, SR>(p, stream);
-    if (c <= 2048) return launch_rowwise_cfg<64, 4, COLABS, SR>(p, stream);
-    if (c <= 4096) return launch_rowwise_cfg<128, 4, COLABS, SR>(p, stream);
-    if (c <= 8192) return launch_rowwise_cfg<256, 4, COLABS, SR>(p, stream);
-    if (c <= 16384) return launch_rowwise_cfg<256, 8, COLABS, SR>(p, stream);
-    if constexpr (!COLABS) return launch_rowwise_cfg<256, 16, COLABS, SR>(p, stream);
+    if (c <= 256) return launch_rowwise_cfg<32, 1, COLABS, SR, UPD>(p, stream);
+    if (c <= 512) return launch_rowwise_cfg<32, 2, COLABS, SR, UPD>(p, stream);
+    if (c <= 1024) return launch_rowwise_cfg<32, 4, COLABS, SR, UPD>(p, stream);
+    if (c <= 2048) return launch_rowwise_cfg<64, 4, COLABS, SR, UPD>(p, stream);
+    if (c <= 4096) return launch_rowwise_cfg<128, 4, COLABS, SR, UPD>(p, stream);
+    if (c <= 8192) return launch_rowwise_cfg<256, 4, COLABS, SR, UPD>(p, stream);
+    if (c <= 16384) return launch_rowwise_cfg<256, 8, COLABS, SR, UPD>(p, stream);
+    if constexpr (!COLABS) return launch_rowwise_cfg<256, 16, COLABS, SR, UPD>(p, stream);
     return fail(QT_ERR_UNSUPPORTED, "unreachable");
 }
 
@@ -577,7 +631,7 @@ int quantize_rowwise_impl(const void* x, int x_dtype, int64_t rows, int64_t cols
     }
     if (rows == 0 || cols == 0) return QT_OK;
 
-    RowwiseParams p;
+    RowwiseParams p = {};
     p.x = x; p.rows = rows; p.cols = cols; p.stride = stride;
     p.q = reinterpret_cast<uint8_t*>(q); p.scale = scale; p.col_absmax = col_absmax;
     p.q_dtype = q_dtype; p.scale_dtype = scale_dtype; p.eps = eps; p.stochastic = stochastic;
@@ -1092,6 +1146,28 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
 }
 
 // ---- allocation-free column-wise quantize ---------------------------------------------------------
+
+extern "C" int qt_int8_weight_update(void* q, void* scale, int64_t rows, int64_t cols, int mode, const void* t1,
+                                     const void* t2, float value, float eps, uint64_t seed, uint64_t offset,
+                                     void* stream_) {
+    QT_REQUIRE(mode == 0 || mode == 1, "int8_weight_update: mode must be 0 (add) or 1 (addcdiv), got %d", mode);
+    QT_REQUIRE(rows >= 0 && cols >= 0, "int8_weight_update: negative shape (%lld, %lld)", (long long)rows, (long long)cols);
+    if (rows == 0 || cols == 0) return QT_OK;
+    QT_REQUIRE(q && scale && t1 && (mode == 0 || t2), "int8_weight_update: null pointer");
+    if (cols % 8 != 0 || cols > 32768)
+        return fail(QT_ERR_UNSUPPORTED, "int8_weight_update: cols must be a multiple of 8 and at most 32768 (got %lld)", (long long)cols);
+    if (!aligned_to(q, 8) || !aligned_to(t1, 16) || (mode == 1 && !aligned_to(t2, 16)))
+        return fail(QT_ERR_UNSUPPORTED, "int8_weight_update: q must be 8-byte and the operands 16-byte aligned");
+    QT_REQUIRE(eps >= 1e-30f, "int8_weight_update: eps must be at least 1e-30");
+    RowwiseParams p = {};
+    p.rows = rows; p.cols = cols; p.stride = cols;
+    p.q = reinterpret_cast<uint8_t*>(q); p.scale = scale;
+    p.q_dtype = QT_I8; p.scale_dtype = QT_BF16; p.eps = eps; p.stochastic = 1;
+    p.seed = seed; p.offset = offset; p.vec_load = 1; p.vec_store = 1;
+    p.t1 = reinterpret_cast<const __nv_bfloat16*>(t1); p.t2 = reinterpret_cast<const __nv_bfloat16*>(t2); p.value = value;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    return mode == 0 ? launch_rowwise_bf16<false, true, 1>(p, stream) : launch_rowwise_bf16<false, true, 2>(p, stream);
+}
 
 // Scratch for qt_quantize_colwise_t_noalloc: the per-column absmax that the two-call form keeps in
 // a caller-allocated buffer. It lives in the library's own image (256 KB on every GPU that loads

@@ -6,6 +6,8 @@ Ops outside it (int4, fp4, conv2d, MX/NVFP4 utilities) raise NotImplementedError
 from .mm import int8_mm, scaled_mm
 from .quantize import (
     col_absmax,
+    int8_weight_update_,
+    int8_weight_update_supported,
     next_philox_key,
     quantize_colwise_t,
     quantize_rowwise,

@@ -221,3 +221,34 @@ def quantize_tile(x: Tensor, tile_shape: tuple[int, int], out_dtype: torch.dtype
     """Per-tile absmax quantize (tiles 1x128 or 128x128): returns (q [R,C], scale [R/tr, C/tc])."""
     fn = _tile_cuda if _direct(x) else lib_ops.quantize_tile
     return fn(x, tile_shape[0], tile_shape[1], out_dtype, scale_dtype or x.dtype, eps)
+
+
+def int8_weight_update_supported(int_data: Tensor, scale: Tensor, *operands: Tensor) -> bool:
+    """True when the fused in-place update kernel takes these tensors (otherwise the caller
+    de-quantizes, updates and re-quantizes in three steps)."""
+    if not (int_data.is_cuda and int_data.dtype is torch.int8 and int_data.ndim == 2 and int_data.is_contiguous()):
+        return False
+    rows, cols = int_data.shape
+    if cols % 8 != 0 or cols > 32768 or int_data.data_ptr() % 8:
+        return False
+    if scale.dtype is not torch.bfloat16 or scale.numel() != rows or not scale.is_contiguous() or scale.device != int_data.device:
+        return False
+    for t in operands:
+        if not (isinstance(t, Tensor) and type(t) is Tensor and t.dtype is torch.bfloat16 and t.shape == int_data.shape
+                and t.is_contiguous() and t.device == int_data.device and t.data_ptr() % 16 == 0):
+            return False
+    return True
+
+
+def int8_weight_update_(int_data: Tensor, scale: Tensor, t1: Tensor, t2: Tensor | None, value: float, *,
+                        eps: float = 1e-12, key: tuple[int, int] | None = None) -> None:
+    """int_data, scale <- stochastic row-wise INT8 quantization of (int_data * scale) + value * t1
+    (t2 is None) or + value * t1 / t2, in one pass and in place (reference: the de-quantize -> op ->
+    re-quantize -> copy_ sequence of subclasses/int8.py:114-133)."""
+    dev = nv.require_cuda(int_data, scale, t1, *(() if t2 is None else (t2,)))
+    seed, offset = key if key is not None else next_philox_key(dev)
+    rows, cols = int_data.shape
+    with nv.on_device(dev):
+        nv.check(nv.load().qt_int8_weight_update(
+            int_data.data_ptr(), scale.data_ptr(), rows, cols, 0 if t2 is None else 1, t1.data_ptr(),
+            None if t2 is None else t2.data_ptr(), float(value), float(eps), seed, offset, nv.stream_ptr(dev)))

@@ -202,9 +202,21 @@ class Int8LinearWeight(Tensor):
                 dst.copy_(src.dequantize())
             return dst
 
-        # in-place optimizer arithmetic: de-quantize, apply, write back through copy_
+        # in-place optimizer arithmetic: de-quantize, apply, re-quantize with stochastic rounding
+        # (int8.py:124-133) -- one fused kernel when the operands are plain bf16 tensors of the
+        # weight's shape, else the three steps through copy_
         if func in (aten.addcdiv_.default, aten.add_.Tensor):
             dst = args[0]
+            if isinstance(dst, cls) and not torch.compiler.is_compiling():
+                if func is aten.add_.Tensor:
+                    operands, value = args[1:2], kwargs.get("alpha", 1)
+                else:
+                    operands, value = args[1:3], kwargs.get("value", 1)
+                if (len(args) == 1 + len(operands) and isinstance(value, (int, float))
+                        and gn_kernels.int8_weight_update_supported(dst.int_data, dst.scale, *operands)):
+                    gn_kernels.int8_weight_update_(dst.int_data, dst.scale, operands[0],
+                                                   operands[1] if len(operands) > 1 else None, value)
+                    return dst
             return dst.copy_(func(dst.dequantize(), *args[1:], **kwargs))
 
         raise NotImplementedError(f"{cls.__name__} dispatch: attempting to run {func}, this is not supported")

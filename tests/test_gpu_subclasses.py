@@ -249,6 +249,53 @@ def test_adamw_stochastic_rounding_is_unbiased():
     assert len(torch.unique(outs[0])) == 2
 
 
+@pytest.mark.parametrize("shape", [(3, 8), (257, 264), (1024, 1024), (384, 1536), (96, 5632), (40, 12288), (9, 32768)])
+@pytest.mark.parametrize("mode", ["add", "addcdiv"])
+def test_fused_int8_weight_update_equals_three_steps(shape, mode):
+    """The fused kernel against the reference's own sequence run with eager CUDA ops: de-quantize,
+    add_/addcdiv_ on the bf16 tensor, stochastic row-wise re-quantize with the same Philox key."""
+    import gn_kernels
+
+    w = randn_bf16(shape, seed=1) * 0.05
+    w[0].zero_()                                         # an all-zero row keeps scale 0
+    q, scale = gn_kernels.quantize_rowwise(w)
+    t1 = randn_bf16(shape, seed=2) * 0.01
+    t2 = (randn_bf16(shape, seed=3).abs() * 0.1 + 1e-3).to(torch.bfloat16)
+    key = (4321, 17)
+    value = -3e-2
+    ref = q * scale.view(-1, 1)
+    assert ref.dtype is torch.bfloat16
+    if mode == "add":
+        ref.add_(t1, alpha=value)
+    else:
+        ref.addcdiv_(t1, t2, value=value)
+    want_q, want_s = gn_kernels.quantize_rowwise(ref, torch.int8, True, key=key)
+    assert gn_kernels.int8_weight_update_supported(q, scale, t1, t2)
+    gn_kernels.int8_weight_update_(q, scale, t1, None if mode == "add" else t2, value, key=key)
+    assert torch.equal(scale.view(-1), want_s.view(-1))
+    assert torch.equal(q, want_q)
+
+
+def test_int8_weight_optimizer_step_uses_the_fused_update(monkeypatch):
+    import gn_kernels
+
+    calls = []
+    real = gn_kernels.int8_weight_update_
+    monkeypatch.setattr(gn_kernels, "int8_weight_update_", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    lin = torch.nn.Linear(256, 128, bias=False).bfloat16().cuda()
+    convert_int8_quantized_training(lin)
+    before = lin.weight.detach().dequantize().float()
+    opt = torch.optim.AdamW(lin.parameters(), lr=1e-2, weight_decay=0.0, foreach=False)
+    x = randn_bf16((64, 256), seed=5)
+    lin(x).float().square().mean().backward()
+    opt.step()
+    assert calls, "the optimizer's addcdiv_ did not reach the fused kernel"
+    after = lin.weight.detach().dequantize().float()
+    # Adam's first step moves every weight with a non-zero gradient by about lr
+    moved = (after - before).abs()
+    assert 0.5e-2 < moved.mean().item() < 2e-2
+
+
 @pytest.mark.parametrize("p_dtype,g_dtype,sr", [(torch.bfloat16, torch.bfloat16, True), (torch.bfloat16, torch.float32, True),
                                                 (torch.float32, torch.bfloat16, False), (torch.float32, torch.float32, False)])
 def test_adamw_multi_equals_per_tensor_calls(p_dtype, g_dtype, sr):

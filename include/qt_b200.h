@@ -287,7 +287,7 @@ int qt_int8_weight_update(void* q, void* scale, int64_t rows, int64_t cols, int 
 
 /*
  * The same update for n_tensors parameter tensors in as few launches as possible (a launch covers up
- * to 48 tensors / 320 blocks of 32768 elements). p, grad, exp_avg, exp_avg_sq and numel are HOST
+ * to 160 tensors, 8192 elements per block). p, grad, exp_avg, exp_avg_sq and numel are HOST
  * arrays of n_tensors device pointers / lengths; all tensors share the dtypes and the scalars (the
  * reference steps every parameter of a group with the same hyper-parameters, other_optim/
  * bf16_sr.py:37-74, and launches one compiled kernel per parameter). Tensor t gets exactly the result

@@ -17,6 +17,8 @@
 // fetched as [K][128 B of M or N] boxes and described to the tensor core as MN-major, so A@B.T,
 // A@B and A.T@B run without any transpose pass. No TMA multicast is used anywhere: every CTA
 // fetches its own tiles (the pair form only redirects the completion bytes to the leader's barrier).
+#include <type_traits>
+
 #include "tcgen05.cuh"
 
 namespace qt {
@@ -31,9 +33,10 @@ constexpr int BM = 128;      // tile rows per CTA (one TMEM lane per row)
 constexpr int BN = 256;      // tile cols (= UMMA N, one TMEM column per col)
 constexpr int BK = 128;      // reduction elements per stage (8-bit => 128 bytes = one swizzle row)
 constexpr int UMMA_K = 32;   // reduction elements per tcgen05.mma for 8-bit operands
-constexpr int NUM_EPI_WARPS = 8;                       // two warps per TMEM lane quarter, 128 columns each
+constexpr int NUM_EPI_WARPS = 8;                       // two groups of four (one warp per TMEM lane quarter); group g drains accumulator g
+constexpr int EPI_GROUP_WARPS = 4;
+constexpr int STORE_STAGE_BYTES = 32 * 128;            // per epilogue warp: 32 rows x 128 bytes, the box of one TMA store
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;   // + TMA producer warp + MMA issuer warp
-constexpr int NUM_EPI_THREADS = 32 * NUM_EPI_WARPS;
 constexpr int TMEM_COLS = 512;                         // 2 accumulators x BN fp32/int32 columns
 constexpr int MAX_STAGES = 6;
 
@@ -57,12 +60,15 @@ struct Cfg {
     static constexpr int B_ATOM_BYTES = B_ROWS * BK;
     static constexpr int B_STAGE_BYTES = B_ATOM_BYTES * KA;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int SMEM_COLSCALE_OFF = STAGES * STAGE_BYTES;      // float [epilogue warps][BN / 2]
-    static constexpr int SMEM_BAR_OFF = SMEM_COLSCALE_OFF + NUM_EPI_WARPS * (BN / 2) * 4; // mbarriers
+    static constexpr int SMEM_STORE_OFF = STAGES * STAGE_BYTES;         // output staging, one box per epilogue warp
+    static constexpr int SMEM_COLSCALE_OFF = SMEM_STORE_OFF + NUM_EPI_WARPS * STORE_STAGE_BYTES;  // float [2 groups][BN]
+    static constexpr int SMEM_BAR_OFF = SMEM_COLSCALE_OFF + 2 * BN * 4;                       // mbarriers
     static constexpr int NUM_BARRIERS = 2 * MAX_STAGES + 4;
     static constexpr int SMEM_TMEMPTR_OFF = SMEM_BAR_OFF + NUM_BARRIERS * 8;
     static constexpr int SMEM_ABORT_OFF = SMEM_TMEMPTR_OFF + 4;
-    static constexpr int SMEM_TOTAL = SMEM_ABORT_OFF + 4 + 1024;        // + alignment slack
+    // no alignment slack: the dynamic shared memory is declared 1024-byte aligned (the kernel checks)
+    static constexpr int SMEM_TOTAL = SMEM_ABORT_OFF + 4;
+    static_assert(SMEM_TOTAL <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
 
 enum Epilogue { EPI_RAW = 0, EPI_ROWCOL = 1, EPI_TILE = 2 };
@@ -85,7 +91,35 @@ struct GemmParams {
     int splits;
     int kb_per_split;
     uint32_t* ws;
+    // the output goes through shared memory and TMA stores (needs a 16-byte aligned base and pitch);
+    // otherwise, and for split-K partials, every thread stores its own row directly
+    int tma_store;
+    int cs_vec;   // scale_b is 16-byte aligned: column scales load as vectors
 };
+
+// One lane's share of a tile's 256 column scales: columns n .. n+7, requested one tile ahead and kept
+// raw until they are written to shared memory. bf16 scales that can be fetched as one vector stay
+// packed in raw[0] (returns true); otherwise raw[0..1] hold eight fp32 values (zero beyond N).
+__device__ __forceinline__ bool load_col_scales8(uint4 (&raw)[2], const GemmParams& p, int64_t n) {
+    if (!p.scale_b_is_scalar && p.cs_vec && n + 8 <= p.N) {
+        if (p.scale_dtype == QT_BF16) {
+            raw[0] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.scale_b) + n));
+            return true;
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.scale_b) + n);
+        raw[0] = __ldg(src);
+        raw[1] = __ldg(src + 1);
+        return false;
+    }
+    float cs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        cs[j] = p.scale_b_is_scalar ? load_scale(p.scale_b, p.scale_dtype, 0)
+                                    : ((n + j < p.N) ? load_scale(p.scale_b, p.scale_dtype, n + j) : 0.0f);
+    raw[0] = make_uint4(__float_as_uint(cs[0]), __float_as_uint(cs[1]), __float_as_uint(cs[2]), __float_as_uint(cs[3]));
+    raw[1] = make_uint4(__float_as_uint(cs[4]), __float_as_uint(cs[5]), __float_as_uint(cs[6]), __float_as_uint(cs[7]));
+    return false;
+}
 
 // ---- the kernel -----------------------------------------------------------------------------
 
@@ -93,14 +127,17 @@ struct GemmParams {
 // global memory. CG: CTAs per MMA (see Cfg). The fp8 element formats arrive in `idesc`.
 template <int KIND, int EPI, bool A_MN, bool B_MN, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p,
-            const uint32_t idesc) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const uint32_t idesc) {
     using C = Cfg<CG>;
     constexpr int STAGES = C::STAGES;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t smem_base = smem_u32(smem);
-    float* s_colscale = reinterpret_cast<float*>(smem + C::SMEM_COLSCALE_OFF);
+    if ((smem_base & 1023u) != 0u) {
+        // the 128-byte swizzle of the TMA boxes and UMMA descriptors assumes this alignment
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, 0x900);
+        return;
+    }
     volatile uint32_t* s_tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + C::SMEM_TMEMPTR_OFF);
     volatile int* s_abort = reinterpret_cast<volatile int*>(smem + C::SMEM_ABORT_OFF);
 
@@ -131,7 +168,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar(b), 1);
-            mbar_init(tmem_empty_bar(b), NUM_EPI_WARPS * CG);  // one arrival per epilogue warp
+            mbar_init(tmem_empty_bar(b), EPI_GROUP_WARPS * CG);  // one arrival per warp of the group that drains it
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -257,47 +294,100 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
         }
     } else {
-        // ===== epilogue =====
-        const int ew = warp & 3;              // TMEM lane quarter this warp may read
-        const int half = (warp - 2) >> 2;     // which 128 of the tile's 256 columns this warp drains
-        constexpr int HALF_N = BN / 2;
-        // every row start and every 32-column chunk is 32-byte aligned: full-sector stores
+        // ===== epilogue: group g (four warps, one per TMEM lane quarter) drains accumulator g, i.e. every
+        // second tile of this CTA, so two tiles are in the epilogue at a time =====
+        const int ew = warp & 3;                          // TMEM lane quarter this warp may read
+        const int grp = (warp - 2) / EPI_GROUP_WARPS;     // accumulator buffer = parity of the CTA's tile count
         const int esz = (EPI == EPI_RAW || p.scale_dtype == QT_F32) ? 4 : 2;
-        const bool wide32 = ((reinterpret_cast<uintptr_t>(p.c) & 31) == 0) && (((p.ldc * esz) & 31) == 0);
-        int acc = 0;
+        const bool via_tma = p.tma_store != 0;
+        const uint32_t stage_addr = smem_base + C::SMEM_STORE_OFF + (uint32_t)(warp - 2) * STORE_STAGE_BYTES;
+        // this lane's row of the staging box; 16-byte piece q of the row sits at piece q ^ (row % 8)
+        // (the 128-byte swizzle the output tensor map declares): conflict-free vector stores
+        const uint32_t stage_row = stage_addr + (uint32_t)lane * 128u;
+        const uint32_t swz = (uint32_t)(lane & 7);
         uint32_t acc_phase = 0;
         bool ok = true;
-        const uint32_t leader_empty0 = CG == 2 ? map_to_cta(tmem_empty_bar(0), 0) : 0u;
-        const uint32_t leader_empty1 = CG == 2 ? map_to_cta(tmem_empty_bar(1), 0) : 0u;
-        for (int64_t work = first_tile; work < num_work && ok; work += tile_step) {
+        const uint32_t empty_bar_addr = CG == 2 ? map_to_cta(tmem_empty_bar(grp), 0) : tmem_empty_bar(grp);
+
+        auto row_of = [&](int64_t work) {
+            const TileCoord tc = tile_coord(work / p.splits, tiles_m, tiles_n);
+            return (int64_t)tc.m * (BM * CG) + (int64_t)cta_rank * BM + ew * 32 + lane;
+        };
+        int64_t work = first_tile + (int64_t)grp * tile_step;
+        const int64_t work_step = 2 * tile_step;
+        // Scales are requested one tile ahead: this lane's row scale, and its 8 of the tile's 256 column
+        // scales. Every warp of the group then writes all 256 column scales (as fp32) to the group's
+        // shared array: the four warps write identical values, so no barrier is needed between them, and
+        // a warp only gets here after all four handed the previous accumulator back, which they do after
+        // their last read of the previous tile's scales.
+        float* cs_grp = reinterpret_cast<float*>(smem + C::SMEM_COLSCALE_OFF) + grp * BN;
+        const uint32_t cs_grp_addr = smem_base + C::SMEM_COLSCALE_OFF + (uint32_t)grp * BN * 4u;
+        auto col0_of = [&](int64_t work) {
+            const TileCoord tc = tile_coord(work / p.splits, tiles_m, tiles_n);
+            return (int64_t)tc.n * BN;
+        };
+        float next_row_scale = 0.0f;
+        uint4 next_cs[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        bool next_cs_packed = false;
+        if constexpr (EPI == EPI_ROWCOL) {
+            if (work < num_work) {
+                const int64_t r = row_of(work);
+                if (r < p.M) next_row_scale = load_scale(p.scale_a, p.scale_dtype, r);
+                next_cs_packed = load_col_scales8(next_cs, p, col0_of(work) + lane * 8);
+            }
+        }
+        for (; work < num_work && ok; work += work_step) {
             const int64_t tile = work / p.splits;
             const int split = (int)(work - tile * p.splits);
             const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
             const int64_t m0 = (int64_t)tc.m * (BM * CG) + (int64_t)cta_rank * BM, n0 = (int64_t)tc.n * BN;
-            const int64_t row = m0 + ew * 32 + lane;
+            const int64_t row0 = m0 + ew * 32;
+            const int64_t row = row0 + lane;
             // split-K partials go out raw, one [M][N] plane per split
             uint32_t* ws_row = (p.splits > 1 && row < p.M) ? p.ws + ((int64_t)split * p.M + row) * p.N : nullptr;
 
-            float row_scale = 0.0f;
-            float* cs_warp = s_colscale + (warp - 2) * HALF_N;  // private to this warp: no cross-warp barrier
-            if constexpr (EPI == EPI_ROWCOL) {
-                // stage this tile's column scales as fp32
-                for (int j = lane; j < HALF_N; j += 32) {
-                    const int64_t n = n0 + half * HALF_N + j;
-                    cs_warp[j] = (n < p.N) ? load_scale(p.scale_b, p.scale_dtype, p.scale_b_is_scalar ? 0 : n) : 0.0f;
-                }
-                if (row < p.M) row_scale = load_scale(p.scale_a, p.scale_dtype, row);
-                __syncwarp();
-            }
+            const float row_scale = next_row_scale;
 
-            ok = mbar_wait(tmem_full_bar(acc), acc_phase, s_abort, p.status, 0x400 | acc);
+            ok = mbar_wait(tmem_full_bar(grp), acc_phase, s_abort, p.status, 0x400 | grp);
             if (!ok) break;
             tcgen05_fence_after();
+            if constexpr (EPI == EPI_ROWCOL) {
+                if (p.splits == 1) {
+                    uint4 lo = next_cs[0], hi = next_cs[1];
+                    if (next_cs_packed) {
+                        const uint4 w = next_cs[0];
+                        lo = make_uint4(w.x << 16, w.x & 0xFFFF0000u, w.y << 16, w.y & 0xFFFF0000u);
+                        hi = make_uint4(w.z << 16, w.z & 0xFFFF0000u, w.w << 16, w.w & 0xFFFF0000u);
+                    }
+                    st_shared_v4(cs_grp_addr + (uint32_t)lane * 32u, lo.x, lo.y, lo.z, lo.w);
+                    st_shared_v4(cs_grp_addr + (uint32_t)lane * 32u + 16u, hi.x, hi.y, hi.z, hi.w);
+                    __syncwarp();
+                }
+                // request the scales of this group's next tile
+                next_row_scale = 0.0f;
+                if (work + work_step < num_work) {
+                    const int64_t r = row_of(work + work_step);
+                    if (r < p.M) next_row_scale = load_scale(p.scale_a, p.scale_dtype, r);
+                    next_cs_packed = load_col_scales8(next_cs, p, col0_of(work + work_step) + lane * 8);
+                }
+            }
 
-            const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * BN + half * HALF_N);
-            // scale + store one 32-column chunk held in registers
-            auto emit = [&](const uint32_t (&r)[32], int c) {
-                const int64_t n = n0 + half * HALF_N + c * 32;
+            const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(grp * BN);
+            // hand the accumulator back to the MMA issuer (after this warp's last TMEM load has completed)
+            auto release_acc = [&]() {
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (CG == 2) mbar_arrive_cluster(empty_bar_addr);   // the pair's accumulator: both CTAs report to the leader
+                    else mbar_arrive(empty_bar_addr);
+                }
+            };
+            // Scale (or pass through) one 32-column chunk held in registers and send it out, eight columns
+            // at a time so that few values are live at once.
+            auto emit = [&](const uint32_t (&r)[32], int c, auto odd_tag, auto last_tag) {
+                constexpr bool ODD = decltype(odd_tag)::value;    // chunk parity, known at compile time
+                constexpr bool LAST = decltype(last_tag)::value;  // the tile's last chunk
+                const int64_t n = n0 + c * 32;
                 if (ws_row != nullptr) {
                     if (n < p.N) {
                         uint32_t* dst = ws_row + n;
@@ -306,84 +396,138 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                             for (int j = 0; j < 32; j += 8)
                                 st_global_v8(dst + j, r[j], r[j + 1], r[j + 2], r[j + 3], r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
                         } else {
-                            for (int j = 0; j < 32 && n + j < p.N; ++j) dst[j] = r[j];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n + j < p.N) dst[j] = r[j];
                         }
                     }
-                } else if (row < p.M && n < p.N) {
+                    return;
+                }
+                if (p.splits > 1) return;  // a row beyond M of a split-K partial
+                // The last chunk takes its column scales into registers up front and hands the accumulator
+                // back before converting: the next tile's scales may be written once all four warps of the
+                // group are past their last read of this tile's.
+                float4 csr[(LAST && EPI == EPI_ROWCOL) ? 8 : 1];
+                if constexpr (LAST && EPI == EPI_ROWCOL) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) csr[q] = *reinterpret_cast<const float4*>(cs_grp + c * 32 + q * 4);
+                    release_acc();
+                }
+                // eight output values as 32-bit words: 8 words (4-byte outputs) or 4 (bf16 pairs)
+                auto convert8 = [&](uint32_t (&w)[8], int g) {
                     if constexpr (EPI == EPI_RAW) {
-                        // int32 (or fp32 bit pattern) straight out
-                        uint32_t* dst = reinterpret_cast<uint32_t*>(p.c) + row * p.ldc + n;
-                        if (n + 32 <= p.N && wide32) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8)
-                                st_global_v8(dst + j, r[j], r[j + 1], r[j + 2], r[j + 3], r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
-                        } else if (n + 32 <= p.N && (p.ldc & 3) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                        for (int j = 0; j < 8; ++j) w[j] = r[g * 8 + j];
+                    } else {
+                        float4 c0, c1;
+                        if constexpr (LAST) {
+                            c0 = csr[2 * g]; c1 = csr[2 * g + 1];
                         } else {
-                            for (int j = 0; j < 32 && n + j < p.N; ++j) dst[j] = r[j];
+                            c0 = *reinterpret_cast<const float4*>(cs_grp + c * 32 + g * 8);      // broadcast reads
+                            c1 = *reinterpret_cast<const float4*>(cs_grp + c * 32 + g * 8 + 4);
+                        }
+                        const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                        // (acc * row_scale) * col_scale, two columns per packed fp32x2 multiply
+                        float v[8];
+                        const float2 rs2 = make_float2(row_scale, row_scale);
+#pragma unroll
+                        for (int j = 0; j < 8; j += 2) {
+                            const float a0 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j] : __uint_as_float(r[g * 8 + j]);
+                            const float a1 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j + 1] : __uint_as_float(r[g * 8 + j + 1]);
+                            const float2 t = __fmul2_rn(__fmul2_rn(make_float2(a0, a1), rs2), make_float2(cs[j], cs[j + 1]));
+                            v[j] = t.x; v[j + 1] = t.y;
+                        }
+                        if (esz == 2) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) w[j] = __float_as_uint(v[j]);
+                        }
+                    }
+                };
+                if (via_tma) {
+                    // a staging box holds 128 bytes per row: one chunk of 4-byte outputs, two of bf16
+                    const bool first_of_box = esz == 4 || !ODD;
+                    const bool last_of_box = esz == 4 || ODD;
+                    if (esz == 4) {
+                        if (lane == 0) bulk_store_wait_read();   // the previous box has left shared memory
+                        __syncwarp();
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint32_t w[8];
+                            convert8(w, g);
+                            st_shared_v4(stage_row + (((uint32_t)(2 * g) ^ swz) << 4), w[0], w[1], w[2], w[3]);
+                            st_shared_v4(stage_row + (((uint32_t)(2 * g + 1) ^ swz) << 4), w[4], w[5], w[6], w[7]);
                         }
                     } else {
-                        const float* cs = cs_warp + c * 32;
-                        float v[32];
+                        // convert first, then wait: the previous box's store was issued just before, and
+                        // its read of the staging buffer overlaps this chunk's arithmetic
+                        uint32_t w[4][8];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const float a = (KIND == 0) ? (float)(int32_t)r[j] : __uint_as_float(r[j]);
-                            v[j] = __fmul_rn(__fmul_rn(a, row_scale), cs[j]);
+                        for (int g = 0; g < 4; ++g) convert8(w[g], g);
+                        if (first_of_box) {
+                            if (lane == 0) bulk_store_wait_read();
+                            __syncwarp();
                         }
-                        if (p.scale_dtype == QT_BF16) {
-                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + row * p.ldc + n;
-                            if (n + 32 <= p.N && wide32) {
 #pragma unroll
-                                for (int j = 0; j < 32; j += 16)
-                                    st_global_v8(dst + j, pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                                                 pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]),
-                                                 pack_bf16x2(v[j + 8], v[j + 9]), pack_bf16x2(v[j + 10], v[j + 11]),
-                                                 pack_bf16x2(v[j + 12], v[j + 13]), pack_bf16x2(v[j + 14], v[j + 15]));
-                            } else if (n + 32 <= p.N && (p.ldc & 7) == 0) {
+                        for (int g = 0; g < 4; ++g)
+                            st_shared_v4(stage_row + (((uint32_t)((ODD ? 4 : 0) + g) ^ swz) << 4), w[g][0], w[g][1], w[g][2], w[g][3]);
+                    }
+                    if (last_of_box) {
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        const int64_t nb = (esz == 4) ? n : n - 32;   // first column of the box
+                        if (lane == 0 && row0 < p.M && nb < p.N) {
+                            tma_store_2d(&tmap_c, stage_addr, (int)(nb * esz), (int)row0);
+                            bulk_store_commit();
+                        }
+                    }
+                    return;
+                }
+                // an output whose base or pitch is not 16-byte aligned: element stores (unrolled: the chunk
+                // registers must never be indexed dynamically)
 #pragma unroll
-                                for (int j = 0; j < 32; j += 8)
-                                    *reinterpret_cast<uint4*>(dst + j) =
-                                        make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                                                   pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
-                            } else {
-                                for (int j = 0; j < 32 && n + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
-                            }
-                        } else {
-                            float* dst = reinterpret_cast<float*>(p.c) + row * p.ldc + n;
-                            if (n + 32 <= p.N && (p.ldc & 3) == 0) {
+                for (int g = 0; g < 4; ++g) {
+                    uint32_t w[8];
+                    convert8(w, g);
+                    if (row < p.M) {
 #pragma unroll
-                                for (int j = 0; j < 32; j += 4)
-                                    *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            } else {
-                                for (int j = 0; j < 32 && n + j < p.N; ++j) dst[j] = v[j];
+                        for (int j = 0; j < 8; ++j) {
+                            const int64_t at = row * p.ldc + n + g * 8 + j;
+                            if (n + g * 8 + j < p.N) {
+                                if (esz == 4) reinterpret_cast<uint32_t*>(p.c)[at] = w[j];
+                                else reinterpret_cast<uint16_t*>(p.c)[at] = (uint16_t)((w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu);
                             }
                         }
                     }
                 }
             };
-            // two register buffers: the TMEM load of chunk c+1 is in flight while chunk c is stored
+            // two register buffers: the TMEM load of chunk c+1 is in flight while chunk c goes out. The
+            // accumulator is handed back as soon as its last chunk is in registers.
+            constexpr int CHUNKS = BN / 32;
+            const bool scales_in_smem = EPI == EPI_ROWCOL && p.splits == 1;
             uint32_t ra[32], rb[32];
             tmem_ld_32x32(t_row, ra);
 #pragma unroll 1
-            for (int c = 0; c < HALF_N / 32; c += 2) {
+            for (int c = 0; c < CHUNKS - 2; c += 2) {
                 tmem_ld_wait();
                 tmem_ld_32x32(t_row + (c + 1) * 32, rb);
-                emit(ra, c);
+                emit(ra, c, std::false_type{}, std::false_type{});
                 tmem_ld_wait();
-                if (c + 2 < HALF_N / 32) tmem_ld_32x32(t_row + (c + 2) * 32, ra);
-                emit(rb, c + 1);
+                tmem_ld_32x32(t_row + (c + 2) * 32, ra);
+                emit(rb, c + 1, std::true_type{}, std::false_type{});
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            // the accumulator belongs to the pair: both CTAs report to the leader's barrier
-            if (lane == 0) {
-                if constexpr (CG == 2) mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
-                else mbar_arrive(tmem_empty_bar(acc));
-            }
-            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            tmem_ld_wait();
+            tmem_ld_32x32(t_row + (CHUNKS - 1) * 32, rb);
+            emit(ra, CHUNKS - 2, std::false_type{}, std::false_type{});
+            tmem_ld_wait();
+            if (!scales_in_smem) release_acc();   // (the scaled epilogue releases inside its last emit)
+            emit(rb, CHUNKS - 1, std::true_type{}, std::true_type{});
+            acc_phase ^= 1u;
         }
+        // shared memory must outlive the last store's read of it; global visibility follows at grid end
+        if (via_tma && lane == 0) bulk_store_wait_all();
     }
 
     tcgen05_fence_before();
@@ -405,8 +549,8 @@ int g_forced_cta_group = 0;
 int g_sm_margin = 0;
 
 template <int KIND, int EPI, bool A_MN, bool B_MN, int CG>
-int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, uint32_t idesc, int64_t tiles,
-               cudaStream_t stream) {
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, uint32_t idesc,
+               int64_t tiles, cudaStream_t stream) {
     auto kfn = gemm_kernel<KIND, EPI, A_MN, B_MN, CG>;
     constexpr int SMEM = Cfg<CG>::SMEM_TOTAL;
     static bool attr_set[64] = {false};
@@ -446,17 +590,17 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
         if (sms < 1) sms = 1;
         cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));
     }
-    QT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kfn, ta, tb, p, idesc));
+    QT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kfn, ta, tb, tc, p, idesc));
     return QT_OK;
 }
 
 template <int KIND, int EPI, int CG>
-int launch_layout(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, uint32_t idesc,
-                  int64_t tiles, cudaStream_t stream) {
-    if (!a_mn && !b_mn) return launch_one<KIND, EPI, false, false, CG>(ta, tb, p, idesc, tiles, stream);
-    if (!a_mn && b_mn) return launch_one<KIND, EPI, false, true, CG>(ta, tb, p, idesc, tiles, stream);
-    if (a_mn && b_mn) return launch_one<KIND, EPI, true, true, CG>(ta, tb, p, idesc, tiles, stream);
-    return launch_one<KIND, EPI, true, false, CG>(ta, tb, p, idesc, tiles, stream);
+int launch_layout(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                  uint32_t idesc, int64_t tiles, cudaStream_t stream) {
+    if (!a_mn && !b_mn) return launch_one<KIND, EPI, false, false, CG>(ta, tb, tc, p, idesc, tiles, stream);
+    if (!a_mn && b_mn) return launch_one<KIND, EPI, false, true, CG>(ta, tb, tc, p, idesc, tiles, stream);
+    if (a_mn && b_mn) return launch_one<KIND, EPI, true, true, CG>(ta, tb, tc, p, idesc, tiles, stream);
+    return launch_one<KIND, EPI, true, false, CG>(ta, tb, tc, p, idesc, tiles, stream);
 }
 
 // Sums the split-K partial planes and applies the epilogue. Integer partials add exactly, so the
@@ -575,6 +719,15 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
     if (b_mn) { if (int rc = make_tmap(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)b_pitch, 128, BK)) return rc; }
     else      { if (int rc = make_tmap(&tb, b, (uint64_t)K, (uint64_t)N, (uint64_t)b_pitch, BK, (uint32_t)b_rows)) return rc; }
 
+    // the output as a byte tensor (rows of N * esz bytes): boxes of 32 rows x 128 bytes, clipped at the edges
+    const int esz = (epi == EPI_RAW || p.scale_dtype == QT_F32) ? 4 : 2;
+    p.tma_store = (p.splits == 1 && aligned_to(p.c, 16) && (p.ldc * esz) % 16 == 0) ? 1 : 0;
+    p.cs_vec = (epi == EPI_ROWCOL && aligned_to(p.scale_b, 16)) ? 1 : 0;
+    CUtensorMap tc = ta;  // a valid map even when unused
+    if (p.tma_store) {
+        if (int rc = make_tmap(&tc, p.c, (uint64_t)(N * esz), (uint64_t)M, (uint64_t)(p.ldc * esz), 128, 32)) return rc;
+    }
+
     if (int rc = device_status_ptr(&p.status)) return rc;
 
     const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + BN - 1) / BN) * p.splits;  // work items
@@ -582,8 +735,8 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
                                  : make_idesc(1, fp8_format(a_dtype), fp8_format(b_dtype), a_mn, b_mn, BM * cg, BN);
 #define QT_DISPATCH(KIND, EPI)                                                                               \
     do {                                                                                                     \
-        const int rc_ = cg == 2 ? launch_layout<KIND, EPI, 2>(a_mn, b_mn, ta, tb, p, idesc, tiles, stream)   \
-                                : launch_layout<KIND, EPI, 1>(a_mn, b_mn, ta, tb, p, idesc, tiles, stream);  \
+        const int rc_ = cg == 2 ? launch_layout<KIND, EPI, 2>(a_mn, b_mn, ta, tb, tc, p, idesc, tiles, stream)   \
+                                : launch_layout<KIND, EPI, 1>(a_mn, b_mn, ta, tb, tc, p, idesc, tiles, stream);  \
         if (rc_ != QT_OK || p.splits == 1) return rc_;                                                       \
         return launch_finish<KIND, EPI>(p, stream);                                                          \
     } while (0)

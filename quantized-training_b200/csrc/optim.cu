@@ -138,13 +138,13 @@ __global__ void __launch_bounds__(kThreads) adamw_kernel(const AdamParams a) {
 }
 
 // ---- multi-tensor form: one launch updates many parameter tensors ---------------------------------
-// A launch carries a table of up to kMaxTensors tensors and kMaxBlocks blocks; block b updates chunk
-// block_chunk[b] (kChunk elements) of tensor block_tensor[b]. Tensor t draws its random bits with
-// Philox offset `offset + t`, i.e. exactly what a single-tensor call with that offset draws.
+// A launch carries a table of up to kMaxTensors tensors; the grid is the total number of kChunk-element
+// chunks of all of them, and a block finds its tensor by bisecting the running chunk count. Tensor t
+// draws its random bits with Philox offset `offset + t`, i.e. exactly what a single-tensor call with
+// that offset draws.
 
-constexpr int kMaxTensors = 48;
-constexpr int kMaxBlocks = 320;
-constexpr int kChunk = 32768;   // elements per block (458 KB of traffic for bf16 p and g)
+constexpr int kMaxTensors = 160;
+constexpr int kChunk = 8192;   // elements per block: 8 quads per thread
 
 struct MultiTable {
     void* p[kMaxTensors];
@@ -153,17 +153,22 @@ struct MultiTable {
     __nv_bfloat16* v[kMaxTensors];
     int64_t numel[kMaxTensors];
     uint32_t tensor_index[kMaxTensors];
-    int32_t block_chunk[kMaxBlocks];
-    uint8_t block_tensor[kMaxBlocks];
+    uint32_t chunk_begin[kMaxTensors + 1];   // first block of each tensor; [n] = grid size
+    int n;
 };
 
 template <typename PT, typename GT>
 __global__ void __launch_bounds__(kThreads) adamw_multi_kernel(const __grid_constant__ MultiTable tab, const AdamParams proto) {
-    const int t = tab.block_tensor[blockIdx.x];
+    int lo = 0, hi = tab.n;   // the tensor t with chunk_begin[t] <= blockIdx.x < chunk_begin[t + 1]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tab.chunk_begin[mid] <= blockIdx.x) lo = mid; else hi = mid;
+    }
+    const int t = lo;
     AdamParams a = proto;
     a.p = tab.p[t]; a.g = tab.g[t]; a.m = tab.m[t]; a.v = tab.v[t]; a.n = tab.numel[t];
     a.offset = proto.offset + tab.tensor_index[t];
-    const int64_t q_begin = (int64_t)tab.block_chunk[blockIdx.x] * (kChunk / 4);
+    const int64_t q_begin = (int64_t)(blockIdx.x - tab.chunk_begin[t]) * (kChunk / 4);
     const int64_t n4 = (a.n + 3) / 4;
     const int64_t q_end = q_begin + kChunk / 4 < n4 ? q_begin + kChunk / 4 : n4;
     for (int64_t q = q_begin + threadIdx.x; q < q_end; q += kThreads) adam_quad<PT, GT>(a, q);
@@ -226,15 +231,17 @@ extern "C" int qt_adamw_bf16_sr_multi(int n_tensors, void* const* p, const void*
     a.stochastic = stochastic; a.seed = seed; a.offset = offset;
 
     MultiTable tab;
-    int nt = 0, nb = 0;
+    tab.n = 0;
+    tab.chunk_begin[0] = 0;
     auto flush = [&]() -> int {
-        if (nb == 0) { nt = 0; return QT_OK; }
-        if (p_dtype == QT_BF16 && grad_dtype == QT_BF16) adamw_multi_kernel<__nv_bfloat16, __nv_bfloat16><<<nb, kThreads, 0, stream>>>(tab, a);
-        else if (p_dtype == QT_BF16) adamw_multi_kernel<__nv_bfloat16, float><<<nb, kThreads, 0, stream>>>(tab, a);
-        else if (grad_dtype == QT_BF16) adamw_multi_kernel<float, __nv_bfloat16><<<nb, kThreads, 0, stream>>>(tab, a);
-        else adamw_multi_kernel<float, float><<<nb, kThreads, 0, stream>>>(tab, a);
+        if (tab.n == 0) return QT_OK;
+        const unsigned grid = tab.chunk_begin[tab.n];
+        if (p_dtype == QT_BF16 && grad_dtype == QT_BF16) adamw_multi_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, stream>>>(tab, a);
+        else if (p_dtype == QT_BF16) adamw_multi_kernel<__nv_bfloat16, float><<<grid, kThreads, 0, stream>>>(tab, a);
+        else if (grad_dtype == QT_BF16) adamw_multi_kernel<float, __nv_bfloat16><<<grid, kThreads, 0, stream>>>(tab, a);
+        else adamw_multi_kernel<float, float><<<grid, kThreads, 0, stream>>>(tab, a);
         QT_CUDA_CHECK(cudaGetLastError());
-        nt = 0; nb = 0;
+        tab.n = 0;
         return QT_OK;
     };
     for (int t = 0; t < n_tensors; ++t) {
@@ -244,20 +251,16 @@ extern "C" int qt_adamw_bf16_sr_multi(int n_tensors, void* const* p, const void*
         QT_REQUIRE(aligned_to(p[t], 16) && aligned_to(grad[t], 16) && aligned_to(exp_avg[t], 8) && aligned_to(exp_avg_sq[t], 8),
                    "adamw_multi: tensor %d must be 16-byte aligned", t);
         const int64_t chunks = (numel[t] + kChunk - 1) / kChunk;
-        int64_t c = 0;
-        while (c < chunks) {
-            if (nt == kMaxTensors || nb == kMaxBlocks) { if (int rc = flush()) return rc; }
-            // (re-)enter this tensor into the current table
-            const int slot = nt++;
-            tab.p[slot] = p[t]; tab.g[slot] = grad[t];
-            tab.m[slot] = reinterpret_cast<__nv_bfloat16*>(exp_avg[t]); tab.v[slot] = reinterpret_cast<__nv_bfloat16*>(exp_avg_sq[t]);
-            tab.numel[slot] = numel[t]; tab.tensor_index[slot] = (uint32_t)t;
-            while (c < chunks && nb < kMaxBlocks) {
-                tab.block_tensor[nb] = (uint8_t)slot;
-                tab.block_chunk[nb] = (int32_t)c;
-                ++nb; ++c;
-            }
+        QT_REQUIRE(chunks < (1ll << 30), "adamw_multi: tensor %d is too large", t);
+        // a launch holds at most kMaxTensors tensors and 2^31 - 1 blocks
+        if (tab.n == kMaxTensors || (int64_t)tab.chunk_begin[tab.n] + chunks >= (1ll << 31)) {
+            if (int rc = flush()) return rc;
         }
+        const int slot = tab.n++;
+        tab.p[slot] = p[t]; tab.g[slot] = grad[t];
+        tab.m[slot] = reinterpret_cast<__nv_bfloat16*>(exp_avg[t]); tab.v[slot] = reinterpret_cast<__nv_bfloat16*>(exp_avg_sq[t]);
+        tab.numel[slot] = numel[t]; tab.tensor_index[slot] = (uint32_t)t;
+        tab.chunk_begin[slot + 1] = tab.chunk_begin[slot] + (uint32_t)chunks;
     }
     return flush();
 }

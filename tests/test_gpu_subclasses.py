@@ -299,9 +299,9 @@ def test_int8_weight_optimizer_step_uses_the_fused_update(monkeypatch):
 @pytest.mark.parametrize("p_dtype,g_dtype,sr", [(torch.bfloat16, torch.bfloat16, True), (torch.bfloat16, torch.float32, True),
                                                 (torch.float32, torch.bfloat16, False), (torch.float32, torch.float32, False)])
 def test_adamw_multi_equals_per_tensor_calls(p_dtype, g_dtype, sr):
-    # sizes around the kernel's chunk (32768 elements) and table limits (48 tensors, 320 blocks per launch),
-    # ragged tails, an empty tensor
-    sizes = [1, 3, 4, 7, 0, 32768, 32769, 65536 + 5, 1000, 4096 * 4096 + 8] + [257 + 4 * i for i in range(60)]
+    # sizes around the kernel's chunk (8192 elements) and table limit (160 tensors per launch), ragged
+    # tails, an empty tensor
+    sizes = [1, 3, 4, 7, 0, 8192, 8193, 32768, 65536 + 5, 1000, 4096 * 4096 + 8] + [257 + 4 * i for i in range(180)]
     gen = torch.Generator(device="cuda").manual_seed(3)
     mk = lambda n, dt, scale=1.0: (torch.randn(n, device="cuda", generator=gen) * scale).to(dt)  # noqa: E731
     ps = [mk(n, p_dtype) for n in sizes]

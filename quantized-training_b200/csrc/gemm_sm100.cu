@@ -155,11 +155,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // tiles are BM*CG rows x BN columns, one per CTA (CG == 1) or per CTA pair (CG == 2)
     const int tiles_m = (int)((p.M + BM * CG - 1) / (BM * CG));
     const int tiles_n = (int)((p.N + BN - 1) / BN);
-    const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
     const int num_kb = (int)((p.K + C::BKS - 1) / C::BKS);
-    const int64_t first_tile = blockIdx.x / CG;
-    const int64_t tile_step = gridDim.x / CG;
-    const int64_t num_work = num_tiles * p.splits;  // a work item is (tile, K split)
+    // a work item is (tile, K split); the host keeps their number below 2^30, so 32-bit indices do
+    const uint32_t first_tile = blockIdx.x / CG;
+    const uint32_t tile_step = gridDim.x / CG;
+    const uint32_t num_work = (uint32_t)tiles_m * (uint32_t)tiles_n * (uint32_t)p.splits;
+    struct WorkItem { int m, n, split; };
+    auto locate = [&](uint32_t work) {
+        uint32_t tile = work, split = 0;
+        if (p.splits > 1) {
+            tile = work / (uint32_t)p.splits;
+            split = work - tile * (uint32_t)p.splits;
+        }
+        const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+        return WorkItem{tc.m, tc.n, (int)split};
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -194,12 +204,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int64_t work = first_tile; work < num_work && ok; work += tile_step) {
-            const int64_t tile = work / p.splits;
-            const int split = (int)(work - tile * p.splits);
-            const int kb_begin = split * p.kb_per_split;
+        for (uint32_t work = first_tile; work < num_work && ok; work += tile_step) {
+            const WorkItem tc = locate(work);
+            const int kb_begin = tc.split * p.kb_per_split;
             const int kb_end = (kb_begin + p.kb_per_split < num_kb) ? kb_begin + p.kb_per_split : num_kb;
-            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
             const int m0 = tc.m * (BM * CG) + (int)cta_rank * BM;
             const int n0 = tc.n * BN + (int)cta_rank * C::B_ROWS;
             for (int kb = kb_begin; kb < kb_end; ++kb) {
@@ -251,8 +259,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int64_t work = first_tile; work < num_work && ok; work += tile_step) {
-                const int split = (int)(work % p.splits);
+            for (uint32_t work = first_tile; work < num_work && ok; work += tile_step) {
+                const int split = p.splits > 1 ? (int)(work % (uint32_t)p.splits) : 0;
                 const int kb_begin = split * p.kb_per_split;
                 const int kb_end = (kb_begin + p.kb_per_split < num_kb) ? kb_begin + p.kb_per_split : num_kb;
                 ok = mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, s_abort, p.status, 0x200 | acc);
@@ -309,12 +317,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         bool ok = true;
         const uint32_t empty_bar_addr = CG == 2 ? map_to_cta(tmem_empty_bar(grp), 0) : tmem_empty_bar(grp);
 
-        auto row_of = [&](int64_t work) {
-            const TileCoord tc = tile_coord(work / p.splits, tiles_m, tiles_n);
-            return (int64_t)tc.m * (BM * CG) + (int64_t)cta_rank * BM + ew * 32 + lane;
-        };
-        int64_t work = first_tile + (int64_t)grp * tile_step;
-        const int64_t work_step = 2 * tile_step;
         // Scales are requested one tile ahead: this lane's row scale, and its 8 of the tile's 256 column
         // scales. Every warp of the group then writes all 256 column scales (as fp32) to the group's
         // shared array: the four warps write identical values, so no barrier is needed between them, and
@@ -322,24 +324,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // their last read of the previous tile's scales.
         float* cs_grp = reinterpret_cast<float*>(smem + C::SMEM_COLSCALE_OFF) + grp * BN;
         const uint32_t cs_grp_addr = smem_base + C::SMEM_COLSCALE_OFF + (uint32_t)grp * BN * 4u;
-        auto col0_of = [&](int64_t work) {
-            const TileCoord tc = tile_coord(work / p.splits, tiles_m, tiles_n);
-            return (int64_t)tc.n * BN;
-        };
         float next_row_scale = 0.0f;
         uint4 next_cs[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
         bool next_cs_packed = false;
+        auto request_scales = [&](const WorkItem& w) {
+            const int64_t r = (int64_t)w.m * (BM * CG) + (int64_t)cta_rank * BM + ew * 32 + lane;
+            next_row_scale = (r < p.M) ? load_scale(p.scale_a, p.scale_dtype, r) : 0.0f;
+            next_cs_packed = load_col_scales8(next_cs, p, (int64_t)w.n * BN + lane * 8);
+        };
+        uint32_t work = first_tile + (uint32_t)grp * tile_step;
+        const uint32_t work_step = 2 * tile_step;
+        WorkItem next_item = locate(work < num_work ? work : 0u);
         if constexpr (EPI == EPI_ROWCOL) {
-            if (work < num_work) {
-                const int64_t r = row_of(work);
-                if (r < p.M) next_row_scale = load_scale(p.scale_a, p.scale_dtype, r);
-                next_cs_packed = load_col_scales8(next_cs, p, col0_of(work) + lane * 8);
-            }
+            if (work < num_work) request_scales(next_item);
         }
         for (; work < num_work && ok; work += work_step) {
-            const int64_t tile = work / p.splits;
-            const int split = (int)(work - tile * p.splits);
-            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+            const WorkItem tc = next_item;
+            const int split = tc.split;
             const int64_t m0 = (int64_t)tc.m * (BM * CG) + (int64_t)cta_rank * BM, n0 = (int64_t)tc.n * BN;
             const int64_t row0 = m0 + ew * 32;
             const int64_t row = row0 + lane;
@@ -363,13 +364,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     st_shared_v4(cs_grp_addr + (uint32_t)lane * 32u + 16u, hi.x, hi.y, hi.z, hi.w);
                     __syncwarp();
                 }
-                // request the scales of this group's next tile
-                next_row_scale = 0.0f;
-                if (work + work_step < num_work) {
-                    const int64_t r = row_of(work + work_step);
-                    if (r < p.M) next_row_scale = load_scale(p.scale_a, p.scale_dtype, r);
-                    next_cs_packed = load_col_scales8(next_cs, p, col0_of(work + work_step) + lane * 8);
-                }
             }
 
             const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(grp * BN);
@@ -378,7 +372,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    if constexpr (CG == 2) mbar_arrive_cluster(empty_bar_addr);   // the pair's accumulator: both CTAs report to the leader
+                    if constexpr (CG == 2) mbar_arrive_cluster_relaxed(empty_bar_addr);   // the pair's accumulator: both CTAs report to the leader
                     else mbar_arrive(empty_bar_addr);
                 }
             };
@@ -411,6 +405,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if constexpr (LAST && EPI == EPI_ROWCOL) {
 #pragma unroll
                     for (int q = 0; q < 8; ++q) csr[q] = *reinterpret_cast<const float4*>(cs_grp + c * 32 + q * 4);
+                    // the arrive below carries no memory ordering when it crosses to the peer CTA: make it
+                    // wait for the scale values themselves (loads of one thread from shared memory return in order)
+                    asm volatile("" ::"f"(csr[0].x), "f"(csr[1].x), "f"(csr[2].x), "f"(csr[3].x), "f"(csr[4].x), "f"(csr[5].x),
+                                 "f"(csr[6].x), "f"(csr[7].w)
+                                 : "memory");
                     release_acc();
                 }
                 // eight output values as 32-bit words: 8 words (4-byte outputs) or 4 (bf16 pairs)
@@ -509,6 +508,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const bool scales_in_smem = EPI == EPI_ROWCOL && p.splits == 1;
             uint32_t ra[32], rb[32];
             tmem_ld_32x32(t_row, ra);
+            // while that load is in flight: find this group's next tile and request its scales
+            if (work + work_step < num_work) {
+                next_item = locate(work + work_step);
+                if constexpr (EPI == EPI_ROWCOL) request_scales(next_item);
+            }
 #pragma unroll 1
             for (int c = 0; c < CHUNKS - 2; c += 2) {
                 tmem_ld_wait();
@@ -666,7 +670,7 @@ void choose_splits(int64_t M, int64_t N, int64_t K, int cg, int* splits, int* kb
 // block.
 int pick_cta_group(int64_t M, int64_t K) {
     int cg = g_forced_cta_group;
-    if (cg != 1 && cg != 2) cg = (M > BM && K > 1024) ? 2 : 1;
+    if (cg != 1 && cg != 2) cg = (M > BM && K >= 512) ? 2 : 1;
     return cg;
 }
 
@@ -731,6 +735,7 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
     if (int rc = device_status_ptr(&p.status)) return rc;
 
     const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + BN - 1) / BN) * p.splits;  // work items
+    QT_REQUIRE(tiles < (1ll << 30), "gemm: %lld work items exceed the kernel's 32-bit tile index", (long long)tiles);
     const uint32_t idesc = is_i8 ? make_idesc(2, 1, 1, a_mn, b_mn, BM * cg, BN)
                                  : make_idesc(1, fp8_format(a_dtype), fp8_format(b_dtype), a_mn, b_mn, BM * cg, BN);
 #define QT_DISPATCH(KIND, EPI)                                                                               \

@@ -270,6 +270,7 @@ extern "C" int qt_tile_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     QT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "tile_scaled_mm: negative dimension");
     QT_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "tile_scaled_mm: dimension exceeds 2^31");
+    QT_REQUIRE(((M + TBM - 1) / TBM) * ((N + TBN - 1) / TBN) < (1ll << 31), "tile_scaled_mm: too many output tiles for the 32-bit tile index");
     const bool is_i8 = a_dtype == QT_I8 && b_dtype == QT_I8;
     const bool is_f8 = (a_dtype == QT_E4M3 || a_dtype == QT_E5M2) && (b_dtype == QT_E4M3 || b_dtype == QT_E5M2);
     QT_REQUIRE(is_i8 || is_f8, "tile_scaled_mm: operands must both be int8 or both be fp8 (got %d, %d)", a_dtype, b_dtype);

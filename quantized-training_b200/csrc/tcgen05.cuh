@@ -122,6 +122,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// The same without memory ordering: a release at cluster scope waits until every earlier write of the
+// thread is visible to the whole cluster, which the TMEM hand-over does not need (tcgen05.wait::ld has
+// already completed the reads, and tcgen05.fence::before_thread_sync orders them before this arrive).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 // TMA load whose completion bytes are credited to an mbarrier of the CTA pair's leader.
 // No multicast: each CTA fetches its own tile into its own shared memory.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
@@ -218,13 +224,16 @@ struct TileCoord {
 };
 // Grouped rasterisation: GROUP_M row-tiles sweep all column-tiles before moving down, so the CTAs
 // that run together share A and B panels in L2.
-__device__ __forceinline__ TileCoord tile_coord(int64_t tile, int tiles_m, int tiles_n) {
-    const int64_t width = (int64_t)GROUP_M * tiles_n;
-    const int group = (int)(tile / width);
-    const int first_m = group * GROUP_M;
-    const int group_size = (tiles_m - first_m) < GROUP_M ? (tiles_m - first_m) : GROUP_M;
-    const int in_group = (int)(tile % width);
-    return TileCoord{first_m + in_group % group_size, in_group / group_size};
+// 32-bit arithmetic throughout (the host checks that the tile count fits): 64-bit divisions are
+// emulated and cost hundreds of cycles each, on the critical path of every role once per tile.
+__device__ __forceinline__ TileCoord tile_coord(uint32_t tile, int tiles_m, int tiles_n) {
+    const uint32_t width = (uint32_t)GROUP_M * (uint32_t)tiles_n;
+    const uint32_t group = tile / width;
+    const uint32_t in_group = tile - group * width;
+    const int first_m = (int)group * GROUP_M;
+    const uint32_t group_size = (uint32_t)((tiles_m - first_m) < GROUP_M ? (tiles_m - first_m) : GROUP_M);
+    const uint32_t col = in_group / group_size;
+    return TileCoord{first_m + (int)(in_group - col * group_size), (int)col};
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

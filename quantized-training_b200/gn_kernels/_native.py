@@ -103,7 +103,14 @@ def check(rc: int) -> None:
         raise RuntimeError(f"qt_b200 error {rc}: {msg}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(device: torch.device) -> int:
+    """cudaStream_t of torch's current stream on `device` (the raw-handle query skips building a
+    torch.cuda.Stream object: this is on the path of every kernel launch)."""
+    if _raw_stream is not None:
+        return _raw_stream(device.index if device.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(device).cuda_stream
 
 

@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M = N = K")
+    ap.add_argument("--mnk", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
+                    help="a non-square problem for the gemm workload (profiling the layer shapes; the headline is --size 8192)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gemm", choices=["gemm", "train-470m", "train-1b"],
                     help="gemm: the headline quantize + scaled GEMM step; train-*: one INT8 mixed-precision Llama step (tok/s)")
@@ -345,24 +347,25 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     S = args.size
-    assert S % world == 0, "the weight rows must split evenly over the ranks"
-    shard_rows = S // world
+    gM, gN, gK = tuple(args.mnk) if args.mnk else (S, S, S)
+    assert gN % world == 0, "the weight rows must split evenly over the ranks"
+    shard_rows = gN // world
     torch.manual_seed(2024 + rank)
-    A_host = torch.randn(S, S).bfloat16().pin_memory()
+    A_host = torch.randn(gM, gK).bfloat16().pin_memory()
     torch.manual_seed(2024)  # the weight is the same tensor on every rank; each rank owns a row slice
-    W_full_host = (torch.randn(S, S) * 0.02).bfloat16()
+    W_full_host = (torch.randn(gN, gK) * 0.02).bfloat16()
     W_host = W_full_host[rank * shard_rows:(rank + 1) * shard_rows].contiguous().pin_memory()
     del W_full_host
     A = A_host.to(dev)
     W = W_host.to(dev)
-    out_host = torch.empty((S, S), dtype=torch.bfloat16).pin_memory()
+    out_host = torch.empty((gM, gN), dtype=torch.bfloat16).pin_memory()
 
     # Gathered weight, double-buffered: with more than one GPU the quantize + all-gather of the NEXT
     # step's weight runs on a side stream under the current step's activation quantize and GEMM (the
     # prefetch FSDP2 does for the next layer), so every step still holds exactly one shard quantize,
     # one all-gather, one activation quantize and one GEMM.
-    wq_full = [torch.empty((S, S), dtype=torch.int8, device=dev) for _ in range(2)]
-    ws_full = [torch.empty((S, 1), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    wq_full = [torch.empty((gN, gK), dtype=torch.int8, device=dev) for _ in range(2)]
+    ws_full = [torch.empty((gN, 1), dtype=torch.bfloat16, device=dev) for _ in range(2)]
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
     gathered = [torch.cuda.Event() for _ in range(2)]   # buffer b holds a complete gathered weight
     consumed = [torch.cuda.Event() for _ in range(2)]   # the GEMM that read buffer b has finished
@@ -533,7 +536,7 @@ def main():
             dist.destroy_process_group()
         return
 
-    flops = 2.0 * S ** 3
+    flops = 2.0 * gM * gN * gK
     value = world * flops / (ms_per_step * 1e-3) / 1e12
     e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
     hbm_peak, bf16_peak, peak_kind = measured_peaks()
@@ -541,10 +544,10 @@ def main():
     achieved = flops / (gemm_ms * 1e-3) / 1e12
     # dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of this kernel, from the ncu
     # capture summarised in profiles/gemm_scaled_int8_8192.md
-    traffic = 461.3e6 if S == 8192 else None
+    traffic = 461.3e6 if (gM, gN, gK) == (8192, 8192, 8192) else None
 
     cpu_baseline = None
-    if not args.no_cpu_baseline and world == 1:
+    if not args.no_cpu_baseline and world == 1 and gM == gN == gK:
         tops, threads, dt = time_cpu_path(S, 3 if S >= 8192 else 5, 1)
         cpu_baseline = {"value": tops, "unit": UNIT, "cores": threads, "kind": "port",
                         "sample": f"3 full passes of the {S}^3 workload after 1 warm-up ({dt:.2f} s each), torch eager quantize + torch._int_mm on the host"}
@@ -554,9 +557,9 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
         "config": {
-            "workload": f"rowwise dynamic INT8 quantize (activation + weight shard) + scaled INT8 GEMM A@B.T, M=N=K={S} per GPU, bf16 in/out",
+            "workload": f"rowwise dynamic INT8 quantize (activation + weight shard) + scaled INT8 GEMM A@B.T, M={gM} N={gN} K={gK} per GPU, bf16 in/out",
             "weight_all_gather": "int8 rows + bf16 scales over NCCL, prefetched one step ahead on a side stream" if world > 1 else "none (1 GPU)",
-            "l2": "inputs larger than L2 (2 x 134 MB bf16 in, 2 x 67 MB int8 operands, 134 MB out per step)",
+            "l2": f"inputs larger than L2 ({(gM + gN) * gK * 2 / 1e6:.0f} MB bf16 in, {(gM + gN) * gK / 1e6:.0f} MB int8 operands, {gM * gN * 2 / 1e6:.0f} MB out per step)",
             "value_is": "2*M*N*K * n_gpus / step time; the step includes both quantize kernels",
         },
         "gemm_only": {"tops": achieved, "ms": gemm_ms, "ms_median": gemm_ms_median, "ms_max": max(e0.elapsed_time(e1) for e0, e1 in gemm_events)},

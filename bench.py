@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--mnk", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
                     help="a non-square problem for the gemm workload (profiling the layer shapes; the headline is --size 8192)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "train-470m", "train-1b"],
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "quantize", "train-470m", "train-1b"],
                     help="gemm: the headline quantize + scaled GEMM step; train-*: one INT8 mixed-precision Llama step (tok/s)")
     ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp"], help="train-* workloads with --gpus > 1: DDP, or FSDP2 with the INT8 weight all-gather")
     ap.add_argument("--quantize", default="mixed_precision", choices=["mixed_precision", "none", "int8_quantized_training", "bitnet"],
@@ -317,6 +317,54 @@ def run_train(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_quantize(args):
+    """The HBM-bound kernels of the path on one [M, K] bf16 tensor (--mnk M N K; N is ignored; default
+    32768 x 2048, the activation of a 2048-wide layer at 32768 tokens): one JSON line per kernel with
+    its algorithmic bytes, CUDA-event time (median over --steps launches, a 1 GiB memset between
+    launches so no input is left in L2) and the fraction of the measured HBM copy bandwidth."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    import gn_kernels as gk
+
+    dev = torch.device("cuda", 0)
+    M, _, K = tuple(args.mnk) if args.mnk else (32768, 0, 2048)
+    x = torch.randn(M, K, device=dev).bfloat16()
+    flush = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    hbm_peak, _, peak_kind = measured_peaks()
+    colmax = gk.col_absmax(x)
+    RC = M * K
+    cases = [
+        ("rowwise_kernel int8", lambda: gk.quantize_rowwise(x), 2 * RC + RC + 2 * M),
+        ("rowwise_kernel int8 stochastic", lambda: gk.quantize_rowwise(x, torch.int8, True), 2 * RC + RC + 2 * M),
+        ("rowwise_kernel e4m3", lambda: gk.quantize_rowwise(x, torch.float8_e4m3fn), 2 * RC + RC + 2 * M),
+        ("rowwise_kernel int8 + column absmax", lambda: gk.quantize_rowwise_colabsmax(x), 2 * RC + RC + 2 * M + 4 * K),
+        ("col_absmax_bf16_kernel", lambda: gk.col_absmax(x), 2 * RC + 4 * K),
+        ("colwise_t_kernel int8 (given column absmax)", lambda: gk.quantize_colwise_t(x, col_absmax_=colmax), 2 * RC + RC + 4 * K + 2 * K),
+        ("tile_1x128_kernel int8", lambda: gk.quantize_tile(x, (1, 128)), 2 * RC + RC + 2 * RC // 128),
+        ("tile_128x128_kernel int8", lambda: gk.quantize_tile(x, (128, 128)), 2 * RC + RC + 2 * RC // 16384),
+    ]
+    steps = max(args.steps, 5)
+    for name, fn, nbytes in cases:
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        times = []
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        print(json.dumps({"metric": "quantize_gbs", "kernel": name, "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps,
+                          "ms_per_launch": ms, "higher_is_better": True, "dtype": "bf16->int8/fp8", "data": "synthetic",
+                          "config": {"workload": f"[{M}, {K}] bf16 N(0,1)", "l2": "1 GiB memset between launches"},
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                                       "peak_is": f"{peak_kind} STREAM-style copy", "algorithmic_bytes": nbytes}}), flush=True)
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -325,6 +373,10 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "quantize":
+        if rank == 0:
+            run_quantize(args)
         return
     if args.workload != "gemm":
         run_train(args, rank, local_rank, world)

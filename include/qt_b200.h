@@ -260,6 +260,7 @@ int qt_unpack_i2(const void* packed, int64_t numel_packed, void* out, void* stre
  * beta1/beta2 are doubles because the reference forms the lerp weight (1 - beta) in double before
  * it is rounded to fp32. bias_correction1 = 1 - beta1^step and sqrt_bias_correction2 =
  * sqrt(1 - beta2^step) are computed by the caller in fp32. exp_avg / exp_avg_sq are bf16 [numel].
+ * Tensors are contiguous; 16-byte aligned ones move four elements per access, others one (same values).
  * replaces: other_optim/bf16_sr.py:78-124 (adamw), called per parameter from AdamWBF16SR.step :30-75.
  */
 int qt_adamw_bf16_sr(void* p, int p_dtype, const void* grad, int grad_dtype, void* exp_avg,

@@ -25,6 +25,7 @@ struct AdamParams {
     float lr_wd, lr, w1, w2, bc1, sqrt_bc2, eps;
     int stochastic;
     uint64_t seed, offset;
+    int vec;  // p and g are 16-byte, m and v 8-byte aligned: four elements move as one vector
 };
 
 template <typename T>
@@ -63,10 +64,10 @@ __device__ __forceinline__ void adam_quad(const AdamParams& a, int64_t q) {
         Philox4 r = {0, 0, 0, 0};
         if (a.stochastic) r = philox4x32_10((uint64_t)q, a.offset, a.seed);
         const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
-        if (i0 + 4 <= a.n) {
+        if (a.vec && i0 + 4 <= a.n) {
             float pv[4], gv[4], mv[4], vv[4];
-            // 4 consecutive elements: 8-byte (bf16) or 16-byte (fp32) accesses; tensors from the
-            // caching allocator are at least 16-byte aligned and i0 is a multiple of 4
+            // 4 consecutive elements: 8-byte (bf16) or 16-byte (fp32) accesses (the host checked the
+            // alignment of this tensor; views at odd offsets take the element path below)
             if constexpr (sizeof(PT) == 2) {
                 const uint2 raw = *reinterpret_cast<const uint2*>(p + i0);
                 pv[0] = __uint_as_float(raw.x << 16); pv[1] = __uint_as_float(raw.x & 0xFFFF0000u);
@@ -153,6 +154,7 @@ struct MultiTable {
     __nv_bfloat16* v[kMaxTensors];
     int64_t numel[kMaxTensors];
     uint32_t tensor_index[kMaxTensors];
+    uint8_t vec[kMaxTensors];
     uint32_t chunk_begin[kMaxTensors + 1];   // first block of each tensor; [n] = grid size
     int n;
 };
@@ -168,6 +170,7 @@ __global__ void __launch_bounds__(kThreads) adamw_multi_kernel(const __grid_cons
     AdamParams a = proto;
     a.p = tab.p[t]; a.g = tab.g[t]; a.m = tab.m[t]; a.v = tab.v[t]; a.n = tab.numel[t];
     a.offset = proto.offset + tab.tensor_index[t];
+    a.vec = tab.vec[t];
     const int64_t q_begin = (int64_t)(blockIdx.x - tab.chunk_begin[t]) * (kChunk / 4);
     const int64_t n4 = (a.n + 3) / 4;
     const int64_t q_end = q_begin + kChunk / 4 < n4 ? q_begin + kChunk / 4 : n4;
@@ -190,8 +193,6 @@ extern "C" int qt_adamw_bf16_sr(void* p, int p_dtype, const void* grad, int grad
     QT_REQUIRE(!stochastic || p_dtype == QT_BF16, "adamw: stochastic rounding applies to bf16 parameters only");
     if (numel == 0) return QT_OK;
     QT_REQUIRE(p && grad && exp_avg && exp_avg_sq, "adamw: null pointer");
-    QT_REQUIRE(aligned_to(p, 16) && aligned_to(grad, 16) && aligned_to(exp_avg, 8) && aligned_to(exp_avg_sq, 8),
-               "adamw: tensors must be 16-byte aligned");
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     AdamParams a;
     a.p = p; a.g = grad; a.m = reinterpret_cast<__nv_bfloat16*>(exp_avg); a.v = reinterpret_cast<__nv_bfloat16*>(exp_avg_sq);
@@ -201,6 +202,7 @@ extern "C" int qt_adamw_bf16_sr(void* p, int p_dtype, const void* grad, int grad
     a.w1 = (float)(1.0 - beta1); a.w2 = (float)(1.0 - beta2);
     a.bc1 = bias_correction1; a.sqrt_bc2 = sqrt_bias_correction2; a.eps = eps;
     a.stochastic = stochastic; a.seed = seed; a.offset = offset;
+    a.vec = aligned_to(p, 16) && aligned_to(grad, 16) && aligned_to(exp_avg, 8) && aligned_to(exp_avg_sq, 8);
     const int64_t want = ((numel + 3) / 4 + kThreads - 1) / kThreads;
     const int64_t cap = (int64_t)num_sms() * 16;
     const int grid = (int)(want < cap ? want : cap);
@@ -248,8 +250,6 @@ extern "C" int qt_adamw_bf16_sr_multi(int n_tensors, void* const* p, const void*
         QT_REQUIRE(numel[t] >= 0, "adamw_multi: negative numel for tensor %d", t);
         if (numel[t] == 0) continue;
         QT_REQUIRE(p[t] && grad[t] && exp_avg[t] && exp_avg_sq[t], "adamw_multi: null pointer for tensor %d", t);
-        QT_REQUIRE(aligned_to(p[t], 16) && aligned_to(grad[t], 16) && aligned_to(exp_avg[t], 8) && aligned_to(exp_avg_sq[t], 8),
-                   "adamw_multi: tensor %d must be 16-byte aligned", t);
         const int64_t chunks = (numel[t] + kChunk - 1) / kChunk;
         QT_REQUIRE(chunks < (1ll << 30), "adamw_multi: tensor %d is too large", t);
         // a launch holds at most kMaxTensors tensors and 2^31 - 1 blocks
@@ -260,6 +260,7 @@ extern "C" int qt_adamw_bf16_sr_multi(int n_tensors, void* const* p, const void*
         tab.p[slot] = p[t]; tab.g[slot] = grad[t];
         tab.m[slot] = reinterpret_cast<__nv_bfloat16*>(exp_avg[t]); tab.v[slot] = reinterpret_cast<__nv_bfloat16*>(exp_avg_sq[t]);
         tab.numel[slot] = numel[t]; tab.tensor_index[slot] = (uint32_t)t;
+        tab.vec[slot] = aligned_to(p[t], 16) && aligned_to(grad[t], 16) && aligned_to(exp_avg[t], 8) && aligned_to(exp_avg_sq[t], 8);
         tab.chunk_begin[slot + 1] = tab.chunk_begin[slot] + (uint32_t)chunks;
     }
     return flush();

@@ -85,7 +85,7 @@ def test_quantize_int8_matches_reference_fixtures(golden_dir, name):
         assert q.shape == x.shape and s.shape == g[f"{name}_dim{dim}_scale"].shape
 
 
-@pytest.mark.parametrize("shape", [(1024, 1024), (333, 777), (4096, 256), (130, 70), (128, 64), (1, 64), (257, 8), (5000, 1024)])
+@pytest.mark.parametrize("shape", [(1024, 1024), (333, 777), (4096, 256), (130, 70), (128, 64), (1, 64), (257, 8), (5000, 1024), (2560, 192), (128 * 37, 64)])
 def test_colwise_transposed_matches_oracle(shape):
     x = randn_bf16(shape, seed=shape[0] + shape[1])
     qt, s = gn_kernels.quantize_colwise_t(x)
@@ -180,6 +180,19 @@ def test_tile_quantize_matches_oracle():
         q8, s8 = gn_kernels.quantize_tile(x, (1, 128), out_dtype=torch.float8_e4m3fn)
         oq8, os8 = om.quantize_tile(values_of(x), (1, 128), out="e4m3")
         np.testing.assert_array_equal(bits_of(q8), oq8)
+
+
+@pytest.mark.parametrize("shape", [(256, 128), (130, 70)])
+def test_colwise_saturates_when_the_given_absmax_is_too_small(shape):
+    """The column absmax is the caller's: values beyond it saturate at the int8 range (whole-tile and
+    ragged shapes take different kernels)."""
+    x = randn_bf16(shape, seed=7)
+    small = gn_kernels.col_absmax(x) * 0.25
+    qt, st = gn_kernels.quantize_colwise_t(x, col_absmax_=small)
+    scale = (small.cpu() / 127).view(-1, 1)
+    want = torch.clamp(torch.round(x.float().cpu().T / scale.clamp_min(1e-12)), -128, 127).to(torch.int8)
+    assert torch.equal(qt.cpu(), want)
+    assert (qt == 127).any() and (qt == -128).any()
 
 
 def test_full_size_properties():

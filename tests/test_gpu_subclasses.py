@@ -318,6 +318,17 @@ def test_adamw_multi_equals_per_tensor_calls(p_dtype, g_dtype, sr):
         assert torch.equal(got, want)
     assert not torch.equal(ps[5], mk(sizes[5], p_dtype))  # the update did something
 
+    # views that start at an odd element (2- or 4-byte aligned only) take the element path: same values
+    n = 5000
+    base = [mk(n + 1, dt, sc) for dt, sc in ((p_dtype, 1.0), (g_dtype, 0.1), (torch.bfloat16, 0.01), (torch.bfloat16, 0.01))]
+    base[3].abs_()
+    odd = [t[1:] for t in base]
+    even = [t[1:].clone() for t in base]
+    adamw_multi([odd[0]], [odd[1]], 3.0, [odd[2]], [odd[3]], *hyper, key=(5, 9))
+    adamw(even[0], even[1], torch.tensor(3.0), even[2], even[3], *hyper, key=(5, 9))
+    for got, want in zip(odd, even):
+        assert torch.equal(got, want)
+
 
 def test_optimizer_class_trains_a_converted_model():
     torch.manual_seed(0)

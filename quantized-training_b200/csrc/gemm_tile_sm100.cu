@@ -155,9 +155,9 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int64_t row = m0 + ew * 32 + lane;
             const int64_t sa_row = (row < p.M ? row : p.M - 1) / p.qm;
             const int64_t sb_col = (n0 + half * HN < p.N ? n0 + half * HN : n0) / p.qn;
-            float acc[HN];
+            float2 acc2[HN / 2];   // accumulators in pairs: the promotion uses packed fp32x2 instructions
 #pragma unroll
-            for (int j = 0; j < HN; ++j) acc[j] = 0.0f;
+            for (int j = 0; j < HN / 2; ++j) acc2[j] = make_float2(0.0f, 0.0f);
             // scale of K block 0, then always one block ahead
             float s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0) * load_scale(p.scale_b, p.scale_dtype, sb_col * p.sb_s1);
             for (int kb = 0; kb < num_kb; ++kb) {
@@ -170,16 +170,20 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 tcgen05_fence_after();
                 const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(buf * TBN + half * HN);
                 // 16-column chunks through two register buffers: the next TMEM load is in flight while
-                // the current chunk is promoted. For int8 the partial of one 128-element K block is below
-                // 2^22 in magnitude, so adding it to the bit pattern of 1.5 * 2^23 and subtracting that
-                // constant converts it exactly without the (slower) integer-to-float instruction.
+                // the current chunk is promoted. The fp32 pipe bounds this loop, so the int8 partial is
+                // converted by the integer-to-float instruction (another pipe) and the multiply-add is the
+                // packed fp32x2 form (half the issue slots); measured 1.37 -> 1.56 POPS at 8192^3 against a
+                // magic-number conversion that spent a second fp32 operation per element.
+                const float2 s2 = make_float2(s, s);
                 auto promote = [&](const uint32_t (&r)[16], int c) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float x;
-                        if constexpr (KIND == 0) x = __fsub_rn(__uint_as_float(r[j] + 0x4B400000u), 12582912.0f);
-                        else x = __uint_as_float(r[j]);
-                        acc[c * 16 + j] = __fmaf_rn(x, s, acc[c * 16 + j]);
+                    for (int j = 0; j < 16; j += 2) {
+                        float2 x;
+                        if constexpr (KIND == 0)
+                            x = make_float2((float)(int32_t)r[j], (float)(int32_t)r[j + 1]);
+                        else
+                            x = make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                        acc2[c * 8 + j / 2] = __ffma2_rn(x, s2, acc2[c * 8 + j / 2]);
                     }
                 };
                 uint32_t ra[16], rb[16];
@@ -199,6 +203,9 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (++buf == T_BUFS) { buf = 0; buf_phase ^= 1u; }
             }
             if (!ok) break;
+            float acc[HN];
+#pragma unroll
+            for (int j = 0; j < HN / 2; ++j) { acc[2 * j] = acc2[j].x; acc[2 * j + 1] = acc2[j].y; }
             if (row < p.M) {
                 const int64_t nh = n0 + half * HN;
                 if (p.scale_dtype == QT_BF16) {

@@ -55,7 +55,11 @@ def parse_args():
     ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp"], help="train-* workloads with --gpus > 1: DDP, or FSDP2 with the INT8 weight all-gather")
     ap.add_argument("--quantize", default="mixed_precision", choices=["mixed_precision", "none", "int8_quantized_training", "bitnet"],
                     help="train-* workloads: which weight subclass the decoder's Linear layers get (none = bf16 baseline)")
-    ap.add_argument("--sm-margin", type=int, default=8, help="SMs the GEMM leaves to the concurrent all-gather when --gpus > 1")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="--gpus > 1: 'fused' = one kernel quantizes the weight shard and stores it into every rank's gathered "
+                         "buffer over NVLink (symmetric memory); 'nccl' = quantize, then NCCL all-gather")
+    ap.add_argument("--sm-margin", type=int, default=None,
+                    help="SMs the GEMM leaves free when --gpus > 1 (default: 8 beside NCCL's all-gather kernel, 0 with the fused gather)")
     ap.add_argument("--no-clock-sampler", action="store_true", help="do not run nvidia-smi beside the timed region")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0, help="keep warming up at least this long (0 under a profiler)")
     return ap.parse_args()
@@ -389,8 +393,11 @@ def main():
     from gn_kernels import _native
 
     _native.load()
+    fused_gather = world > 1 and args.gather == "fused"
+    if args.sm_margin is None:
+        # NCCL's all-gather kernel needs SMs beside the persistent GEMM; the fused form launches no collective kernel
+        args.sm_margin = 0 if (world == 1 or fused_gather) else 8
     if world > 1:
-        # leave a few SMs to the all-gather that runs beside the persistent GEMM
         _native.check(_native.load().qt_set_gemm_sm_margin(args.sm_margin))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -416,8 +423,14 @@ def main():
     # step's weight runs on a side stream under the current step's activation quantize and GEMM (the
     # prefetch FSDP2 does for the next layer), so every step still holds exactly one shard quantize,
     # one all-gather, one activation quantize and one GEMM.
-    wq_full = [torch.empty((gN, gK), dtype=torch.int8, device=dev) for _ in range(2)]
-    ws_full = [torch.empty((gN, 1), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    if fused_gather:
+        from gn_kernels.sharded import SymmetricRowGather
+        sym = SymmetricRowGather(gN, gK, device=dev, buffers=2)
+        wq_full, ws_full = sym.q, sym.scale
+    else:
+        sym = None
+        wq_full = [torch.empty((gN, gK), dtype=torch.int8, device=dev) for _ in range(2)]
+        ws_full = [torch.empty((gN, 1), dtype=torch.bfloat16, device=dev) for _ in range(2)]
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
     gathered = [torch.cuda.Event() for _ in range(2)]   # buffer b holds a complete gathered weight
     consumed = [torch.cuda.Event() for _ in range(2)]   # the GEMM that read buffer b has finished
@@ -430,11 +443,19 @@ def main():
         comm_stream.wait_stream(torch.cuda.current_stream(dev))   # w_dev is ready
         comm_stream.wait_event(consumed[b])
         with torch.cuda.stream(comm_stream):
-            wq, ws = gn_kernels.quantize_rowwise(w_dev)
-            dist.all_gather_into_tensor(wq_full[b], wq)
-            dist.all_gather_into_tensor(ws_full[b], ws)
-            wq.record_stream(comm_stream)
-            ws.record_stream(comm_stream)
+            if sym is not None:
+                # The first fence: every rank's GEMM that last read buffer b has finished (each rank is
+                # behind its own `consumed[b]` here), so peers may overwrite it. The second: every rank's
+                # new rows have landed before anybody reads the buffer.
+                sym.fence()
+                sym.quantize_scatter(w_dev, b)
+                sym.fence()
+            else:
+                wq, ws = gn_kernels.quantize_rowwise(w_dev)
+                dist.all_gather_into_tensor(wq_full[b], wq)
+                dist.all_gather_into_tensor(ws_full[b], ws)
+                wq.record_stream(comm_stream)
+                ws.record_stream(comm_stream)
             gathered[b].record(comm_stream)
         state["next"] = 1 - b
         return b
@@ -610,7 +631,10 @@ def main():
         "dtype": "int8", "data": "synthetic",
         "config": {
             "workload": f"rowwise dynamic INT8 quantize (activation + weight shard) + scaled INT8 GEMM A@B.T, M={gM} N={gN} K={gK} per GPU, bf16 in/out",
-            "weight_all_gather": "int8 rows + bf16 scales over NCCL, prefetched one step ahead on a side stream" if world > 1 else "none (1 GPU)",
+            "weight_all_gather": ("none (1 GPU)" if world == 1 else
+                                  "fused into the quantize kernel: int8 rows + bf16 scales stored into every rank's buffer over NVLink (peer-to-peer stores, symmetric memory), one step ahead on a side stream" if fused_gather else
+                                  "int8 rows + bf16 scales over NCCL, prefetched one step ahead on a side stream"),
+            "sm_margin": args.sm_margin,
             "l2": f"inputs larger than L2 ({(gM + gN) * gK * 2 / 1e6:.0f} MB bf16 in, {(gM + gN) * gK / 1e6:.0f} MB int8 operands, {gM * gN * 2 / 1e6:.0f} MB out per step)",
             "value_is": "2*M*N*K * n_gpus / step time; the step includes both quantize kernels",
         },

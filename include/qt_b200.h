@@ -75,6 +75,23 @@ int qt_quantize_rowwise(const void* x, int x_dtype, int64_t rows, int64_t cols, 
                         int stochastic, uint64_t seed, uint64_t offset, void* stream);
 
 /*
+ * qt_quantize_rowwise (round-half-even) fused with the all-gather of a row-sharded tensor: the rows of
+ * this shard and their scales are written at row offset dst_row0 into n_dst gathered buffers
+ * q_dst[d] ([total_rows, cols] contiguous) and scale_dst[d] ([total_rows]) -- this GPU's own buffer and
+ * its peers' (device pointers into peer memory mapped into this process, e.g. the buffers of a symmetric
+ * allocation; plain peer-to-peer stores over NVLink, no multicast). q_dst and scale_dst are HOST arrays
+ * of n_dst <= 16 device pointers. The caller orders the consumers after every rank's kernel (a barrier
+ * across the ranks on the same streams). bf16 input, rows 16-byte aligned, cols a multiple of 8 and at
+ * most 32768; otherwise QT_ERR_UNSUPPORTED (quantize locally and use a library all-gather).
+ * replaces: quantize_int8 of the FSDP2 shard followed by the all-gather of the reference's
+ * fsdp_pre_all_gather (subclasses/bitnet.py:83-90 is its only instance); no kernel of the reference
+ * writes to peer memory.
+ */
+int qt_quantize_rowwise_scatter(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                                int n_dst, void* const* q_dst, void* const* scale_dst, int64_t dst_row0,
+                                int q_dtype, int scale_dtype, float eps, void* stream);
+
+/*
  * Same as qt_quantize_rowwise and, in the same pass over x, the per-column absolute maximum
  * col_absmax[c] = max_r |x[r,c]| (fp32, [cols]). col_absmax is zeroed by this call (on the
  * stream) before the kernel runs. Lets a later qt_quantize_colwise_t skip its reduction pass.

@@ -225,6 +225,8 @@ __device__ __forceinline__ void store_bytes8(uint8_t* q, int64_t idx, int64_t va
 
 // ---- row-wise -------------------------------------------------------------------------------
 
+constexpr int kMaxScatter = 16;   // destinations of the scatter form (GPUs of one NVLink domain)
+
 struct RowwiseParams {
     const void* x;
     int64_t rows, cols, stride;
@@ -241,6 +243,13 @@ struct RowwiseParams {
     const __nv_bfloat16* t1;
     const __nv_bfloat16* t2;
     float value;
+    // scatter form (SCATTER): the quantized rows and scales of this shard are written at row offset
+    // `dst_row0` into n_dst gathered buffers -- this GPU's own and its peers' (peer-to-peer stores) --
+    // so the quantize and the all-gather of a row-sharded weight are one kernel
+    uint8_t* q_dst[kMaxScatter];
+    void* scale_dst[kMaxScatter];
+    int n_dst;
+    int64_t dst_row0;
 };
 
 // ---- packed bf16 helpers -----------------------------------------------------------------------
@@ -352,7 +361,7 @@ __device__ __forceinline__ uint4 updated_vec8(uint2 qb, float s, const uint4& a,
 // With UPD != 0 the kernel re-quantizes an int8 weight in place: the "row" is the updated weight formed
 // by updated_vec8 from q, scale and the operand tensors; q and scale are then overwritten (each row
 // is complete in registers before its bytes are stored, and a prefetched row is a different row).
-template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0>
+template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0, bool SCATTER = false>
 __global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1)))
 rowwise_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;  // rows per CTA per iteration
@@ -443,7 +452,12 @@ rowwise_kernel(const RowwiseParams p) {
 
         const float scale = div_rn(amax, qmax);
         const Divider<false> div(fmaxf(scale, p.eps));
-        if (valid && t == 0) store_scale(p.scale, p.scale_dtype, row, scale);
+        if constexpr (SCATTER) {
+            if (valid && t == 0)
+                for (int d = 0; d < p.n_dst; ++d) store_scale(p.scale_dst[d], p.scale_dtype, p.dst_row0 + row, scale);
+        } else {
+            if (valid && t == 0) store_scale(p.scale, p.scale_dtype, row, scale);
+        }
 
         uint8_t* qrow = p.q + row * p.cols;
 #pragma unroll
@@ -451,7 +465,12 @@ rowwise_kernel(const RowwiseParams p) {
             const int col = (i * TPR + t) * 8;
             if (valid && col < p.cols) {
                 const uint2 bytes = quantize_vec8<SR>(cur[i], div, p.q_dtype, SR ? row * p.cols + col : 0, p.seed, p.offset);
-                *reinterpret_cast<uint2*>(qrow + col) = bytes;
+                if constexpr (SCATTER) {
+                    const int64_t at = (p.dst_row0 + row) * p.cols + col;
+                    for (int d = 0; d < p.n_dst; ++d) *reinterpret_cast<uint2*>(p.q_dst[d] + at) = bytes;
+                } else {
+                    *reinterpret_cast<uint2*>(qrow + col) = bytes;
+                }
             }
         }
 
@@ -550,14 +569,14 @@ __global__ void __launch_bounds__(kThreads) rowwise_generic_kernel(const Rowwise
 // of 4 or 8 constrain CTA placement enough to slow the streaming loop by a quarter (measured).
 constexpr int kClusterSize = 2;
 
-template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0>
+template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0, bool SCATTER = false>
 int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
     constexpr int RPC = kThreads / TPR;
     constexpr int CTAS_PER_SM = (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1));
     const int64_t want = (p.rows + RPC - 1) / RPC;
     const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
     int64_t grid = want < cap ? want : cap;
-    auto kfn = rowwise_kernel<TPR, VPT, COLABS, SR, UPD>;
+    auto kfn = rowwise_kernel<TPR, VPT, COLABS, SR, UPD, SCATTER>;
     if constexpr (COLABS) {
         constexpr int csize = kClusterSize;
         grid = (grid + csize - 1) / csize * csize;
@@ -581,17 +600,17 @@ int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
     return QT_OK;
 }
 
-template <bool COLABS, bool SR, int UPD = 0>
+template <bool COLABS, bool SR, int UPD = 0, bool SCATTER = false>
 int launch_rowwise_bf16(const RowwiseParams& p, cudaStream_t stream) {
     const int64_t c = p.cols;
-    if (c <= 256) return launch_rowwise_cfg<32, 1, COLABS, SR, UPD>(p, stream);
-    if (c <= 512) return launch_rowwise_cfg<32, 2, COLABS, SR, UPD>(p, stream);
-    if (c <= 1024) return launch_rowwise_cfg<32, 4, COLABS, SR, UPD>(p, stream);
-    if (c <= 2048) return launch_rowwise_cfg<64, 4, COLABS, SR, UPD>(p, stream);
-    if (c <= 4096) return launch_rowwise_cfg<128, 4, COLABS, SR, UPD>(p, stream);
-    if (c <= 8192) return launch_rowwise_cfg<256, 4, COLABS, SR, UPD>(p, stream);
-    if (c <= 16384) return launch_rowwise_cfg<256, 8, COLABS, SR, UPD>(p, stream);
-    if constexpr (!COLABS) return launch_rowwise_cfg<256, 16, COLABS, SR, UPD>(p, stream);
+    if (c <= 256) return launch_rowwise_cfg<32, 1, COLABS, SR, UPD, SCATTER>(p, stream);
+    if (c <= 512) return launch_rowwise_cfg<32, 2, COLABS, SR, UPD, SCATTER>(p, stream);
+    if (c <= 1024) return launch_rowwise_cfg<32, 4, COLABS, SR, UPD, SCATTER>(p, stream);
+    if (c <= 2048) return launch_rowwise_cfg<64, 4, COLABS, SR, UPD, SCATTER>(p, stream);
+    if (c <= 4096) return launch_rowwise_cfg<128, 4, COLABS, SR, UPD, SCATTER>(p, stream);
+    if (c <= 8192) return launch_rowwise_cfg<256, 4, COLABS, SR, UPD, SCATTER>(p, stream);
+    if (c <= 16384) return launch_rowwise_cfg<256, 8, COLABS, SR, UPD, SCATTER>(p, stream);
+    if constexpr (!COLABS) return launch_rowwise_cfg<256, 16, COLABS, SR, UPD, SCATTER>(p, stream);
     return fail(QT_ERR_UNSUPPORTED, "unreachable");
 }
 
@@ -1256,6 +1275,29 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
 }
 
 // ---- allocation-free column-wise quantize ---------------------------------------------------------
+
+extern "C" int qt_quantize_rowwise_scatter(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                                          int n_dst, void* const* q_dst, void* const* scale_dst, int64_t dst_row0,
+                                          int q_dtype, int scale_dtype, float eps, void* stream_) {
+    QT_REQUIRE(n_dst >= 1 && n_dst <= kMaxScatter, "quantize_rowwise_scatter: 1..%d destinations (got %d)", kMaxScatter, n_dst);
+    QT_REQUIRE(q_dst && scale_dst, "quantize_rowwise_scatter: null destination table");
+    QT_REQUIRE(dst_row0 >= 0, "quantize_rowwise_scatter: negative row offset");
+    for (int d = 0; d < n_dst; ++d) QT_REQUIRE(q_dst[d] && scale_dst[d], "quantize_rowwise_scatter: destination %d is null", d);
+    if (int rc = check_quant_args(x, x_dtype, rows, cols, x_row_stride, q_dst[0], q_dtype, scale_dst[0], scale_dtype)) return rc;
+    if (rows == 0 || cols == 0) return QT_OK;
+    // the register-resident row kernel only: bf16 rows, 16-byte aligned, a multiple of 8 columns
+    const bool vec_load = aligned_to(x, 16) && ((x_row_stride * 2) % 16 == 0);
+    bool vec_store = cols % 8 == 0;
+    for (int d = 0; d < n_dst; ++d) vec_store = vec_store && aligned_to(q_dst[d], 8);
+    if (x_dtype != QT_BF16 || !vec_load || !vec_store || cols > 32768 || eps < 1e-30f)
+        return fail(QT_ERR_UNSUPPORTED, "quantize_rowwise_scatter: needs bf16 rows, 16-byte aligned, cols a multiple of 8 and at most 32768");
+    RowwiseParams p = {};
+    p.x = x; p.rows = rows; p.cols = cols; p.stride = x_row_stride;
+    p.q_dtype = q_dtype; p.scale_dtype = scale_dtype; p.eps = eps; p.vec_load = 1; p.vec_store = 1;
+    p.n_dst = n_dst; p.dst_row0 = dst_row0;
+    for (int d = 0; d < n_dst; ++d) { p.q_dst[d] = reinterpret_cast<uint8_t*>(q_dst[d]); p.scale_dst[d] = scale_dst[d]; }
+    return launch_rowwise_bf16<false, false, 0, true>(p, reinterpret_cast<cudaStream_t>(stream_));
+}
 
 extern "C" int qt_int8_weight_update(void* q, void* scale, int64_t rows, int64_t cols, int mode, const void* t1,
                                      const void* t2, float value, float eps, uint64_t seed, uint64_t offset,

@@ -62,6 +62,8 @@ SIGNATURES = {
     "qt_unpack_i2": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
     "qt_adamw_bf16_sr": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_float, ctypes.c_double,
                                  ctypes.c_double, c_float, c_float, c_float, c_float, c_int, c_uint64, c_uint64, c_void_p]),
+    "qt_quantize_rowwise_scatter": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, ctypes.POINTER(c_void_p),
+                                            ctypes.POINTER(c_void_p), c_int64, c_int, c_int, c_float, c_void_p]),
     "qt_int8_weight_update": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_float, c_float,
                                       c_uint64, c_uint64, c_void_p]),
     "qt_adamw_bf16_sr_multi": (c_int, [c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),

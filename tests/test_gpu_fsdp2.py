@@ -122,3 +122,58 @@ def test_fsdp2_bitnet_2bit_all_gather_matches_unsharded(tmp_path):
         assert (a - b).norm() / b.norm() < 3e-2
     gx = x.grad.float().cpu()
     assert (got["gx"] - gx).norm() / gx.norm() < 3e-2
+
+
+def _gather_worker(rank: int, world: int, port: int, out_path: str):
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    sys.path[:0] = [str(root), str(root / "quantized-training_b200")]
+    import torch.distributed as dist
+
+    import gn_kernels
+    from gn_kernels.sharded import SymmetricRowGather, all_gather_quantized_rows
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        rows, cols = 1024, 1536
+        g = torch.Generator().manual_seed(7)
+        w = (torch.randn(rows, cols, generator=g) * 0.02).bfloat16().to(dev)
+        shard = w[rank * rows // world:(rank + 1) * rows // world]
+        q_local, s_local = gn_kernels.quantize_rowwise(shard)
+        q_nccl, s_nccl = all_gather_quantized_rows(q_local, s_local, total_rows=rows)
+        gather = SymmetricRowGather(rows, cols, device=dev)
+        ok = True
+        for b in (0, 1, 0):                       # both buffers, and a buffer reused
+            gather.q[b].fill_(99)
+            dist.barrier()                        # nobody's fill may overwrite a peer's rows
+            gather.quantize_scatter(shard, b)
+            gather.fence()
+            ok = ok and torch.equal(gather.q[b], q_nccl) and torch.equal(gather.scale[b], s_nccl)
+        q_full, s_full = gn_kernels.quantize_rowwise(w)
+        ok = ok and torch.equal(q_nccl, q_full) and torch.equal(s_nccl, s_full)
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            torch.save({"ok": bool(flag.item())}, out_path)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_fused_quantize_scatter_equals_quantize_then_all_gather(tmp_path, world):
+    """One kernel that quantizes this rank's weight rows and stores them into every rank's gathered buffer
+    (peer-to-peer stores into symmetric memory) against quantize + NCCL all-gather: bit-identical, and
+    identical to quantizing the whole weight on one GPU."""
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs two GPUs")
+    out_path = str(tmp_path / "gather.pt")
+    mp.spawn(_gather_worker, args=(world, _free_port(), out_path), nprocs=world, join=True)
+    assert torch.load(out_path)["ok"]

@@ -394,11 +394,6 @@ def main():
 
     _native.load()
     fused_gather = world > 1 and args.gather == "fused"
-    if args.sm_margin is None:
-        # NCCL's all-gather kernel needs SMs beside the persistent GEMM; the fused form launches no collective kernel
-        args.sm_margin = 0 if (world == 1 or fused_gather) else 8
-    if world > 1:
-        _native.check(_native.load().qt_set_gemm_sm_margin(args.sm_margin))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -423,12 +418,29 @@ def main():
     # step's weight runs on a side stream under the current step's activation quantize and GEMM (the
     # prefetch FSDP2 does for the next layer), so every step still holds exactly one shard quantize,
     # one all-gather, one activation quantize and one GEMM.
+    sym, gather_note = None, None
     if fused_gather:
-        from gn_kernels.sharded import SymmetricRowGather
-        sym = SymmetricRowGather(gN, gK, device=dev, buffers=2)
+        # every rank must take the same path: agree on whether the symmetric buffers could be set up
+        try:
+            from gn_kernels.sharded import SymmetricRowGather
+            sym = SymmetricRowGather(gN, gK, device=dev, buffers=2)
+            ok_here = 1
+        except Exception as exc:  # no symmetric memory on this system: the NCCL all-gather serves
+            gather_note = f"fused gather unavailable ({type(exc).__name__}: {exc}); NCCL all-gather used"
+            ok_here = 0
+        agree = torch.tensor([ok_here], dtype=torch.int32, device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 0:
+            sym, fused_gather = None, False
+            gather_note = gather_note or "fused gather unavailable on another rank; NCCL all-gather used"
+    if args.sm_margin is None:
+        # NCCL's all-gather kernel needs SMs beside the persistent GEMM; the fused form launches no collective kernel
+        args.sm_margin = 0 if (world == 1 or fused_gather) else 8
+    if world > 1:
+        _native.check(_native.load().qt_set_gemm_sm_margin(args.sm_margin))
+    if sym is not None:
         wq_full, ws_full = sym.q, sym.scale
     else:
-        sym = None
         wq_full = [torch.empty((gN, gK), dtype=torch.int8, device=dev) for _ in range(2)]
         ws_full = [torch.empty((gN, 1), dtype=torch.bfloat16, device=dev) for _ in range(2)]
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
@@ -635,6 +647,7 @@ def main():
                                   "fused into the quantize kernel: int8 rows + bf16 scales stored into every rank's buffer over NVLink (peer-to-peer stores, symmetric memory), one step ahead on a side stream" if fused_gather else
                                   "int8 rows + bf16 scales over NCCL, prefetched one step ahead on a side stream"),
             "sm_margin": args.sm_margin,
+            **({"gather_note": gather_note} if gather_note else {}),
             "l2": f"inputs larger than L2 ({(gM + gN) * gK * 2 / 1e6:.0f} MB bf16 in, {(gM + gN) * gK / 1e6:.0f} MB int8 operands, {gM * gN * 2 / 1e6:.0f} MB out per step)",
             "value_is": "2*M*N*K * n_gpus / step time; the step includes both quantize kernels",
         },

@@ -4,14 +4,16 @@
 // Persistent kernel, one CTA per SM, 10 warps:
 //   warp 0      TMA producer   global -> 128B-swizzled shared-memory stages (cp.async.bulk.tensor)
 //   warp 1      MMA issuer     one elected lane issues tcgen05.mma; accumulators live in TMEM
-//   warps 2..9  epilogue       tcgen05.ld TMEM -> registers -> scale -> global (two warps per lane quarter)
+//   warps 2..9  epilogue       two groups of four warps (one per TMEM lane quarter); group g drains
+//                              accumulator g: tcgen05.ld TMEM -> registers -> scale -> swizzled staging box
+//                              in shared memory -> TMA store (whole 128-byte output lines)
 // Large problems run as CTA PAIRS (2-CTA clusters, tcgen05 cta_group::2): the pair owns a 256 x 256
 // tile, each CTA stages its 128 rows of A and half of B, the leader CTA issues M=256 MMAs for both
-// and each CTA drains its own 128 accumulator rows. Small problems (M <= 128) use one CTA per
-// 128 x 256 tile. The accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of
-// tile i overlaps the main loop of tile i+1. Stages and accumulators are handed over through
-// mbarriers; every wait is bounded and reports through the device status word instead of spinning
-// forever.
+// and each CTA drains its own 128 accumulator rows. Small problems (M <= 128 or K < 512) use one CTA
+// per 128 x 256 tile. The accumulator is double-buffered in TMEM (2 x 256 columns), so while tile i+2
+// is in the main loop tiles i and i+1 are in the two epilogue groups. Stages and accumulators are handed
+// over through mbarriers; every wait is bounded and reports through the device status word instead of
+// spinning forever.
 //
 // Operand layouts: both operands may be K-major or MN-major in global memory; MN-major tiles are
 // fetched as [K][128 B of M or N] boxes and described to the tensor core as MN-major, so A@B.T,

@@ -65,6 +65,17 @@ def test_argument_errors_do_not_need_a_gpu(lib):
     # unsupported tile shape
     rc = lib.qt_quantize_tile(addr, 0, 4, 4, 4, 3, 5, addr, 2, addr, 0, 1e-12, None)
     assert rc == 3
+    # scatter form: destination count out of range, then a shape its kernel does not take
+    ptrs = (ctypes.c_void_p * 1)(addr)
+    rc = lib.qt_quantize_rowwise_scatter(addr, 0, 4, 8, 8, 0, ptrs, ptrs, 0, 2, 0, 1e-12, None)
+    assert rc == 1 and b"destinations" in lib.qt_last_error()
+    rc = lib.qt_quantize_rowwise_scatter(addr, 0, 4, 12, 16, 1, ptrs, ptrs, 0, 2, 0, 1e-12, None)
+    assert rc == 3
+    # optimizer and weight update: dtype and mode checks come before any launch
+    rc = lib.qt_adamw_bf16_sr_multi(1, ptrs, ptrs, ptrs, ptrs, (ctypes.c_int64 * 1)(4), 2, 0, 1e-3, 0.9, 0.99, 0.0, 1e-8, 1.0, 1.0, 0, 0, 0, None)
+    assert rc == 1 and b"dtype" in lib.qt_last_error()
+    rc = lib.qt_int8_weight_update(addr, addr, 4, 8, 7, addr, addr, 1.0, 1e-12, 0, 0, None)
+    assert rc == 1 and b"mode" in lib.qt_last_error()
 
 
 def test_python_ops_refuse_cpu_tensors():

@@ -423,7 +423,7 @@ def main():
         # every rank must take the same path: agree on whether the symmetric buffers could be set up
         try:
             from gn_kernels.sharded import SymmetricRowGather
-            sym = SymmetricRowGather(gN, gK, device=dev, buffers=2)
+            sym = SymmetricRowGather(gN, gK, device=dev, buffers=3)
             ok_here = 1
         except Exception as exc:  # no symmetric memory on this system: the NCCL all-gather serves
             gather_note = f"fused gather unavailable ({type(exc).__name__}: {exc}); NCCL all-gather used"
@@ -434,8 +434,9 @@ def main():
             sym, fused_gather = None, False
             gather_note = gather_note or "fused gather unavailable on another rank; NCCL all-gather used"
     if args.sm_margin is None:
-        # NCCL's all-gather kernel needs SMs beside the persistent GEMM; the fused form launches no collective kernel
-        args.sm_margin = 0 if (world == 1 or fused_gather) else 8
+        # NCCL's all-gather kernels need SMs beside the persistent GEMM; the fused form only has its 4-byte
+        # fence (one CTA) and the first CTAs of the scatter kernel to place while a GEMM is running
+        args.sm_margin = 0 if world == 1 else (2 if fused_gather else 8)
     if world > 1:
         _native.check(_native.load().qt_set_gemm_sm_margin(args.sm_margin))
     if sym is not None:
@@ -444,8 +445,9 @@ def main():
         wq_full = [torch.empty((gN, gK), dtype=torch.int8, device=dev) for _ in range(2)]
         ws_full = [torch.empty((gN, 1), dtype=torch.bfloat16, device=dev) for _ in range(2)]
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-    gathered = [torch.cuda.Event() for _ in range(2)]   # buffer b holds a complete gathered weight
-    consumed = [torch.cuda.Event() for _ in range(2)]   # the GEMM that read buffer b has finished
+    n_wbuf = len(wq_full)                                    # 2 with NCCL, 3 with the fused gather
+    gathered = [torch.cuda.Event() for _ in range(n_wbuf)]   # buffer b holds a complete gathered weight
+    consumed = [torch.cuda.Event() for _ in range(n_wbuf)]   # the GEMM that read buffer b has finished
     state = {"next": 0, "primed": False}
     gemm_events = []
 
@@ -456,10 +458,11 @@ def main():
         comm_stream.wait_event(consumed[b])
         with torch.cuda.stream(comm_stream):
             if sym is not None:
-                # The first fence: every rank's GEMM that last read buffer b has finished (each rank is
-                # behind its own `consumed[b]` here), so peers may overwrite it. The second: every rank's
-                # new rows have landed before anybody reads the buffer.
-                sym.fence()
+                # One fence per step, after the scatter: the readers of buffer b start once every rank's
+                # rows have landed. No fence is needed before overwriting b on the peers, because there
+                # are three buffers: b was last read by the GEMM two steps back, and this stream has
+                # already passed the fence of the previous prefetch, which no rank reaches before its
+                # own copy of that GEMM has finished (each rank's prefetch waits for its main stream).
                 sym.quantize_scatter(w_dev, b)
                 sym.fence()
             else:
@@ -469,7 +472,7 @@ def main():
                 wq.record_stream(comm_stream)
                 ws.record_stream(comm_stream)
             gathered[b].record(comm_stream)
-        state["next"] = 1 - b
+        state["next"] = (b + 1) % n_wbuf
         return b
 
     def step(a_dev, w_dev, record_gemm=False):
@@ -572,6 +575,17 @@ def main():
     status = _native.device_status()
     if status != 0:
         raise SystemExit(f"a kernel reported a bounded wait that ran out (status {status:#x})")
+    if world > 1:
+        # the pipelined result of the last step against the same product through quantize + NCCL all-gather
+        from gn_kernels.sharded import all_gather_quantized_rows
+        wq_ref, ws_ref = all_gather_quantized_rows(*gn_kernels.quantize_rowwise(W), total_rows=gN)
+        aq_ref, as_ref = gn_kernels.quantize_rowwise(A)
+        ref = gn_kernels.scaled_mm(aq_ref, wq_ref.T, as_ref, ws_ref.view(1, -1))
+        same = torch.tensor([1 if torch.equal(out, ref) else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        if int(same.item()) != 1:
+            raise SystemExit("the pipelined multi-GPU step disagrees with quantize + all-gather + GEMM run in order")
+        del wq_ref, ws_ref, aq_ref, as_ref, ref
 
     # ---- end to end through the public API from pinned host buffers -----------------------------
     # Every step copies its two bf16 inputs from pinned host memory and its bf16 result back. The

@@ -74,9 +74,16 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons of one GPU beside the timed region, through NVML
-    in a background thread (the same fields `nvidia-smi --query-gpu=clocks.sm,...` prints; reading
-    only). Falls back to an nvidia-smi subprocess when the NVML binding is missing."""
+    """Samples SM clock and throttle reasons of one GPU beside the timed region, through NVML in a
+    background thread (the same fields `nvidia-smi --query-gpu=clocks.sm,...` prints; reading only).
+    Falls back to an nvidia-smi subprocess when the NVML binding is missing.
+
+    Timed regions on these hosts are now and then hit by a hole of 7-80 ms (one launch delayed, the
+    rest normal). Runs with this thread sampling through the region showed it more often (2 of 3)
+    than runs without the thread (0 of 3) or with the thread paused (1 of 5), so the thread is paused
+    while the host queues the timed steps, and the main thread takes the in-region samples itself right
+    after the last
+    launch is queued -- the GPU is then still inside the timed region, and no launch can be delayed."""
 
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -92,6 +99,24 @@ class ClockSampler:
         self.stop_flag = None
         self.proc = None
         self.file = None
+        self.paused = False
+        self._read = None
+
+    def pause(self):
+        self.paused = True
+
+    def resume(self):
+        self.paused = False
+
+    def sample_now(self, n: int = 2):
+        """Take n samples on the calling thread (used while the GPU works through queued launches)."""
+        if self._read is None:
+            return
+        for _ in range(n):
+            try:
+                self.samples.append(self._read())
+            except Exception:
+                pass
 
     def start(self):
         try:
@@ -111,17 +136,23 @@ class ClockSampler:
             self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
             self.stop_flag = threading.Event()
 
+            def read():
+                mhz = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                try:
+                    mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                except Exception:
+                    mask = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                return mhz, mask
+
+            self._read = read
+
             def loop():
                 while not self.stop_flag.is_set():
-                    try:
-                        mhz = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                    if not self.paused:
                         try:
-                            mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                            self.samples.append(read())
                         except Exception:
-                            mask = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
-                        self.samples.append((mhz, mask))
-                    except Exception:
-                        pass
+                            pass
                     self.stop_flag.wait(self.interval_s)
 
             self.thread = threading.Thread(target=loop, daemon=True)
@@ -556,11 +587,14 @@ def main():
             step(A, W)
         warm_steps += 2
         gemm_events.clear()
+        sampler.pause()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for _ in range(args.steps):
             out = step(A, W, record_gemm=True)
         stop.record()
+        sampler.sample_now()    # every launch is queued; the GPU is still inside the region
+        sampler.resume()
         sync_all()
         ms_total = max_over_ranks(start.elapsed_time(stop))
         gemm_times = [e0.elapsed_time(e1) for e0, e1 in gemm_events]
@@ -636,12 +670,15 @@ def main():
     e2e_steps = max(3, min(args.steps, 10))
     e2e_regions = []
     for _ in range(2):   # two regions, the undisturbed (faster) one is reported; both are in the line
+        sampler.pause()
         s2, t2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s2.record()
         for _ in range(e2e_steps):
             e2e_step()
         e2e_drain()                                        # the last result has reached the host
         t2.record()
+        sampler.sample_now()
+        sampler.resume()
         sync_all()
         e2e_regions.append(max_over_ranks(s2.elapsed_time(t2)) / e2e_steps)
     e2e_ms = min(e2e_regions)

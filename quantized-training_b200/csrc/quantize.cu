@@ -995,31 +995,33 @@ __global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p
     const int tpr = 1 << tpr_log2;
     const int rpp = kThreads >> tpr_log2;            // rows per pass
     const int sub = threadIdx.x >> tpr_log2, t = threadIdx.x & (tpr - 1);
-    const int64_t chunks = (p.cols + tpr * 8 - 1) / (tpr * 8);
-    const int64_t row_blocks = (p.rows + ROWS * rpp - 1) / (ROWS * rpp);
-    const int64_t items = row_blocks * chunks;
+    // an item is 4 x rpp rows by tpr x 8 columns (8192 elements): their count always fits 32 bits, and
+    // 32-bit divisions keep the per-item index arithmetic cheap (64-bit ones are emulated)
+    const uint32_t chunks = (uint32_t)((p.cols + tpr * 8 - 1) / (tpr * 8));
+    const uint32_t row_blocks = (uint32_t)((p.rows + ROWS * rpp - 1) / (ROWS * rpp));
+    const uint32_t items = row_blocks * chunks;
 
-    auto load_item = [&](Vec8<XT> (&v)[ROWS], int64_t item) {
-        const int64_t rblk = item / chunks, chunk = item - rblk * chunks;
-        const int64_t col = (chunk * tpr + t) * 8;
+    auto load_item = [&](Vec8<XT> (&v)[ROWS], uint32_t item) {
+        const uint32_t rblk = item / chunks, chunk = item - rblk * chunks;
+        const int64_t col = ((int64_t)chunk * tpr + t) * 8;
 #pragma unroll
         for (int j = 0; j < ROWS; ++j) {
-            const int64_t row = (rblk * ROWS + j) * rpp + sub;
+            const int64_t row = ((int64_t)rblk * ROWS + j) * rpp + sub;
             if (row < p.rows && col < p.cols) load_vec8<XT>(v[j], x + row * p.stride, col, p.cols, p.vec_load != 0);
             else v[j].zero();
         }
     };
 
     Vec8<XT> v[ROWS], vn[ROWS];
-    int64_t item = blockIdx.x;
+    uint32_t item = blockIdx.x;
     if (item < items) load_item(v, item);
     for (; item < items; item += gridDim.x) {
         if (item + gridDim.x < items) load_item(vn, item + gridDim.x);
-        const int64_t rblk = item / chunks, chunk = item - rblk * chunks;
-        const int64_t col = (chunk * tpr + t) * 8;
+        const uint32_t rblk = item / chunks, chunk = item - rblk * chunks;
+        const int64_t col = ((int64_t)chunk * tpr + t) * 8;
 #pragma unroll
         for (int j = 0; j < ROWS; ++j) {
-            const int64_t row = (rblk * ROWS + j) * rpp + sub;
+            const int64_t row = ((int64_t)rblk * ROWS + j) * rpp + sub;
             float f[8];
             v[j].unpack(f);
             float amax = 0.0f;

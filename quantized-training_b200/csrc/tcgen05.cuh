@@ -11,7 +11,10 @@ namespace qt {
 namespace tc {
 
 constexpr int GROUP_M = 8;                 // rasterisation: 8 row-tiles share B panels in L2
-constexpr uint32_t WAIT_LIMIT = 1u << 26;  // polls before a wait gives up (seconds, not minutes)
+// A poll is mbarrier.try_wait with a suspend-time hint: the hardware parks the warp until the phase
+// completes or the hint (nanoseconds) runs out, so a waiting role neither burns issue slots nor power.
+constexpr uint32_t WAIT_HINT_NS = 20000;                 // per poll
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // a wait gives up after two seconds
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 
@@ -30,19 +33,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(WAIT_HINT_NS)
         : "memory");
     return ok != 0;
 }
 
 // Bounded wait. Returns false (and records `code`) when the limit is hit or another role aborted.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    // the limit is wall time, not a poll count: it holds whether or not the hardware honours the hint
+    const unsigned long long t0 = global_timer_ns();
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if ((i & 7u) == 7u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+        }
     }
     *abort_flag = 1;
     atomicCAS(status, 0, code);

@@ -553,6 +553,11 @@ def main():
         sampler.start()
         time.sleep(0.2)
     sync_all()
+    # The collector runs now and stays off until the timed region is over: a collection between warm-up
+    # and the timed steps would leave the GPU idle for tens of milliseconds, the power controller would
+    # hand the clocks back, and the region would measure that transient instead of the loaded state.
+    gc.collect()
+    gc.disable()
     warm_steps = 0
     t_warm = time.perf_counter()
     chunk = max(args.warmup, 3)
@@ -571,8 +576,6 @@ def main():
         if not more:
             break
     sync_all()
-    gc.collect()
-    gc.disable()   # a collector pause between two launches would be charged to the step
     # The barrier + synchronize above leave the GPU idle for milliseconds; two more untimed steps put it
     # back under load so the first timed step does not pay the ramp-up.
     #

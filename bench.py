@@ -78,12 +78,10 @@ class ClockSampler:
     background thread (the same fields `nvidia-smi --query-gpu=clocks.sm,...` prints; reading only).
     Falls back to an nvidia-smi subprocess when the NVML binding is missing.
 
-    Timed regions on these hosts are now and then hit by a hole of 7-80 ms (one launch delayed, the
-    rest normal). Runs with this thread sampling through the region showed it more often (2 of 3)
-    than runs without the thread (0 of 3) or with the thread paused (1 of 5), so the thread is paused
-    while the host queues the timed steps, and the main thread takes the in-region samples itself right
-    after the last
-    launch is queued -- the GPU is then still inside the timed region, and no launch can be delayed."""
+    An NVML query can stall the GPU's queued work for milliseconds to tens of milliseconds. The thread
+    therefore samples during warm-up only; it is paused around the timed region, and the main thread
+    takes the samples that bracket the region itself (see the timed loop) while untimed steps keep the
+    GPU under the same load."""
 
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -586,17 +584,33 @@ def main():
     # rank. The line reports how many regions were timed and what the rejected ones measured.
     discarded = []
     for attempt in range(3):
-        for _ in range(2):
-            step(A, W)
-        warm_steps += 2
-        gemm_events.clear()
+        # Clock samples bracket the region under the same continuous load instead of falling inside it:
+        # an NVML query stalls the GPU's queued work for milliseconds to tens of milliseconds (with a
+        # query placed inside every region, 5 of 6 regions had such a hole; with none, 0 of 3). One sample
+        # is taken while untimed lead-in steps run, the others while untimed tail steps run right after
+        # the region's last kernel has finished.
         sampler.pause()
+        for _ in range(4):
+            step(A, W)
+        sampler.sample_now(1)
+        # ... and that query (or the hole that got the previous region rejected) may have left the GPU
+        # idle long enough for the power controller to hand the clocks back: 400 more untimed steps
+        # (a fixed count, the same on every rank; about 0.2 s) bring back the loaded state the timed
+        # steps are meant to see.
+        for _ in range(400):
+            step(A, W)
+        warm_steps += 404
+        gemm_events.clear()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for _ in range(args.steps):
             out = step(A, W, record_gemm=True)
         stop.record()
-        sampler.sample_now()    # every launch is queued; the GPU is still inside the region
+        for _ in range(12):
+            step(A, W)             # keeps the GPU under the same load while the clocks are read
+        while not stop.query():
+            time.sleep(0)
+        sampler.sample_now(2)
         sampler.resume()
         sync_all()
         ms_total = max_over_ranks(start.elapsed_time(stop))
@@ -680,7 +694,6 @@ def main():
             e2e_step()
         e2e_drain()                                        # the last result has reached the host
         t2.record()
-        sampler.sample_now()
         sampler.resume()
         sync_all()
         e2e_regions.append(max_over_ranks(s2.elapsed_time(t2)) / e2e_steps)

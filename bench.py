@@ -280,7 +280,7 @@ def run_reference(args, rank: int):
 
 
 LLAMA_SHAPES = {
-    # the reference's shipped config (mini_llamas/Llama-2-470m/config.json:5-10) and the 1.1B shape of BASELINE.json
+    # the reference's shipped config (mini_llamas/Llama-2-470m/config.json:5-10) and the 1.1B shape the reference's README trains (hidden 2048, 22 layers, MLP 5632)
     "train-470m": dict(hidden_size=1024, intermediate_size=4096, num_hidden_layers=24, num_attention_heads=16,
                        num_key_value_heads=16),
     "train-1b": dict(hidden_size=2048, intermediate_size=5632, num_hidden_layers=22, num_attention_heads=32,

@@ -1,4 +1,4 @@
-"""The reference's CPU-runnable form of the hot path, restated with torch CPU ops.  TEST / BASELINE
+"""The reference's CPU-runnable form of the hot path, restated with torch CPU ops.  TEST / CPU-BASELINE
 INFRASTRUCTURE ONLY: imported by the test-suite and by the benchmark's CPU-baseline and
 `--impl reference` legs, never by the product packages.
 
@@ -26,7 +26,7 @@ def quantize_rows_int8(x: Tensor, eps: float = 1e-12):
 
 @torch.no_grad()
 def dynamic_int8_linear(A: Tensor, B: Tensor) -> Tensor:
-    """bf16 A [M,K], B [N,K] -> bf16 A @ B.T through row-wise INT8 (BASELINE config 1):
+    """bf16 A [M,K], B [N,K] -> bf16 A @ B.T through row-wise INT8 (the 1024^2, seed-2024 configuration):
     quantize both along K, int32 accumulate with torch._int_mm, de-scale as the Triton epilogue
     does (kernels/gn_kernels/triton_mm.py:210-216)."""
     qa, sa = quantize_rows_int8(A)

@@ -14,7 +14,7 @@ What is recorded (all small, seeded, CPU):
                      (kernels/gn_kernels/triton_mm.py:210-216), the ops having no CPU kernel
   adamw_bf16_sr.npz  other_optim/bf16_sr.py:78-124 `adamw`, eager, with and without stochastic rounding
   bitnet.npz         get_bitnet_scale / quantize_bitnet_weight / pack / unpack (subclasses/bitnet.py)
-  config1_digest.json  SHA-256 digests of the BASELINE config-1 tensors (1024^2, seed 2024)
+  config1_digest.json  SHA-256 digests of the 1024^2, seed-2024 configuration's tensors
 """
 from __future__ import annotations
 
@@ -166,7 +166,7 @@ def main(ref_root: str) -> None:
     np.savez_compressed(HERE / "int8_weight.npz", w=bf16_bits(w), int_data=qw.int_data.numpy(), scale=bf16_bits(qw.scale),
                         deq=bf16_bits(qw.dequantize()))
 
-    # ---------------- BASELINE config 1 digests ----------------
+    # ---------------- digests of the 1024^2, seed-2024 configuration ----------------
     torch.manual_seed(2024)
     A = torch.randn(1024, 1024).bfloat16()
     B = (torch.randn(1024, 1024) * 0.02).bfloat16()
@@ -189,4 +189,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of gau-nernst/quantized-training>")
+    main(sys.argv[1])

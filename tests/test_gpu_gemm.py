@@ -119,7 +119,7 @@ def test_scaled_mm_reference_fixture_and_tolerances(golden_dir):
 
 
 def test_config1_dynamic_quantize_plus_gemm(golden_dir):
-    """BASELINE config 1: A ~ N(0,1), B ~ N(0,0.02), 1024^2, seed 2024, A @ B.T row-wise INT8."""
+    """The reference's CPU-runnable configuration: A ~ N(0,1), B ~ N(0,0.02), 1024^2, seed 2024, A @ B.T row-wise INT8."""
     torch.manual_seed(2024)
     A = torch.randn(1024, 1024).bfloat16()
     B = (torch.randn(1024, 1024) * 0.02).bfloat16()

@@ -196,7 +196,7 @@ def test_colwise_saturates_when_the_given_absmax_is_too_small(shape):
 
 
 def test_full_size_properties():
-    """BASELINE sizes (tokens x hidden): size-independent properties instead of an oracle run:
+    """Full training sizes (tokens x hidden): size-independent properties instead of an oracle run:
     transposed result == transpose of the column-scaled result, dequantization error bounded by
     half a step, scales == absmax / 127."""
     x = randn_bf16((32768, 2048), seed=61)

@@ -134,7 +134,7 @@ def test_int8_weight_fixture(golden_dir):
 
 
 def test_config1_digests(golden_dir):
-    """BASELINE config 1 (1024^2, seed 2024): regenerate the inputs from the seed and compare
+    """The 1024^2, seed-2024 configuration: regenerate the inputs from the seed and compare
     SHA-256 digests of every intermediate with those the reference produced."""
     torch = pytest.importorskip("torch")
     ref = json.loads((golden_dir / "config1_digest.json").read_text())
@@ -162,7 +162,7 @@ def test_config1_digests(golden_dir):
 
 def test_cpu_path_matches_reference_fixtures(golden_dir):
     """The torch-CPU restatement used as the timed CPU baseline reproduces the reference's digests
-    on BASELINE config 1 and agrees bit-for-bit with the numpy oracle."""
+    on the 1024^2, seed-2024 configuration and agrees bit-for-bit with the numpy oracle."""
     torch = pytest.importorskip("torch")
     from oracle import cpu_path
 

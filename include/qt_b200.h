@@ -328,6 +328,15 @@ int qt_adamw_bf16_sr_multi(int n_tensors, void* const* p, const void* const* gra
  */
 int qt_selftest_division(int q_dtype, float eps, unsigned long long* mismatches);
 
+/*
+ * Exercises the bounded-wait path of the GEMM kernels without a GEMM: one warp waits on an mbarrier
+ * that nothing arrives on, gives up after 50 ms, records the code 0x7E57 in the device status word
+ * and returns. *observed_status receives the word (0x7E57 when the mechanism works); the word is reset
+ * to zero before the call returns. Fails if the word was already set. Synchronises the device.
+ * Test utility; no counterpart in the reference.
+ */
+int qt_selftest_wait_timeout(int* observed_status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -763,6 +763,40 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
 
 using namespace qt;
 
+namespace qt {
+namespace {
+// One warp waits on an mbarrier that nothing ever arrives on, with a 50 ms limit: the wait gives up,
+// sets the abort flag and records its code, and the kernel returns normally.
+__global__ void wait_timeout_selftest_kernel(int* status) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    const uint32_t bar_addr = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(bar_addr, 1);
+        abort_flag = 0;
+    }
+    __syncthreads();
+    mbar_wait(bar_addr, 0u, &abort_flag, status, 0x7E57, 50000000ull);
+}
+}  // namespace
+}  // namespace qt
+
+extern "C" int qt_selftest_wait_timeout(int* observed_status) {
+    QT_REQUIRE(observed_status, "selftest_wait_timeout: null output");
+    int* status = nullptr;
+    if (int rc = device_status_ptr(&status)) return rc;
+    int before = 0;
+    QT_CUDA_CHECK(cudaDeviceSynchronize());
+    QT_CUDA_CHECK(cudaMemcpy(&before, status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (before != 0) return fail(QT_ERR_DEVICE, "selftest_wait_timeout: the device status word is already set (%#x)", before);
+    wait_timeout_selftest_kernel<<<1, 32>>>(status);
+    QT_CUDA_CHECK(cudaGetLastError());
+    QT_CUDA_CHECK(cudaDeviceSynchronize());
+    QT_CUDA_CHECK(cudaMemcpy(observed_status, status, sizeof(int), cudaMemcpyDeviceToHost));
+    QT_CUDA_CHECK(cudaMemset(status, 0, sizeof(int)));   // the word is clean again for the real kernels
+    return QT_OK;
+}
+
 extern "C" int qt_set_gemm_sm_margin(int sms) {
     QT_REQUIRE(sms >= 0 && sms < 128, "set_gemm_sm_margin: expected 0..127 (got %d)", sms);
     g_sm_margin = sms;

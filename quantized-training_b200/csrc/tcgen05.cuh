@@ -47,7 +47,8 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     // the limit is wall time, not a poll count: it holds whether or not the hardware honours the hint
     const unsigned long long t0 = global_timer_ns();
@@ -55,7 +56,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 7u) == 7u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+            if (global_timer_ns() - t0 > limit_ns) break;
         }
     }
     *abort_flag = 1;

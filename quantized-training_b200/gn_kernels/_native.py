@@ -69,6 +69,7 @@ SIGNATURES = {
     "qt_adamw_bf16_sr_multi": (c_int, [c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                        ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), c_int, c_int, c_float, ctypes.c_double,
                                        ctypes.c_double, c_float, c_float, c_float, c_float, c_int, c_uint64, c_uint64, c_void_p]),
+    "qt_selftest_wait_timeout": (c_int, [ctypes.POINTER(c_int)]),
     "qt_selftest_division": (c_int, [c_int, c_float, ctypes.POINTER(ctypes.c_ulonglong)]),
 }
 

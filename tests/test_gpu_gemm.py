@@ -236,3 +236,20 @@ def test_split_k_is_used_for_grad_weight_shapes():
     assert nv.load().qt_gemm_workspace_bytes(1024, 1024, 32768) > 0
     assert nv.load().qt_gemm_workspace_bytes(8192, 8192, 8192) == 0
     assert nv.load().qt_gemm_workspace_bytes(32768, 1024, 1024) == 0
+
+
+def test_a_wait_that_nothing_satisfies_gives_up_and_reports():
+    """The kernels' mbarrier waits are bounded: a warp waiting on a barrier nobody arrives on returns
+    after its limit with a code in the device status word, the context stays usable, and the word is
+    clean again afterwards."""
+    import ctypes
+
+    from gn_kernels import _native as nv
+
+    seen = ctypes.c_int(0)
+    nv.check(nv.load().qt_selftest_wait_timeout(ctypes.byref(seen)))
+    assert seen.value == 0x7E57
+    assert nv.device_status() == 0
+    a = torch.randint(-128, 127, (256, 256), dtype=torch.int8, device="cuda")
+    out = gn_kernels.int8_mm(a, a.T)
+    assert torch.equal(out.cpu(), torch._int_mm(a.cpu(), a.cpu().T.contiguous()))

@@ -60,6 +60,12 @@ def parse_args():
                          "buffer over NVLink (symmetric memory); 'nccl' = quantize, then NCCL all-gather")
     ap.add_argument("--sm-margin", type=int, default=None,
                     help="SMs the GEMM leaves free when --gpus > 1 (default: 8 beside NCCL's all-gather kernel, 0 with the fused gather)")
+    ap.add_argument("--layers", type=int, default=None, help="train-* workloads: number of decoder layers (default: the model's own)")
+    ap.add_argument("--profile", default=None, metavar="FILE",
+                    help="train-* workloads: after the timed steps, run two more under torch.profiler and write the kernel table "
+                         "(device time per kernel, share of the step) to FILE")
+    ap.add_argument("--plain-launches", action="store_true", help="--workload quantize: plain launches instead of CUDA-graph replays (for a profiler run)")
+    ap.add_argument("--only", default=None, help="--workload quantize: only the kernels whose name contains this text")
     ap.add_argument("--no-clock-sampler", action="store_true", help="do not run nvidia-smi beside the timed region")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0, help="keep warming up at least this long (0 under a profiler)")
     return ap.parse_args()
@@ -304,8 +310,10 @@ def run_train(args, rank, local_rank, world):
         dist.init_process_group("nccl", device_id=dev)
     bs, seq = 16, 2048
     torch.manual_seed(2024)
-    cfg = LlamaConfig(vocab_size=32000, max_position_embeddings=seq, attn_implementation="sdpa", tie_word_embeddings=False,
-                      **LLAMA_SHAPES[args.workload])
+    shape = dict(LLAMA_SHAPES[args.workload])
+    if args.layers is not None:
+        shape["num_hidden_layers"] = args.layers
+    cfg = LlamaConfig(vocab_size=32000, max_position_embeddings=seq, attn_implementation="sdpa", tie_word_embeddings=False, **shape)
     with torch.device(dev):
         model = LlamaForCausalLM(cfg).bfloat16()
     quantize_model(model.model, None if args.quantize == "none" else args.quantize)
@@ -346,6 +354,23 @@ def run_train(args, rank, local_rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
         dist.barrier()
+    if args.profile and rank == 0:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            for _ in range(2):
+                step()
+            torch.cuda.synchronize()
+        rows = [(k.key, k.count, getattr(k, "device_time_total", getattr(k, "cuda_time_total", 0.0)))
+                for k in prof.key_averages() if getattr(k, "device_type", None) is not None and "cuda" in str(k.device_type).lower()]
+        total = sum(r[2] for r in rows) or 1.0
+        rows.sort(key=lambda r: -r[2])
+        with open(args.profile, "w") as f:
+            f.write(f"# {args.workload} layers={shape['num_hidden_layers']} quantize={args.quantize}: device time per kernel over 2 steps "
+                    f"(torch.profiler); step {ms / args.steps:.2f} ms by CUDA events, kernels sum to {total / 2e3:.2f} ms per step\n")
+            f.write("share%  total_us  launches  kernel\n")
+            for name, count, us in rows[:60]:
+                f.write(f"{100 * us / total:6.2f} {us:9.0f} {count:9d}  {name[:150]}\n")
     if rank == 0:
         n_params = sum(p.numel() for p in model.parameters())
         print(json.dumps({
@@ -361,52 +386,161 @@ def run_train(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def _time_graph(launch, n_sets: int, launches: int, reps: int = 5, graph: bool = True) -> float:
+    """Milliseconds per launch of `launch(i)` (i = which buffer set), measured over a CUDA graph of
+    `launches` back-to-back launches that rotate through `n_sets` buffer sets. The sets together are several
+    times larger than L2, so every launch reads its input from HBM and the dirty lines it displaces are a
+    previous launch's output of the same kernel: steady-state traffic equals the algorithmic bytes. Events
+    bracket whole graph replays (no host launch gaps, no event overhead per launch); the median replay counts."""
+    for i in range(n_sets):
+        launch(i)
+    torch.cuda.synchronize()
+    if not graph:   # plain launches between two events (what a profiler run uses): host launch gaps included
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(launches):
+            launch(i % n_sets)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / launches
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(launches):
+            launch(i % n_sets)
+    g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / launches)
+    return statistics.median(times)
+
+
+def quantize_lines(M: int, K: int, launches: int, dev, graph: bool = True, only: str | None = None) -> list:
+    """Roofline entries for the HBM-bound kernels of the path on [M, K] bf16 (N(0,1)) through the C ABI with
+    preallocated outputs: algorithmic bytes, time per launch (_time_graph) and the fraction of the measured
+    HBM copy bandwidth."""
+    from gn_kernels import _native as nv
+
+    lib = nv.load()
+    hbm_peak, _, peak_kind = measured_peaks()
+    RC = M * K
+    n_sets = max(3, -(-3 * 126 * (1 << 20) // (3 * RC)) + 1)
+    xs = [torch.randn(M, K, device=dev).bfloat16() for _ in range(n_sets)]
+    qs = [torch.empty(M, K, dtype=torch.int8, device=dev) for _ in range(n_sets)]
+    qts = [torch.empty(K, M, dtype=torch.int8, device=dev) for _ in range(n_sets)]
+    row_scales = [torch.empty(M, 1, dtype=torch.bfloat16, device=dev) for _ in range(n_sets)]
+    col_scales = [torch.empty(K, 1, dtype=torch.bfloat16, device=dev) for _ in range(n_sets)]
+    tile_scales = [torch.empty(M, -(-K // 128), dtype=torch.bfloat16, device=dev) for _ in range(n_sets)]
+    colmaxes = [torch.empty(K, dtype=torch.float32, device=dev) for _ in range(n_sets)]
+    BF16, I8, E4M3 = nv.QT_BF16, nv.QT_I8, nv.QT_E4M3
+
+    def st():
+        return nv.stream_ptr(dev)
+
+    def rowwise(q_dtype, sr):
+        def f(i):
+            nv.check(lib.qt_quantize_rowwise(xs[i].data_ptr(), BF16, M, K, K, qs[i].data_ptr(), q_dtype, row_scales[i].data_ptr(),
+                                             BF16, 1e-12, int(sr), 2024, 1 + i, st()))
+        return f
+
+    def rowwise_colabs(i):
+        nv.check(lib.qt_quantize_rowwise_colabsmax(xs[i].data_ptr(), BF16, M, K, K, qs[i].data_ptr(), I8, row_scales[i].data_ptr(), BF16,
+                                                   colmaxes[i].data_ptr(), 1e-12, 0, 0, 0, st()))
+
+    def col_absmax(i):
+        nv.check(lib.qt_col_absmax(xs[i].data_ptr(), BF16, M, K, K, colmaxes[i].data_ptr(), st()))
+
+    def colwise_t(i):
+        nv.check(lib.qt_quantize_colwise_t(xs[i].data_ptr(), BF16, M, K, K, colmaxes[i].data_ptr(), qts[i].data_ptr(), I8,
+                                           col_scales[i].data_ptr(), BF16, 1e-12, 0, 0, 0, st()))
+
+    def tile(tr, q_dtype):
+        def f(i):
+            nv.check(lib.qt_quantize_tile(xs[i].data_ptr(), BF16, M, K, K, tr, 128, qs[i].data_ptr(), q_dtype, tile_scales[i].data_ptr(),
+                                          BF16, 1e-12, st()))
+        return f
+
+    # the INT8 weight-only optimizer step on an [M, K] int8 weight: read q, t1, t2 and write q (6 B / weight)
+    t1s = [torch.randn(M, K, device=dev).bfloat16() * 1e-3 for _ in range(n_sets)]
+
+    def weight_update(i):
+        nv.check(lib.qt_int8_weight_update(qs[i].data_ptr(), row_scales[i].data_ptr(), M, K, 1, t1s[i].data_ptr(), xs[i].data_ptr(),
+                                           -1e-3, 1e-12, 2024, 1 + i, st()))
+
+    # multi-tensor AdamW with bf16 stochastic rounding on 8 tensors of RC / 8 elements (p, g, m, v all bf16: 14 B / parameter)
+    import ctypes
+
+    n_t, per = 8, RC // 8
+    ptr_t, len_t = ctypes.c_void_p * n_t, ctypes.c_int64 * n_t
+    ms_ = [torch.zeros(M, K, dtype=torch.bfloat16, device=dev) for _ in range(n_sets)]
+    vs_ = [torch.zeros(M, K, dtype=torch.bfloat16, device=dev) for _ in range(n_sets)]
+    ps_ = [torch.randn(M, K, device=dev).bfloat16() for _ in range(n_sets)]
+
+    def adamw_multi(i):
+        def tab(t):
+            return ptr_t(*[t.data_ptr() + 2 * per * j for j in range(n_t)])
+        nv.check(lib.qt_adamw_bf16_sr_multi(n_t, tab(ps_[i]), tab(xs[i]), tab(ms_[i]), tab(vs_[i]), len_t(*[per] * n_t), BF16, BF16,
+                                            1e-4, 0.9, 0.999, 0.01, 1e-8, 0.1, 0.0316, 1, 2024, 1 + 8 * i, st()))
+
+    # BitNet weight ternarisation (2-bit packed): read bf16, write a quarter byte per weight
+    bscale = torch.full((1,), 0.8, dtype=torch.float32, device=dev)
+    packed = [torch.empty(RC // 4, dtype=torch.int8, device=dev) for _ in range(n_sets)]
+
+    def ternary(i):
+        nv.check(lib.qt_bitnet_quantize_weight(xs[i].data_ptr(), BF16, RC, bscale.data_ptr(), 1e-5, packed[i].data_ptr(), 1, st()))
+
+    for i in range(n_sets):   # the column-wise kernel and the weight update read what these write
+        col_absmax(i)
+        rowwise(I8, False)(i)
+    cases = [
+        ("rowwise_kernel int8", rowwise(I8, False), 3 * RC + 2 * M),
+        ("rowwise_kernel int8 stochastic", rowwise(I8, True), 3 * RC + 2 * M),
+        ("rowwise_kernel e4m3", rowwise(E4M3, False), 3 * RC + 2 * M),
+        ("rowwise_kernel int8 + column absmax", rowwise_colabs, 3 * RC + 2 * M + 4 * K),
+        ("col_absmax_bf16_kernel", col_absmax, 2 * RC + 4 * K),
+        ("colwise_t_fast_kernel int8 (given column absmax)", colwise_t, 3 * RC + 6 * K),
+        ("tile_1x128_fast_kernel int8", tile(1, I8), 3 * RC + 2 * RC // 128),
+        ("tile_1x128_fast_kernel e4m3", tile(1, E4M3), 3 * RC + 2 * RC // 128),
+        ("tile_128x128_fast_kernel int8", tile(128, I8), 3 * RC + 2 * RC // 16384),
+        ("rowwise_kernel<UPD> int8 weight update (addcdiv, stochastic)", weight_update, 6 * RC + 4 * M),
+        ("adamw_multi_kernel bf16 stochastic", adamw_multi, 14 * RC),
+        ("ternary_kernel 2-bit packed", ternary, 2 * RC + RC // 4),
+    ]
+    out = []
+    for name, fn, nbytes in cases:
+        if only and only not in name:
+            continue
+        ms = _time_graph(fn, n_sets, launches, graph=graph)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out.append({"kernel": name, "us_per_launch": round(ms * 1e3, 2), "algorithmic_bytes": nbytes, "achieved": round(gbs, 1),
+                    "peak": hbm_peak, "unit": "GB/s", "frac": round(gbs / hbm_peak, 3), "frac_of_nominal_8tbs": round(gbs / 8000.0, 3),
+                    "bound": "hbm", "peak_is": f"{peak_kind} STREAM-style copy"})
+    out.append({"shape": [M, K], "launches_per_graph": launches, "buffer_sets": n_sets,
+                "l2": "launches rotate through buffer sets several times larger than L2; timed as CUDA-graph replays"})
+    return out
+
+
 def run_quantize(args):
     """The HBM-bound kernels of the path on one [M, K] bf16 tensor (--mnk M N K; N is ignored; default
-    32768 x 2048, the activation of a 2048-wide layer at 32768 tokens): one JSON line per kernel with
-    its algorithmic bytes, CUDA-event time (median over --steps launches, a 1 GiB memset between
-    launches so no input is left in L2) and the fraction of the measured HBM copy bandwidth."""
+    32768 x 2048, the activation of a 2048-wide layer at 32768 tokens): one JSON line per kernel."""
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
-    import gn_kernels as gk
-
     dev = torch.device("cuda", 0)
     M, _, K = tuple(args.mnk) if args.mnk else (32768, 0, 2048)
-    x = torch.randn(M, K, device=dev).bfloat16()
-    flush = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
-    hbm_peak, _, peak_kind = measured_peaks()
-    colmax = gk.col_absmax(x)
-    RC = M * K
-    cases = [
-        ("rowwise_kernel int8", lambda: gk.quantize_rowwise(x), 2 * RC + RC + 2 * M),
-        ("rowwise_kernel int8 stochastic", lambda: gk.quantize_rowwise(x, torch.int8, True), 2 * RC + RC + 2 * M),
-        ("rowwise_kernel e4m3", lambda: gk.quantize_rowwise(x, torch.float8_e4m3fn), 2 * RC + RC + 2 * M),
-        ("rowwise_kernel int8 + column absmax", lambda: gk.quantize_rowwise_colabsmax(x), 2 * RC + RC + 2 * M + 4 * K),
-        ("col_absmax_bf16_kernel", lambda: gk.col_absmax(x), 2 * RC + 4 * K),
-        ("colwise_t_kernel int8 (given column absmax)", lambda: gk.quantize_colwise_t(x, col_absmax_=colmax), 2 * RC + RC + 4 * K + 2 * K),
-        ("tile_1x128_kernel int8", lambda: gk.quantize_tile(x, (1, 128)), 2 * RC + RC + 2 * RC // 128),
-        ("tile_128x128_kernel int8", lambda: gk.quantize_tile(x, (128, 128)), 2 * RC + RC + 2 * RC // 16384),
-    ]
-    steps = max(args.steps, 5)
-    for name, fn, nbytes in cases:
-        for _ in range(max(args.warmup, 3)):
-            fn()
-        times = []
-        for _ in range(steps):
-            flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            torch.cuda.synchronize()
-            times.append(e0.elapsed_time(e1))
-        ms = statistics.median(times)
-        gbs = nbytes / (ms * 1e-3) / 1e9
-        print(json.dumps({"metric": "quantize_gbs", "kernel": name, "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps,
-                          "ms_per_launch": ms, "higher_is_better": True, "dtype": "bf16->int8/fp8", "data": "synthetic",
-                          "config": {"workload": f"[{M}, {K}] bf16 N(0,1)", "l2": "1 GiB memset between launches"},
-                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
-                                       "peak_is": f"{peak_kind} STREAM-style copy", "algorithmic_bytes": nbytes}}), flush=True)
+    lines = quantize_lines(M, K, max(args.steps, 2), dev, graph=not args.plain_launches, only=args.only)
+    how = lines[-1]
+    for e in lines[:-1]:
+        print(json.dumps({"metric": "quantize_gbs", "kernel": e["kernel"], "value": e["achieved"], "unit": "GB/s", "n_gpus": 1,
+                          "steps": how["launches_per_graph"], "ms_per_launch": e["us_per_launch"] / 1e3, "higher_is_better": True,
+                          "dtype": "bf16->int8/fp8", "data": "synthetic",
+                          "config": {"workload": f"[{M}, {K}] bf16 N(0,1)", "l2": how["l2"], "buffer_sets": how["buffer_sets"]},
+                          "roofline": {k: e[k] for k in ("bound", "achieved", "peak", "unit", "frac", "frac_of_nominal_8tbs", "peak_is", "algorithmic_bytes")}}),
+              flush=True)
 
 
 def main():

@@ -57,6 +57,16 @@ const char* qt_version(void);
  */
 int qt_device_status(int* status_out);
 
+/*
+ * The same word without synchronising: kernels copy the code they record into a pinned host word, and
+ * this reads that word. A non-zero value means some earlier GEMM gave up on a wait and its output is not
+ * valid; a zero says nothing about kernels still running. Does not clear the word (qt_device_status
+ * does). The Python operators call this after every GEMM launch and raise RuntimeError, the counterpart
+ * of the reference's TORCH_CHECK failures (kernels/csrc/cutlass_sm89_fp8.cu:15-16,181) for a failure that
+ * is only known once the kernel has run.
+ */
+int qt_device_status_peek(int* status_out);
+
 /* ---- piece 1: absmax quantize ----------------------------------------------------------- */
 
 /*
@@ -332,10 +342,11 @@ int qt_selftest_division(int q_dtype, float eps, unsigned long long* mismatches)
  * Exercises the bounded-wait path of the GEMM kernels without a GEMM: one warp waits on an mbarrier
  * that nothing arrives on, gives up after 50 ms, records the code 0x7E57 in the device status word
  * and returns. *observed_status receives the word (0x7E57 when the mechanism works); the word is reset
- * to zero before the call returns. Fails if the word was already set. Synchronises the device.
+ * to zero before the call returns unless leave_set is non-zero (then the next qt_device_status call
+ * clears it). Fails if the word was already set. Synchronises the device.
  * Test utility; no counterpart in the reference.
  */
-int qt_selftest_wait_timeout(int* observed_status);
+int qt_selftest_wait_timeout(int* observed_status, int leave_set);
 
 #ifdef __cplusplus
 }

@@ -44,6 +44,8 @@ inline int fail(int code, const char* fmt, ...) {
 // Device status word: kernels that give up on a bounded wait store a non-zero code here.
 // One word per device, reached through this accessor (address resolved per device).
 int device_status_ptr(int** out);
+// Host address of the pinned word that mirrors the current device's status (nullptr before first use).
+volatile int* device_status_host_word();
 
 inline int num_sms() {
     static int cached[64] = {0};

@@ -137,7 +137,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const uint32_t smem_base = smem_u32(smem);
     if ((smem_base & 1023u) != 0u) {
         // the 128-byte swizzle of the TMA boxes and UMMA descriptors assumes this alignment
-        if (threadIdx.x == 0) atomicCAS(p.status, 0, 0x900);
+        if (threadIdx.x == 0) record_status(p.status, 0x900);
         return;
     }
     volatile uint32_t* s_tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + C::SMEM_TMEMPTR_OFF);
@@ -781,7 +781,7 @@ __global__ void wait_timeout_selftest_kernel(int* status) {
 }  // namespace
 }  // namespace qt
 
-extern "C" int qt_selftest_wait_timeout(int* observed_status) {
+extern "C" int qt_selftest_wait_timeout(int* observed_status, int leave_set) {
     QT_REQUIRE(observed_status, "selftest_wait_timeout: null output");
     int* status = nullptr;
     if (int rc = device_status_ptr(&status)) return rc;
@@ -793,7 +793,10 @@ extern "C" int qt_selftest_wait_timeout(int* observed_status) {
     QT_CUDA_CHECK(cudaGetLastError());
     QT_CUDA_CHECK(cudaDeviceSynchronize());
     QT_CUDA_CHECK(cudaMemcpy(observed_status, status, sizeof(int), cudaMemcpyDeviceToHost));
-    QT_CUDA_CHECK(cudaMemset(status, 0, sizeof(int)));   // the word is clean again for the real kernels
+    if (!leave_set) {   // the word is clean again for the real kernels
+        QT_CUDA_CHECK(cudaMemset(status, 0, sizeof(int)));
+        if (volatile int* h = device_status_host_word()) *h = 0;
+    }
     return QT_OK;
 }
 

@@ -110,6 +110,32 @@ struct Divider {
     }
 };
 
+// The same division for two values at once on the packed fp32x2 instructions of sm_100 (one issue slot
+// per pair): q0 = x * r, e = x - q0 * d, q = q0 + e * r, each lane rounded like the scalar sequence.
+struct Divider2 {
+    float2 r, nd;   // reciprocal and negated divisor per lane
+    __device__ __forceinline__ explicit Divider2(float d) {
+        const float rr = recip_rn(d);
+        r = make_float2(rr, rr);
+        nd = make_float2(-d, -d);
+    }
+    __device__ __forceinline__ Divider2(float d0, float r0, float d1, float r1) : r(make_float2(r0, r1)), nd(make_float2(-d0, -d1)) {}
+    __device__ __forceinline__ float2 operator()(float2 x) const {
+        const float2 q0 = __fmul2_rn(x, r);
+        const float2 e = __ffma2_rn(q0, nd, x);
+        return __ffma2_rn(e, r, q0);
+    }
+};
+
+// absmax / qmax, correctly rounded, for qmax in {127, 448, 57344}: the reciprocal sequence with a constant
+// reciprocal (qt_selftest_division checks it against div.rn for every bf16 absmax). Results that are not
+// normal numbers (absmax below 2^-100) take div.rn.
+__device__ __forceinline__ float scale_of(float amax, float qmax, float rq) {
+    if (amax < 7.8886090522101181e-31f) return div_rn(amax, qmax);
+    const float q0 = __fmul_rn(amax, rq);
+    return __fmaf_rn(__fmaf_rn(-q0, qmax, amax), rq, q0);
+}
+
 // ---- rounding to a byte ---------------------------------------------------------------------
 
 // int8 from a pre-divided value, round-half-even, clamp [-128, 127]. Clamping before rounding is
@@ -194,18 +220,6 @@ __device__ __forceinline__ void uniforms4(float (&u)[4], int64_t idx, uint64_t s
     }
 }
 
-// Uniforms for 8 consecutive elements starting at linear index idx.
-__device__ __forceinline__ void uniforms8(float (&u)[8], int64_t idx, uint64_t seed, uint64_t offset) {
-    if ((idx & 7) == 0) {
-        const Philox4 a = philox4x32_10((uint64_t)idx >> 3, offset, seed);
-        u[0] = u01_from_half(a.x, 0); u[1] = u01_from_half(a.x, 1); u[2] = u01_from_half(a.y, 0); u[3] = u01_from_half(a.y, 1);
-        u[4] = u01_from_half(a.z, 0); u[5] = u01_from_half(a.z, 1); u[6] = u01_from_half(a.w, 0); u[7] = u01_from_half(a.w, 1);
-    } else {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) u[k] = uniform1(idx + k, seed, offset);
-    }
-}
-
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
@@ -257,8 +271,7 @@ struct RowwiseParams {
 __device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t w) { return *reinterpret_cast<const __nv_bfloat162*>(&w); }
 __device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<const uint32_t*>(&v); }
 
-// |x| of both halves (clear the sign bits) and the lane-wise maximum of two packed pairs.
-__device__ __forceinline__ uint32_t abs2(uint32_t w) { return w & 0x7FFF7FFFu; }
+// Lane-wise maximum of two packed bf16 pairs.
 __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) { return as_u32(__hmax2(as_bf162(a), as_bf162(b))); }
 
 // Four rounded floats (value + kRoundMagic) -> four int8 bytes: the low mantissa byte of each.
@@ -278,47 +291,76 @@ __device__ __forceinline__ uint32_t pack4_sat(float q0, float q1, float q2, floa
     return w;
 }
 
-// Quantize the 8 bf16 values of `raw` (element index idx of the output) with divider `div`.
-// No clamp on the round-half-even int8 path: |x| <= absmax and d >= absmax/127 * (1 - 2^-24) bound
-// the quotient by 127.00001, which rounds to 127.
+// max(|a|, |b|) of both bf16 halves in one instruction. The sign bits of the result are the XOR of the
+// operands' signs (callers mask them off once, after the last fold), so no separate |x| is needed.
+__device__ __forceinline__ uint32_t amax2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// The larger of the two (sign-cleared) bf16 halves as the bit pattern of an fp32 value. Bit patterns of
+// non-negative floats order like unsigned integers.
+__device__ __forceinline__ uint32_t fold_halves(uint32_t m) {
+    const uint32_t lo = (m << 16) & 0x7FFF0000u, hi = m & 0x7FFF0000u;
+    return lo > hi ? lo : hi;
+}
+
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+
+// Quantize the 8 bf16 values of `raw` (element index idx of the output, a multiple of 8) with divider
+// `div`, two elements per packed fp32x2 instruction.
+// int8, round-half-even: add 1.5 * 2^23, the low mantissa byte is the result. No clamp: |x| <= absmax and
+// d >= absmax/127 * (1 - 2^-24) bound the quotient by 127 + 2^-17, which rounds to 127.
+// int8, stochastic: floor(fl(v + u)) with u = 16 Philox bits * 2^-16. The uniform is built without an
+// integer-to-float conversion: OR-ing the 16 bits under the mantissa of 192.0 gives 192 + u exactly, and
+// subtracting 192 is exact. fl(v + u) <= 128 - 2^-17 and >= -128, so again no clamp; adding 1.5 * 2^23
+// rounding toward minus infinity leaves floor() in the low mantissa byte.
+// fp8: cvt.rn.satfinite of the quotient; the reciprocal sequence returns +0 for x = -0, so the sign of
+// the input is OR-ed back into the byte (a quotient never has the opposite sign of x).
 template <bool SR>
-__device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider<false>& div, int q_dtype, int64_t idx,
+__device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider2& div, int q_dtype, int64_t idx,
                                                uint64_t seed, uint64_t offset) {
-    float f[8];
-    f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xFFFF0000u);
-    f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xFFFF0000u);
-    f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xFFFF0000u);
-    f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xFFFF0000u);
-    float v[8];
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float2 v[4];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) v[k] = div(f[k]);
+    for (int k = 0; k < 4; ++k) v[k] = div(unpack_bf16x2(w[k]));
     uint2 out;
     if (q_dtype == QT_I8) {
+        const float2 magic2 = make_float2(kRoundMagic, kRoundMagic);
         if constexpr (SR) {
-            float u[8];
-            uniforms8(u, idx, seed, offset);
+            const Philox4 a = philox4x32_10((uint64_t)idx >> 3, offset, seed);
+            const uint32_t rw[4] = {a.x, a.y, a.z, a.w};
+            const float2 m192 = make_float2(-192.0f, -192.0f);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) v[k] = __fadd_rd(fminf(fmaxf(__fadd_rn(v[k], u[k]), -128.0f), 127.5f), kRoundMagic);
-            out.x = pack4_magic(v[0], v[1], v[2], v[3]);
-            out.y = pack4_magic(v[4], v[5], v[6], v[7]);
+            for (int k = 0; k < 4; ++k) {
+                const float2 big = make_float2(__uint_as_float(__byte_perm(rw[k], 0x43400000u, 0x7610)),
+                                               __uint_as_float(__byte_perm(rw[k], 0x43400000u, 0x7632)));
+                v[k] = __fadd2_rd(__fadd2_rn(v[k], __fadd2_rn(big, m192)), magic2);
+            }
         } else {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) v[k] = __fadd_rn(v[k], kRoundMagic);
-            out.x = pack4_magic(v[0], v[1], v[2], v[3]);
-            out.y = pack4_magic(v[4], v[5], v[6], v[7]);
+            for (int k = 0; k < 4; ++k) v[k] = __fadd2_rn(v[k], magic2);
         }
+        out.x = pack4_magic(v[0].x, v[0].y, v[1].x, v[1].y);
+        out.y = pack4_magic(v[2].x, v[2].y, v[3].x, v[3].y);
     } else {
-        const __nv_fp8_interpretation_t kind = (q_dtype == QT_E4M3) ? __NV_E4M3 : __NV_E5M2;
         uint32_t h[4];
 #pragma unroll
-        for (int k = 0; k < 8; k += 2) {
-            // the reciprocal sequence returns +0 for x = -0; restore the sign of zero inputs
-            const float a = (f[k] == 0.0f) ? f[k] : v[k];
-            const float b = (f[k + 1] == 0.0f) ? f[k + 1] : v[k + 1];
-            h[k >> 1] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, kind);
+        for (int k = 0; k < 4; ++k) {
+            uint16_t two;
+            if (q_dtype == QT_E4M3) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(two) : "f"(v[k].y), "f"(v[k].x));
+            else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(two) : "f"(v[k].y), "f"(v[k].x));
+            h[k] = two;
         }
-        out.x = h[0] | (h[1] << 16);
-        out.y = h[2] | (h[3] << 16);
+        // sign bytes (0x00 / 0xFF) of the eight inputs in output order, then their top bits
+        uint32_t s_lo, s_hi;   // selector nibbles with bit 3 set replicate the selected byte's top bit
+        asm("prmt.b32 %0, %1, %2, 0xFDB9;" : "=r"(s_lo) : "r"(w[0]), "r"(w[1]));
+        asm("prmt.b32 %0, %1, %2, 0xFDB9;" : "=r"(s_hi) : "r"(w[2]), "r"(w[3]));
+        out.x = __byte_perm(h[0], h[1], 0x5410) | (s_lo & 0x80808080u);
+        out.y = __byte_perm(h[2], h[3], 0x5410) | (s_hi & 0x80808080u);
     }
     return out;
 }
@@ -361,14 +403,26 @@ __device__ __forceinline__ uint4 updated_vec8(uint2 qb, float s, const uint4& a,
 // With UPD != 0 the kernel re-quantizes an int8 weight in place: the "row" is the updated weight formed
 // by updated_vec8 from q, scale and the operand tensors; q and scale are then overwritten (each row
 // is complete in registers before its bytes are stored, and a prefetched row is a different row).
+// Barrier among the TPR threads of row group `sub` (at most four groups of several warps per CTA). The
+// barrier number is an immediate so that the CTA reserves five hardware barriers, not all sixteen.
+template <int TPR>
+__device__ __forceinline__ void row_barrier(int sub) {
+    switch (sub) {
+        case 0: asm volatile("bar.sync 1, %0;" ::"n"(TPR) : "memory"); break;
+        case 1: asm volatile("bar.sync 2, %0;" ::"n"(TPR) : "memory"); break;
+        case 2: asm volatile("bar.sync 3, %0;" ::"n"(TPR) : "memory"); break;
+        default: asm volatile("bar.sync 4, %0;" ::"n"(TPR) : "memory"); break;
+    }
+}
+
 template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0, bool SCATTER = false>
 __global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1)))
 rowwise_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;  // rows per CTA per iteration
     constexpr int WPR = TPR / 32;        // warps per row
     // the column-maxima variant spends its registers on the maxima instead of a second row buffer
-    constexpr bool PREFETCH = VPT <= 4 && !COLABS;
-    __shared__ float s_red[kThreads / 32];
+    constexpr bool PREFETCH = VPT <= 8 && !COLABS;
+    __shared__ uint32_t s_red[2][kThreads / 32];
     __shared__ uint32_t s_col[COLABS ? TPR * VPT * 4 : 1];  // packed bf16 pairs, one per two columns
 
     const int sub = threadIdx.x / TPR;
@@ -376,6 +430,7 @@ rowwise_kernel(const RowwiseParams p) {
     const int warp = threadIdx.x >> 5;
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x);
     const float qmax = qmax_of(p.q_dtype);
+    const float rqmax = p.q_dtype == QT_I8 ? (1.0f / 127.0f) : (p.q_dtype == QT_E4M3 ? (1.0f / 448.0f) : (1.0f / 57344.0f));
     const int64_t step = (int64_t)gridDim.x * RPC;
 
     uint32_t colmax[COLABS ? VPT : 1][4];
@@ -418,40 +473,34 @@ rowwise_kernel(const RowwiseParams p) {
         }
     };
 
-    uint4 cur[VPT], nxt[PREFETCH ? VPT : 1];
-    int64_t base = (int64_t)blockIdx.x * RPC;
-    if (base < p.rows) load_row(cur, base + sub);
-
-    for (; base < p.rows; base += step) {
-        const int64_t row = base + sub;
+    // One row held in `cur`: fold its absmax, derive the scale, quantize and store. `parity` alternates
+    // between consecutive calls: rows spanning several warps exchange their partial maxima through one of
+    // two shared-memory slots and meet at a barrier of their own (the row's TPR threads only), so one
+    // barrier per row is enough and the CTA's other rows are not held up.
+    auto process = [&](uint4 (&cur)[VPT], int64_t row, int parity) {
         const bool valid = row < p.rows;
-        if constexpr (PREFETCH) {
-            if (base + step < p.rows) load_row(nxt, base + step + sub);
-        }
-
         uint32_t m2 = 0u;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const uint32_t a0 = abs2(cur[i].x), a1 = abs2(cur[i].y), a2 = abs2(cur[i].z), a3 = abs2(cur[i].w);
-            m2 = max2(m2, max2(max2(a0, a1), max2(a2, a3)));
+            m2 = amax2(m2, amax2(amax2(cur[i].x, cur[i].y), amax2(cur[i].z, cur[i].w)));
             if constexpr (COLABS) {
-                colmax[i][0] = max2(colmax[i][0], a0); colmax[i][1] = max2(colmax[i][1], a1);
-                colmax[i][2] = max2(colmax[i][2], a2); colmax[i][3] = max2(colmax[i][3], a3);
+                colmax[i][0] = amax2(colmax[i][0], cur[i].x); colmax[i][1] = amax2(colmax[i][1], cur[i].y);
+                colmax[i][2] = amax2(colmax[i][2], cur[i].z); colmax[i][3] = amax2(colmax[i][3], cur[i].w);
             }
         }
-        float amax = fmaxf(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xFFFF0000u));
-        amax = warp_max(amax);
+        uint32_t abits = __reduce_max_sync(0xFFFFFFFFu, fold_halves(m2));
         if constexpr (WPR > 1) {
-            if ((threadIdx.x & 31) == 0) s_red[warp] = amax;
-            __syncthreads();
-            amax = s_red[sub * WPR];
+            if ((threadIdx.x & 31) == 0) s_red[parity][warp] = abits;
+            if constexpr (RPC == 1) __syncthreads();
+            else row_barrier<TPR>(sub);
+            abits = s_red[parity][sub * WPR];
 #pragma unroll
-            for (int w = 1; w < WPR; ++w) amax = fmaxf(amax, s_red[sub * WPR + w]);
-            __syncthreads();
+            for (int w = 1; w < WPR; ++w) { const uint32_t o = s_red[parity][sub * WPR + w]; abits = o > abits ? o : abits; }
         }
+        const float amax = __uint_as_float(abits);
 
-        const float scale = div_rn(amax, qmax);
-        const Divider<false> div(fmaxf(scale, p.eps));
+        const float scale = scale_of(amax, qmax, rqmax);
+        const Divider2 div(fmaxf(scale, p.eps));
         if constexpr (SCATTER) {
             if (valid && t == 0)
                 for (int d = 0; d < p.n_dst; ++d) store_scale(p.scale_dst[d], p.scale_dtype, p.dst_row0 + row, scale);
@@ -460,11 +509,12 @@ rowwise_kernel(const RowwiseParams p) {
         }
 
         uint8_t* qrow = p.q + row * p.cols;
+        const int64_t idx0 = SR ? row * p.cols : 0;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int col = (i * TPR + t) * 8;
             if (valid && col < p.cols) {
-                const uint2 bytes = quantize_vec8<SR>(cur[i], div, p.q_dtype, SR ? row * p.cols + col : 0, p.seed, p.offset);
+                const uint2 bytes = quantize_vec8<SR>(cur[i], div, p.q_dtype, idx0 + col, p.seed, p.offset);
                 if constexpr (SCATTER) {
                     const int64_t at = (p.dst_row0 + row) * p.cols + col;
                     for (int d = 0; d < p.n_dst; ++d) *reinterpret_cast<uint2*>(p.q_dst[d] + at) = bytes;
@@ -473,12 +523,30 @@ rowwise_kernel(const RowwiseParams p) {
                 }
             }
         }
+    };
 
-        if constexpr (PREFETCH) {
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) cur[i] = nxt[i];
-        } else {
-            if (base + step < p.rows) load_row(cur, base + step + sub);
+    int64_t base = (int64_t)blockIdx.x * RPC;
+    if constexpr (PREFETCH) {
+        // register double buffer, unrolled by two so the prefetched row is never copied: while one buffer
+        // is reduced and quantized the loads of the row after it are in flight in the other
+        uint4 a[VPT], b[VPT];
+        if (base < p.rows) load_row(a, base + sub);
+        while (base < p.rows) {
+            if (base + step < p.rows) load_row(b, base + step + sub);
+            process(a, base + sub, 0);
+            base += step;
+            if (base >= p.rows) break;
+            if (base + step < p.rows) load_row(a, base + step + sub);
+            process(b, base + sub, 1);
+            base += step;
+        }
+    } else {
+        uint4 a[VPT];
+        int parity = 0;
+        for (; base < p.rows; base += step) {
+            load_row(a, base + sub);
+            process(a, base + sub, parity);
+            parity ^= 1;
         }
     }
 
@@ -494,7 +562,7 @@ rowwise_kernel(const RowwiseParams p) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
                             const int pair = (i * TPR + t) * 4 + k;
-                            s_col[pair] = max2(s_col[pair], colmax[i][k]);
+                            s_col[pair] = max2(s_col[pair], colmax[i][k] & 0x7FFF7FFFu);
                         }
                 }
                 __syncthreads();
@@ -503,7 +571,7 @@ rowwise_kernel(const RowwiseParams p) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) s_col[(i * TPR + t) * 4 + k] = colmax[i][k];
+                for (int k = 0; k < 4; ++k) s_col[(i * TPR + t) * 4 + k] = colmax[i][k] & 0x7FFF7FFFu;
         }
         // 2. fold the CTAs of the thread-block cluster through distributed shared memory; each CTA
         //    owns a slice of the columns and issues one atomic max per column for the whole cluster
@@ -698,20 +766,20 @@ __global__ void __launch_bounds__(kThreads) col_absmax_bf16_kernel(const __nv_bf
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                m[0] = max2(m[0], abs2(v[j].x)); m[1] = max2(m[1], abs2(v[j].y));
-                m[2] = max2(m[2], abs2(v[j].z)); m[3] = max2(m[3], abs2(v[j].w));
+                m[0] = amax2(m[0], v[j].x); m[1] = amax2(m[1], v[j].y);
+                m[2] = amax2(m[2], v[j].z); m[3] = amax2(m[3], v[j].w);
             }
         }
         for (; r < r1; r += 8) {
             uint4 v;
             if (full) v = *reinterpret_cast<const uint4*>(x + r * stride + col);
             else { Vec8<__nv_bfloat16> t; load_vec8<__nv_bfloat16>(t, x + r * stride, col, cols, false); v = t.raw; }
-            m[0] = max2(m[0], abs2(v.x)); m[1] = max2(m[1], abs2(v.y));
-            m[2] = max2(m[2], abs2(v.z)); m[3] = max2(m[3], abs2(v.w));
+            m[0] = amax2(m[0], v.x); m[1] = amax2(m[1], v.y);
+            m[2] = amax2(m[2], v.z); m[3] = amax2(m[3], v.w);
         }
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) s_m[warp][lane * 4 + k] = m[k];
+    for (int k = 0; k < 4; ++k) s_m[warp][lane * 4 + k] = m[k] & 0x7FFF7FFFu;   // amax2 leaves the sign bits undefined
     __syncthreads();
     if (threadIdx.x < 128) {
         uint32_t f = 0u;
@@ -929,16 +997,18 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_fast_kernel(const Colwi
     };
     auto quantize_tile = [&](const uint4 (&v)[4], uint32_t (*tile)[kTileR / 4 + 1]) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            float q[4];
+        for (int k2 = 0; k2 < 4; ++k2) {
+            // columns 2*k2 and 2*k2 + 1 are the two halves of one loaded word: one packed division per row
+            const Divider2 div(dsc[2 * k2], rcp[2 * k2], dsc[2 * k2 + 1], rcp[2 * k2 + 1]);
+            float2 q[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint32_t w = (k >> 1) == 0 ? v[j].x : ((k >> 1) == 1 ? v[j].y : ((k >> 1) == 2 ? v[j].z : v[j].w));
-                const float f = __uint_as_float((k & 1) ? (w & 0xFFFF0000u) : (w << 16));
-                const float q0 = __fmul_rn(f, rcp[k]);
-                q[j] = __fmaf_rn(__fmaf_rn(-q0, dsc[k], f), rcp[k], q0);
+                const uint32_t w = k2 == 0 ? v[j].x : (k2 == 1 ? v[j].y : (k2 == 2 ? v[j].z : v[j].w));
+                q[j] = div(unpack_bf16x2(w));
             }
-            tile[cg * 8 + k][st_word] = pack4_sat(q[0], q[1], q[2], q[3]);   // saturating: col_absmax is the caller's
+            // saturating: col_absmax is the caller's
+            tile[cg * 8 + 2 * k2][st_word] = pack4_sat(q[0].x, q[1].x, q[2].x, q[3].x);
+            tile[cg * 8 + 2 * k2 + 1][st_word] = pack4_sat(q[0].y, q[1].y, q[2].y, q[3].y);
         }
     };
     auto store_tile = [&](uint32_t (*tile)[kTileR / 4 + 1]) {
@@ -1036,7 +1106,7 @@ __global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p
                 if (l16 == 0) store_scale(p.scale, p.scale_dtype, row * p.scale_cols + (col >> 7), sc);
                 uint2 bytes;
                 if constexpr (sizeof(XT) == 2 && !EXACT_DIV) {
-                    bytes = quantize_vec8<false>(v[j].raw, div, p.q_dtype, 0, 0, 0);
+                    bytes = quantize_vec8<false>(v[j].raw, Divider2(div.d, div.r, div.d, div.r), p.q_dtype, 0, 0, 0);
                 } else {
                     divide8(f, div, p.q_dtype != QT_I8);
                     bytes = pack8(f, p.q_dtype, false, zero_u);
@@ -1089,7 +1159,7 @@ __global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams
         if (row < p.rows && col < p.cols) {
             uint2 bytes;
             if constexpr (sizeof(XT) == 2 && !EXACT_DIV) {
-                bytes = quantize_vec8<false>(v[i].raw, div, p.q_dtype, 0, 0, 0);
+                bytes = quantize_vec8<false>(v[i].raw, Divider2(div.d, div.r, div.d, div.r), p.q_dtype, 0, 0, 0);
             } else {
                 float f[8];
                 v[i].unpack(f);
@@ -1098,6 +1168,132 @@ __global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams
             }
             store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
         }
+    }
+}
+
+// 1 x 128 tiles, the common case with everything that costs instructions removed: bf16 input, whole
+// tiles (cols a multiple of 128), 16-byte aligned rows, eps >= 1e-30. Eight lanes own one tile: lane l of
+// the group holds elements [8l, 8l + 8) and [64 + 8l, 64 + 8l + 8), so each of the two loads of a group
+// covers 128 contiguous bytes, the tile's absmax is one 8-lane reduction and the per-tile scalar work
+// (scale, reciprocal, scale store) is shared by 16 elements per thread. `tpr` threads (a power of two,
+// 8..256) span a chunk of tpr * 16 columns of one row, the CTA's other threads take further rows; an item
+// is two such row groups, and the next item's loads are issued before the current one is quantized.
+__global__ void __launch_bounds__(kThreads, 3) tile_1x128_fast_kernel(const TileParams p, int tpr_log2) {
+    constexpr int ROWS = 2;
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x);
+    const float qmax = qmax_of(p.q_dtype);
+    const float rqmax = p.q_dtype == QT_I8 ? (1.0f / 127.0f) : (p.q_dtype == QT_E4M3 ? (1.0f / 448.0f) : (1.0f / 57344.0f));
+    const int tpr = 1 << tpr_log2;
+    const int rpp = kThreads >> tpr_log2;            // rows per pass
+    const int sub = threadIdx.x >> tpr_log2, t = threadIdx.x & (tpr - 1);
+    const int l8 = threadIdx.x & 7;
+    const uint32_t gmask = 0xFFu << (threadIdx.x & 24);   // the 8 lanes of this thread's tile
+    const int chunk_cols = tpr * 16;
+    const uint32_t chunks = (uint32_t)((p.cols + chunk_cols - 1) / chunk_cols);
+    const uint32_t row_blocks = (uint32_t)((p.rows + ROWS * rpp - 1) / (ROWS * rpp));
+    const uint32_t items = row_blocks * chunks;
+    const int col_in_chunk = (t >> 3) * 128 + l8 * 8;
+
+    auto load_item = [&](uint4 (&v)[ROWS][2], uint32_t item) {
+        const uint32_t rblk = item / chunks, chunk = item - rblk * chunks;
+        const int64_t col = (int64_t)chunk * chunk_cols + col_in_chunk;
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            const int64_t row = ((int64_t)rblk * ROWS + j) * rpp + sub;
+            if (row < p.rows && col < p.cols) {
+                const uint4* src = reinterpret_cast<const uint4*>(x + row * p.stride + col);
+                v[j][0] = src[0];
+                v[j][1] = src[8];
+            } else {
+                v[j][0] = make_uint4(0, 0, 0, 0);
+                v[j][1] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    auto process = [&](const uint4 (&v)[ROWS][2], uint32_t item) {
+        const uint32_t rblk = item / chunks, chunk = item - rblk * chunks;
+        const int64_t col = (int64_t)chunk * chunk_cols + col_in_chunk;
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            const int64_t row = ((int64_t)rblk * ROWS + j) * rpp + sub;
+            const uint32_t m2 = amax2(amax2(amax2(v[j][0].x, v[j][0].y), amax2(v[j][0].z, v[j][0].w)),
+                                      amax2(amax2(v[j][1].x, v[j][1].y), amax2(v[j][1].z, v[j][1].w)));
+            // all 8 lanes of a tile take part (out-of-range lanes hold zeros)
+            const float amax = __uint_as_float(__reduce_max_sync(gmask, fold_halves(m2)));
+            const float sc = scale_of(amax, qmax, rqmax);
+            const Divider2 div(fmaxf(sc, p.eps));
+            if (row < p.rows && col < p.cols) {
+                if (l8 == 0) store_scale(p.scale, p.scale_dtype, row * p.scale_cols + (col >> 7), sc);
+                uint8_t* dst = p.q + row * p.cols + col;
+                *reinterpret_cast<uint2*>(dst) = quantize_vec8<false>(v[j][0], div, p.q_dtype, 0, 0, 0);
+                *reinterpret_cast<uint2*>(dst + 64) = quantize_vec8<false>(v[j][1], div, p.q_dtype, 0, 0, 0);
+            }
+        }
+    };
+
+    uint4 a[ROWS][2], b[ROWS][2];
+    uint32_t item = blockIdx.x;
+    if (item < items) load_item(a, item);
+    while (item < items) {
+        if (item + gridDim.x < items) load_item(b, item + gridDim.x);
+        process(a, item);
+        item += gridDim.x;
+        if (item >= items) break;
+        if (item + gridDim.x < items) load_item(a, item + gridDim.x);
+        process(b, item);
+        item += gridDim.x;
+    }
+}
+
+// 128 x 128 tiles, the same common case (bf16, rows and cols multiples of 128, aligned): a CTA walks
+// tiles with a register double buffer; thread (r16, c16) holds 8 vectors of a tile (rows r16 + 16 i).
+__global__ void __launch_bounds__(kThreads, 2) tile_128x128_fast_kernel(const TileParams p) {
+    __shared__ uint32_t s_red[2][kThreads / 32];
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x);
+    const float qmax = qmax_of(p.q_dtype);
+    const float rqmax = p.q_dtype == QT_I8 ? (1.0f / 127.0f) : (p.q_dtype == QT_E4M3 ? (1.0f / 448.0f) : (1.0f / 57344.0f));
+    const int c16 = threadIdx.x & 15, r16 = threadIdx.x >> 4;
+    const uint32_t tiles_c = (uint32_t)p.scale_cols;
+    const uint32_t tiles = (uint32_t)(p.rows / 128) * tiles_c;
+    const int64_t pitch16 = p.stride / 8;   // row pitch in 16-byte units
+
+    auto load_tile = [&](uint4 (&v)[8], uint32_t tile) {
+        const uint32_t tr = tile / tiles_c, tc = tile - tr * tiles_c;
+        const uint4* src = reinterpret_cast<const uint4*>(x + ((int64_t)tr * 128 + r16) * p.stride + (int64_t)tc * 128 + c16 * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = src[(int64_t)i * 16 * pitch16];
+    };
+    auto process = [&](const uint4 (&v)[8], uint32_t tile, int parity) {
+        const uint32_t tr = tile / tiles_c, tc = tile - tr * tiles_c;
+        uint32_t m2 = 0u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m2 = amax2(m2, amax2(amax2(v[i].x, v[i].y), amax2(v[i].z, v[i].w)));
+        uint32_t abits = __reduce_max_sync(0xFFFFFFFFu, fold_halves(m2));
+        if ((threadIdx.x & 31) == 0) s_red[parity][threadIdx.x >> 5] = abits;
+        __syncthreads();   // one barrier per tile: the next tile uses the other slot
+        abits = s_red[parity][0];
+#pragma unroll
+        for (int w = 1; w < kThreads / 32; ++w) { const uint32_t o = s_red[parity][w]; abits = o > abits ? o : abits; }
+        const float sc = scale_of(__uint_as_float(abits), qmax, rqmax);
+        const Divider2 div(fmaxf(sc, p.eps));
+        if (threadIdx.x == 0) store_scale(p.scale, p.scale_dtype, (int64_t)tr * p.scale_cols + tc, sc);
+        uint8_t* dst = p.q + ((int64_t)tr * 128 + r16) * p.cols + (int64_t)tc * 128 + c16 * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<uint2*>(dst + (int64_t)i * 16 * p.cols) = quantize_vec8<false>(v[i], div, p.q_dtype, 0, 0, 0);
+    };
+
+    uint4 a[8], b[8];
+    uint32_t tile = blockIdx.x;
+    if (tile < tiles) load_tile(a, tile);
+    while (tile < tiles) {
+        if (tile + gridDim.x < tiles) load_tile(b, tile + gridDim.x);
+        process(a, tile, 0);
+        tile += gridDim.x;
+        if (tile >= tiles) break;
+        if (tile + gridDim.x < tiles) load_tile(a, tile + gridDim.x);
+        process(b, tile, 1);
+        tile += gridDim.x;
     }
 }
 
@@ -1112,6 +1308,12 @@ __global__ void division_selftest_kernel(int q_dtype, float eps, unsigned long l
         const float a = bf16_bits_to_float(abits);
         const float d = fmaxf(__fdiv_rn(a, qmax), eps);
         const Divider<false> fast(d);
+        const Divider2 fast2(d);
+        // the scale itself: constant-reciprocal sequence against div.rn
+        if (threadIdx.x == 0) {
+            const float rq = q_dtype == QT_I8 ? (1.0f / 127.0f) : (q_dtype == QT_E4M3 ? (1.0f / 448.0f) : (1.0f / 57344.0f));
+            bad += (__float_as_uint(scale_of(a, qmax, rq)) != __float_as_uint(__fdiv_rn(a, qmax)));
+        }
         for (uint32_t xb = threadIdx.x; xb <= abits; xb += blockDim.x) {
             const float x = bf16_bits_to_float(xb);
             const float want = __fdiv_rn(x, d);
@@ -1121,6 +1323,9 @@ __global__ void division_selftest_kernel(int q_dtype, float eps, unsigned long l
             bad += (__float_as_uint(want) != __float_as_uint(got));
             const float want_n = __fdiv_rn(-x, d), got_n = keep ? -x : fast(-x);
             bad += (__float_as_uint(want_n) != __float_as_uint(got_n));
+            // the packed form used by the kernels: both lanes, both signs
+            const float2 got2 = fast2(make_float2(x, -x));
+            bad += (!keep && __float_as_uint(got2.x) != __float_as_uint(want)) + (!keep && __float_as_uint(got2.y) != __float_as_uint(want_n));
             bad_q += (quantize_byte(want, q_dtype, false, 0.f) != quantize_byte(got, q_dtype, false, 0.f));
             bad_q += (quantize_byte(want_n, q_dtype, false, 0.f) != quantize_byte(got_n, q_dtype, false, 0.f));
         }
@@ -1254,6 +1459,26 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
     const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
     p.vec_load = aligned_to(x, 16) && ((x_row_stride * esz) % 16 == 0);
     p.vec_store = aligned_to(q, 8) && (cols % 8 == 0);
+    const bool fast = x_dtype == QT_BF16 && eps >= 1e-30f && p.vec_load && p.vec_store && cols % 128 == 0;
+    if (tile_r == 1 && fast) {
+        int tpr_log2 = 3;  // at least one 8-lane tile group per row
+        while (tpr_log2 < 8 && ((int64_t)16 << tpr_log2) < cols) ++tpr_log2;
+        const int tpr = 1 << tpr_log2, rpp = kThreads / tpr;
+        const int64_t items = ((rows + 2 * rpp - 1) / (2 * rpp)) * ((cols + tpr * 16 - 1) / (tpr * 16));
+        if (items < (int64_t)1 << 31) {
+            const int64_t cap = (int64_t)num_sms() * 3;
+            tile_1x128_fast_kernel<<<(unsigned)(items < cap ? items : cap), kThreads, 0, stream>>>(p, tpr_log2);
+            QT_CUDA_CHECK(cudaGetLastError());
+            return QT_OK;
+        }
+    }
+    if (tile_r == 128 && fast && rows % 128 == 0 && (rows / 128) * p.scale_cols < ((int64_t)1 << 31)) {
+        const int64_t tiles = (rows / 128) * p.scale_cols;
+        const int64_t cap = (int64_t)num_sms() * 2;
+        tile_128x128_fast_kernel<<<(unsigned)(tiles < cap ? tiles : cap), kThreads, 0, stream>>>(p);
+        QT_CUDA_CHECK(cudaGetLastError());
+        return QT_OK;
+    }
     if (tile_r == 1) {
         int tpr_log2 = 4;  // at least one 16-lane tile group per row
         while (tpr_log2 < 8 && ((int64_t)8 << tpr_log2) < cols) ++tpr_log2;
@@ -1276,7 +1501,7 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
     return QT_OK;
 }
 
-// ---- allocation-free column-wise quantize ---------------------------------------------------------
+// ---- row-wise quantize fused with the all-gather of a row-sharded weight ---------------------------
 
 extern "C" int qt_quantize_rowwise_scatter(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
                                           int n_dst, void* const* q_dst, void* const* scale_dst, int64_t dst_row0,
@@ -1322,6 +1547,8 @@ extern "C" int qt_int8_weight_update(void* q, void* scale, int64_t rows, int64_t
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     return mode == 0 ? launch_rowwise_bf16<false, true, 1>(p, stream) : launch_rowwise_bf16<false, true, 2>(p, stream);
 }
+
+// ---- allocation-free column-wise quantize ---------------------------------------------------------
 
 // Scratch for qt_quantize_colwise_t_noalloc: the per-column absmax that the two-call form keeps in
 // a caller-allocated buffer. It lives in the library's own image (256 KB on every GPU that loads

@@ -41,6 +41,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Records `code` in the device status block (first code wins) and copies it to the pinned host word whose
+// device-visible address sits 8 bytes into the block, so the host sees it without synchronising.
+__device__ __forceinline__ void record_status(int* status, int code) {
+    if (atomicCAS(status, 0, code) == 0) {
+        volatile int* mirror = *reinterpret_cast<int* volatile*>(reinterpret_cast<char*>(status) + 8);
+        if (mirror) {
+            *mirror = code;
+            __threadfence_system();
+        }
+    }
+}
+
 // Bounded wait. Returns false (and records `code`) when the limit is hit or another role aborted.
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
@@ -60,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
     *abort_flag = 1;
-    atomicCAS(status, 0, code);
+    record_status(status, code);
     return false;
 }
 

@@ -32,6 +32,7 @@ SIGNATURES = {
     "qt_last_error": (c_char_p, []),
     "qt_version": (c_char_p, []),
     "qt_device_status": (c_int, [ctypes.POINTER(c_int)]),
+    "qt_device_status_peek": (c_int, [ctypes.POINTER(c_int)]),
     "qt_quantize_rowwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int,
                                     c_float, c_int, c_uint64, c_uint64, c_void_p]),
     "qt_quantize_rowwise_colabsmax": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p,
@@ -69,7 +70,7 @@ SIGNATURES = {
     "qt_adamw_bf16_sr_multi": (c_int, [c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                        ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), c_int, c_int, c_float, ctypes.c_double,
                                        ctypes.c_double, c_float, c_float, c_float, c_float, c_int, c_uint64, c_uint64, c_void_p]),
-    "qt_selftest_wait_timeout": (c_int, [ctypes.POINTER(c_int)]),
+    "qt_selftest_wait_timeout": (c_int, [ctypes.POINTER(c_int), c_int]),
     "qt_selftest_division": (c_int, [c_int, c_float, ctypes.POINTER(ctypes.c_ulonglong)]),
 }
 
@@ -157,3 +158,18 @@ def device_status() -> int:
     out = c_int(0)
     check(load().qt_device_status(ctypes.byref(out)))
     return out.value
+
+
+_peek = c_int(0)
+
+
+def raise_if_device_failed() -> None:
+    """Raise RuntimeError when an earlier GEMM on the current device gave up on a bounded wait (its output
+    is garbage). Reads a pinned host word the kernels write, so it costs no synchronisation; called after
+    every GEMM launch, which means the error surfaces at the first launch after the failing kernel ran."""
+    load().qt_device_status_peek(ctypes.byref(_peek))
+    if _peek.value != 0:
+        code = device_status()   # synchronises and clears
+        raise RuntimeError(
+            f"qt_b200: a GEMM kernel gave up on a bounded wait (status {code or _peek.value:#x}: role << 8 | barrier); "
+            "results produced since the previous check are not valid")

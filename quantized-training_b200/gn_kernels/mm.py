@@ -81,6 +81,7 @@ def _int8_mm_cuda(A: Tensor, B: Tensor):
         ws, ws_bytes = _workspace(M, N, K, dev)
         nv.check(nv.load().qt_int8_mm_ws(A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1),
                                          C.data_ptr(), C.stride(0), M, N, K, ws, ws_bytes, nv.stream_ptr(dev)))
+        nv.raise_if_device_failed()
     return C
 
 
@@ -146,6 +147,7 @@ def _scaled_mm_cuda(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor):
             A.data_ptr(), nv.code(A.dtype), A.stride(0), A.stride(1), B.data_ptr(), nv.code(B.dtype), B.stride(0),
             B.stride(1), row_scale.data_ptr(), col_scale.data_ptr(), int(col_scale.numel() == 1 and N != 1),
             nv.code(row_scale.dtype), C.data_ptr(), C.stride(0), M, N, K, ws, ws_bytes, nv.stream_ptr(dev)))
+        nv.raise_if_device_failed()
     return C
 
 
@@ -168,4 +170,5 @@ def _tile_scaled_mm_cuda(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor)
             B.stride(1), scale_A.data_ptr(), scale_A.stride(0), scale_A.stride(1), scale_B.data_ptr(), scale_B.stride(0),
             scale_B.stride(1), qm, qn, qk, nv.code(scale_A.dtype), C.data_ptr(), C.stride(0), M, N, K,
             nv.stream_ptr(dev)))
+        nv.raise_if_device_failed()
     return C

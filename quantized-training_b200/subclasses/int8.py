@@ -25,12 +25,23 @@ class _QuantCache:
     An entry is valid only for the very same tensor object state: same storage address, shape, strides
     and version counter. The entry keeps a reference to its source tensor, so the storage cannot be
     freed and handed to another tensor while the entry lives; an in-place write bumps the version.
-    Stochastic rounding is never cached (every use must draw fresh noise)."""
+    Stochastic rounding is never cached (every use must draw fresh noise). Tensors made under
+    torch.inference_mode have no version counter and are never cached.
+
+    What the cache pins is bounded three ways: at most SLOTS entries, at most MAX_BYTES of source plus
+    quantized bytes (oldest entries go first), and everything is dropped when a backward pass ends (the
+    Linear's backward queues `clear` on the autograd engine)."""
 
     SLOTS = 4
+    MAX_BYTES = 1 << 30
 
     def __init__(self):
-        self.entries: list[tuple[tuple, Tensor, tuple]] = []
+        self.entries: list[tuple[tuple, Tensor, tuple, int]] = []
+        self._clear_queued = False
+
+    @staticmethod
+    def cacheable(t: Tensor) -> bool:
+        return not t.is_inference()
 
     @staticmethod
     def key(t: Tensor, eps: float):
@@ -38,18 +49,28 @@ class _QuantCache:
 
     def get(self, t: Tensor, eps: float):
         k = self.key(t, eps)
-        for kk, _src, out in self.entries:
+        for kk, _src, out, _n in self.entries:
             if kk == k:
                 return out
         return None
 
     def put(self, t: Tensor, eps: float, out: tuple):
-        self.entries.append((self.key(t, eps), t, out))
-        if len(self.entries) > self.SLOTS:
+        nbytes = t.numel() * t.element_size() + sum(o.numel() * o.element_size() for o in out)
+        if nbytes > self.MAX_BYTES:
+            return
+        self.entries.append((self.key(t, eps), t, out, nbytes))
+        while len(self.entries) > self.SLOTS or sum(e[3] for e in self.entries) > self.MAX_BYTES:
             self.entries.pop(0)
 
     def clear(self):
         self.entries.clear()
+        self._clear_queued = False
+
+    def clear_after_backward(self):
+        """Called from inside a backward function: drop every entry once the running backward pass is over."""
+        if not self._clear_queued:
+            self._clear_queued = True
+            torch.autograd.Variable._execution_engine.queue_callback(self.clear)
 
 
 _quant_cache = _QuantCache()
@@ -62,7 +83,7 @@ def _rows_quantize(t2d: Tensor, stochastic_rounding: bool, eps: float, key=None,
     A transposed view (unit stride along dim 0) is served by the transposing column-wise kernel
     on its base, so `quantize_int8(B.T, dim=1)` never materialises `B.T` in bf16. `cache=True` lets
     repeated round-to-nearest requests for the same activation reuse the first result."""
-    use_cache = cache and not stochastic_rounding and not torch.compiler.is_compiling()
+    use_cache = cache and not stochastic_rounding and not torch.compiler.is_compiling() and _QuantCache.cacheable(t2d)
     if use_cache:
         hit = _quant_cache.get(t2d, eps)
         if hit is not None:

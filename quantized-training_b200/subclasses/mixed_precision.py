@@ -22,7 +22,7 @@ from torch import Tensor, nn
 import gn_kernels
 from gn_kernels import scaled_mm
 
-from .int8 import _rows_quantize
+from .int8 import _quant_cache, _rows_quantize
 
 aten = torch.ops.aten
 
@@ -172,6 +172,7 @@ class _Int8MixedPrecisionLinear(torch.autograd.Function):
         input, weight = ctx.saved_tensors
         cfg = ctx.config
         grad_input = grad_weight = grad_bias = None
+        _quant_cache.clear_after_backward()   # cached activations must not outlive the step
 
         batch_dims = grad_output.shape[:-1]
         gy = grad_output.reshape(-1, weight.shape[0])

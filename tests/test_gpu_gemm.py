@@ -247,9 +247,35 @@ def test_a_wait_that_nothing_satisfies_gives_up_and_reports():
     from gn_kernels import _native as nv
 
     seen = ctypes.c_int(0)
-    nv.check(nv.load().qt_selftest_wait_timeout(ctypes.byref(seen)))
+    nv.check(nv.load().qt_selftest_wait_timeout(ctypes.byref(seen), 0))
     assert seen.value == 0x7E57
     assert nv.device_status() == 0
     a = torch.randint(-128, 127, (256, 256), dtype=torch.int8, device="cuda")
     out = gn_kernels.int8_mm(a, a.T)
     assert torch.equal(out.cpu(), torch._int_mm(a.cpu(), a.cpu().T.contiguous()))
+
+
+def test_a_recorded_wait_failure_raises_from_the_next_gemm_call():
+    """A kernel that gave up on a wait copies its code into a pinned host word; the operators read that
+    word after every GEMM launch (no synchronisation) and raise RuntimeError. Here the self-test leaves
+    the code set, so the next scaled_mm call must raise, and the call after that must work again."""
+    import ctypes
+
+    from gn_kernels import _native as nv
+
+    a = torch.randint(-128, 127, (256, 256), dtype=torch.int8, device="cuda")
+    sa = torch.ones(256, 1, dtype=torch.bfloat16, device="cuda")
+    sb = torch.ones(1, 256, dtype=torch.bfloat16, device="cuda")
+    gn_kernels.scaled_mm(a, a.T, sa, sb)   # sets up the status block
+    seen = ctypes.c_int(0)
+    nv.check(nv.load().qt_selftest_wait_timeout(ctypes.byref(seen), 1))
+    assert seen.value == 0x7E57
+    peek = ctypes.c_int(0)
+    nv.check(nv.load().qt_device_status_peek(ctypes.byref(peek)))
+    assert peek.value == 0x7E57
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        gn_kernels.scaled_mm(a, a.T, sa, sb)
+    assert nv.device_status() == 0
+    out = gn_kernels.scaled_mm(a, a.T, sa, sb)
+    ref = torch._int_mm(a.cpu(), a.cpu().T.contiguous()).float().bfloat16()
+    assert torch.equal(out.cpu(), ref)

@@ -91,6 +91,41 @@ __host__ __device__ inline Philox4 philox4x32_10(uint64_t ctr, uint64_t offset, 
     return Philox4{c0, c1, c2, c3};
 }
 
+// The ten round keys of a seed, formed once on the host and handed to kernels inside their parameter
+// block: a round then reads its keys as constant operands instead of carrying and advancing two registers.
+struct PhiloxKeys {
+    uint32_t k[20];
+};
+
+inline PhiloxKeys philox_keys(uint64_t seed) {
+    PhiloxKeys out;
+    uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    for (int r = 0; r < 10; ++r) {
+        out.k[2 * r] = k0;
+        out.k[2 * r + 1] = k1;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return out;
+}
+
+// Same generator as philox4x32_10(ctr, offset, seed) with the round keys of `seed` precomputed.
+__device__ __forceinline__ Philox4 philox4x32_10(uint64_t ctr, uint64_t offset, const PhiloxKeys& keys) {
+    uint32_t c0 = (uint32_t)ctr, c1 = (uint32_t)(ctr >> 32);
+    uint32_t c2 = (uint32_t)offset, c3 = (uint32_t)(offset >> 32);
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+        const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+        const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ keys.k[2 * r];
+        const uint32_t n1 = (uint32_t)p1;
+        const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ keys.k[2 * r + 1];
+        const uint32_t n3 = (uint32_t)p0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    }
+    return Philox4{c0, c1, c2, c3};
+}
+
 // ---- device numerics ------------------------------------------------------------------------
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }

@@ -251,6 +251,7 @@ struct RowwiseParams {
     float eps;
     int stochastic;
     uint64_t seed, offset;
+    PhiloxKeys keys;   // round keys of `seed`
     int vec_load, vec_store;
     // in-place weight update (UPD != 0): the row is not read from x but formed from the int8 weight
     // itself, its scale and one or two bf16 operand tensors
@@ -310,8 +311,8 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t w) {
     return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
 }
 
-// Quantize the 8 bf16 values of `raw` (element index idx of the output, a multiple of 8) with divider
-// `div`, two elements per packed fp32x2 instruction.
+// Quantize the 8 bf16 values of `raw` (elements [8 ctr, 8 ctr + 8) of the output: `ctr` is the Philox
+// counter of the stochastic form) with divider `div`, two elements per packed fp32x2 instruction.
 // int8, round-half-even: add 1.5 * 2^23, the low mantissa byte is the result. No clamp: |x| <= absmax and
 // d >= absmax/127 * (1 - 2^-24) bound the quotient by 127 + 2^-17, which rounds to 127.
 // int8, stochastic: floor(fl(v + u)) with u = 16 Philox bits * 2^-16. The uniform is built without an
@@ -321,8 +322,8 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t w) {
 // fp8: cvt.rn.satfinite of the quotient; the reciprocal sequence returns +0 for x = -0, so the sign of
 // the input is OR-ed back into the byte (a quotient never has the opposite sign of x).
 template <bool SR>
-__device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider2& div, int q_dtype, int64_t idx,
-                                               uint64_t seed, uint64_t offset) {
+__device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider2& div, int q_dtype, uint64_t ctr,
+                                               const PhiloxKeys& keys, uint64_t offset) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
     float2 v[4];
 #pragma unroll
@@ -331,7 +332,7 @@ __device__ __forceinline__ uint2 quantize_vec8(const uint4& raw, const Divider2&
     if (q_dtype == QT_I8) {
         const float2 magic2 = make_float2(kRoundMagic, kRoundMagic);
         if constexpr (SR) {
-            const Philox4 a = philox4x32_10((uint64_t)idx >> 3, offset, seed);
+            const Philox4 a = philox4x32_10(ctr, offset, keys);
             const uint32_t rw[4] = {a.x, a.y, a.z, a.w};
             const float2 m192 = make_float2(-192.0f, -192.0f);
 #pragma unroll
@@ -391,6 +392,55 @@ __device__ __forceinline__ uint4 updated_vec8(uint2 qb, float s, const uint4& a,
         out[k] = as_u32(__floats2bfloat162_rn(__fmaf_rn(value, t0, w0), __fmaf_rn(value, t1, w1)));
     }
     return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// End of the column-maxima variants: `colmax` holds each thread's running |x| maxima (packed bf16 pairs,
+// sign bits undefined) of its VPT vectors. 1. The CTA's sub-rows, which cover the same columns, fold in
+// shared memory. 2. The CTAs of the thread-block cluster fold through distributed shared memory; each CTA
+// owns a slice of the columns and issues one atomic max per column for the whole cluster.
+template <int TPR, int VPT>
+__device__ __forceinline__ void fold_column_maxima(uint32_t (&colmax)[VPT][4], uint32_t* s_col, int sub, int t, int64_t cols,
+                                                   float* col_absmax) {
+    constexpr int RPC = kThreads / TPR;
+    constexpr int PAIRS = TPR * VPT * 4;
+    if constexpr (RPC > 1) {
+#pragma unroll 1
+        for (int turn = 0; turn < RPC; ++turn) {
+            if (sub == turn) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int pair = (i * TPR + t) * 4 + k;
+                        s_col[pair] = max2(s_col[pair], colmax[i][k] & 0x7FFF7FFFu);
+                    }
+            }
+            __syncthreads();
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) s_col[(i * TPR + t) * 4 + k] = colmax[i][k] & 0x7FFF7FFFu;
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const unsigned n_cta = cluster.num_blocks(), rank = cluster.block_rank();
+    for (int pair = rank * kThreads + threadIdx.x; pair < PAIRS; pair += n_cta * kThreads) {
+        uint32_t m = 0u;
+        if (n_cta == 2) {
+            // issue both reads together: the remote one is a trip across the cluster
+            const uint32_t v0 = cluster.map_shared_rank(s_col, 0)[pair], v1 = cluster.map_shared_rank(s_col, 1)[pair];
+            m = max2(v0, v1);
+        } else {
+            for (unsigned c = 0; c < n_cta; ++c) m = max2(m, cluster.map_shared_rank(s_col, c)[pair]);
+        }
+        const int64_t c0 = (int64_t)pair * 2;
+        // fp32 bit patterns of non-negative values order like unsigned integers
+        if (c0 < cols && (m & 0xFFFFu)) atomicMax(reinterpret_cast<unsigned int*>(col_absmax + c0), m << 16);
+        if (c0 + 1 < cols && (m >> 16)) atomicMax(reinterpret_cast<unsigned int*>(col_absmax + c0 + 1), m & 0xFFFF0000u);
+    }
+    cluster.sync();  // nobody leaves while a peer may still read its shared memory
 }
 
 // Row-wise kernel for bf16 rows that fit in registers. TPR threads cooperate on one row, each
@@ -514,7 +564,7 @@ rowwise_kernel(const RowwiseParams p) {
         for (int i = 0; i < VPT; ++i) {
             const int col = (i * TPR + t) * 8;
             if (valid && col < p.cols) {
-                const uint2 bytes = quantize_vec8<SR>(cur[i], div, p.q_dtype, idx0 + col, p.seed, p.offset);
+                const uint2 bytes = quantize_vec8<SR>(cur[i], div, p.q_dtype, (uint64_t)(idx0 + col) >> 3, p.keys, p.offset);
                 if constexpr (SCATTER) {
                     const int64_t at = (p.dst_row0 + row) * p.cols + col;
                     for (int d = 0; d < p.n_dst; ++d) *reinterpret_cast<uint2*>(p.q_dst[d] + at) = bytes;
@@ -550,50 +600,144 @@ rowwise_kernel(const RowwiseParams p) {
         }
     }
 
+    if constexpr (COLABS) fold_column_maxima<TPR, VPT>(colmax, s_col, sub, t, p.cols, p.col_absmax);
+}
+
+// The common case of the kernel above with everything that costs instructions removed: the row count is
+// a multiple of the rows per CTA and below 2^30, so rows are counted in 32 bits and need no bounds check;
+// which of a thread's vectors lie inside the row is decided once (those outside stay zero and are never
+// loaded or stored); the load and store pointers advance by a fixed step instead of being recomputed.
+// Same arithmetic, same results.
+// TILE selects 1 x 128 tiles instead of whole rows (cols a multiple of 128): eight lanes own one tile, lane
+// l of the group holding elements [8l, 8l + 8) and [64 + 8l, 64 + 8l + 8), so each of the two loads of a
+// group covers 128 contiguous bytes, the tile's absmax is one 8-lane reduction, and the per-tile scalar
+// work (scale, reciprocal, scale store) is shared by 16 elements per thread. Vectors 2j and 2j + 1 of a
+// thread are the two halves of its j-th tile.
+template <int TPR, int VPT, bool COLABS, bool SR, bool TILE = false>
+__global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1)))
+rowwise_full_kernel(const RowwiseParams p) {
+    constexpr int RPC = kThreads / TPR;
+    constexpr int WPR = TPR / 32;
+    constexpr bool PREFETCH = VPT <= 8 && !COLABS;
+    static_assert(!TILE || (VPT % 2 == 0 && !COLABS && !SR), "tile form: vector pairs, no column maxima, round-to-nearest");
+    __shared__ uint32_t s_red[2][kThreads / 32];
+    __shared__ uint32_t s_col[COLABS ? TPR * VPT * 4 : 1];
+
+    const int sub = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int warp = threadIdx.x >> 5;
+    const float qmax = qmax_of(p.q_dtype);
+    const float rqmax = p.q_dtype == QT_I8 ? (1.0f / 127.0f) : (p.q_dtype == QT_E4M3 ? (1.0f / 448.0f) : (1.0f / 57344.0f));
+    const int rows = (int)p.rows;
+    const int step = (int)gridDim.x * RPC;
+    const int first = (int)blockIdx.x * RPC;
+    int n_iter = first < rows ? (rows - first + step - 1) / step : 0;
+    int row = first + sub;
+    const int nvec = (int)(p.cols / 8);
+
+    // position of vector i of this thread inside a row, in 8-element units, and whether it exists
+    int vpos[VPT];
+    bool ok[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        if constexpr (TILE) vpos[i] = ((i >> 1) * (TPR / 8) + (t >> 3)) * 16 + (i & 1) * 8 + (t & 7);
+        else vpos[i] = i * TPR + t;
+        ok[i] = vpos[i] < nvec;
+    }
+    const uint32_t gmask = 0xFFu << (threadIdx.x & 24);   // the 8 lanes of this thread's tile (TILE)
+
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.x) + (int64_t)row * p.stride);
+    const int64_t src_step = (int64_t)step * (p.stride / 8);
+    uint2* dst = reinterpret_cast<uint2*>(p.q + (int64_t)row * p.cols);
+    const int64_t dst_step = (int64_t)step * nvec;
+    uint64_t ctr = SR ? (uint64_t)row * (uint64_t)nvec : 0;   // Philox counter of the row's first vector
+
+    uint32_t colmax[COLABS ? VPT : 1][4];
     if constexpr (COLABS) {
-        constexpr int PAIRS = TPR * VPT * 4;
-        // 1. fold the CTA's sub-rows (they cover the same columns) in shared memory
-        if constexpr (RPC > 1) {
-#pragma unroll 1
-            for (int turn = 0; turn < RPC; ++turn) {
-                if (sub == turn) {
 #pragma unroll
-                    for (int i = 0; i < VPT; ++i)
+        for (int i = 0; i < VPT; ++i)
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const int pair = (i * TPR + t) * 4 + k;
-                            s_col[pair] = max2(s_col[pair], colmax[i][k] & 0x7FFF7FFFu);
-                        }
+            for (int k = 0; k < 4; ++k) colmax[i][k] = 0u;
+        for (int i = threadIdx.x; i < TPR * VPT * 4; i += kThreads) s_col[i] = 0u;
+        __syncthreads();
+    }
+
+    auto load_row = [&](uint4 (&v)[VPT]) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i)
+            if (ok[i]) v[i] = src[vpos[i]];
+        src += src_step;
+    };
+    auto process = [&](uint4 (&cur)[VPT], int parity) {
+        if constexpr (TILE) {
+#pragma unroll
+            for (int j = 0; j < VPT / 2; ++j) {
+                const uint4 &lo = cur[2 * j], &hi = cur[2 * j + 1];
+                const uint32_t m2 = amax2(amax2(amax2(lo.x, lo.y), amax2(lo.z, lo.w)), amax2(amax2(hi.x, hi.y), amax2(hi.z, hi.w)));
+                // all 8 lanes of a tile take part (lanes of tiles beyond the row hold zeros)
+                const float amax = __uint_as_float(__reduce_max_sync(gmask, fold_halves(m2)));
+                const float scale = scale_of(amax, qmax, rqmax);
+                const Divider2 div(fmaxf(scale, p.eps));
+                if (ok[2 * j]) {
+                    if ((t & 7) == 0) store_scale(p.scale, p.scale_dtype, (int64_t)row * (nvec >> 4) + (vpos[2 * j] >> 4), scale);
+                    dst[vpos[2 * j]] = quantize_vec8<false>(lo, div, p.q_dtype, 0, p.keys, 0);
+                    dst[vpos[2 * j + 1]] = quantize_vec8<false>(hi, div, p.q_dtype, 0, p.keys, 0);
                 }
-                __syncthreads();
             }
         } else {
+            uint32_t m2 = 0u;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                m2 = amax2(m2, amax2(amax2(cur[i].x, cur[i].y), amax2(cur[i].z, cur[i].w)));
+                if constexpr (COLABS) {
+                    colmax[i][0] = amax2(colmax[i][0], cur[i].x); colmax[i][1] = amax2(colmax[i][1], cur[i].y);
+                    colmax[i][2] = amax2(colmax[i][2], cur[i].z); colmax[i][3] = amax2(colmax[i][3], cur[i].w);
+                }
+            }
+            uint32_t abits = __reduce_max_sync(0xFFFFFFFFu, fold_halves(m2));
+            if constexpr (WPR > 1) {
+                if ((threadIdx.x & 31) == 0) s_red[parity][warp] = abits;
+                if constexpr (RPC == 1) __syncthreads();
+                else row_barrier<TPR>(sub);
+                abits = s_red[parity][sub * WPR];
+#pragma unroll
+                for (int w = 1; w < WPR; ++w) { const uint32_t o = s_red[parity][sub * WPR + w]; abits = o > abits ? o : abits; }
+            }
+            const float scale = scale_of(__uint_as_float(abits), qmax, rqmax);
+            const Divider2 div(fmaxf(scale, p.eps));
+            if (t == 0) store_scale(p.scale, p.scale_dtype, row, scale);
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
+                if (ok[i]) dst[vpos[i]] = quantize_vec8<SR>(cur[i], div, p.q_dtype, ctr + vpos[i], p.keys, p.offset);
+        }
+        dst += dst_step;
+        row += step;
+        if constexpr (SR) ctr += (uint64_t)dst_step;
+    };
+
+    if constexpr (PREFETCH) {
+        uint4 a[VPT], b[VPT];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) s_col[(i * TPR + t) * 4 + k] = colmax[i][k] & 0x7FFF7FFFu;
+        for (int i = 0; i < VPT; ++i) a[i] = b[i] = make_uint4(0, 0, 0, 0);
+        if (n_iter > 0) load_row(a);
+        while (n_iter > 0) {
+            if (n_iter > 1) load_row(b);
+            process(a, 0);
+            if (--n_iter == 0) break;
+            if (n_iter > 1) load_row(a);
+            process(b, 1);
+            --n_iter;
         }
-        // 2. fold the CTAs of the thread-block cluster through distributed shared memory; each CTA
-        //    owns a slice of the columns and issues one atomic max per column for the whole cluster
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        const unsigned n_cta = cluster.num_blocks(), rank = cluster.block_rank();
-        for (int pair = rank * kThreads + threadIdx.x; pair < PAIRS; pair += n_cta * kThreads) {
-            uint32_t m = 0u;
-            if (n_cta == 2) {
-                // issue both reads together: the remote one is a trip across the cluster
-                const uint32_t v0 = cluster.map_shared_rank(s_col, 0)[pair], v1 = cluster.map_shared_rank(s_col, 1)[pair];
-                m = max2(v0, v1);
-            } else {
-                for (unsigned c = 0; c < n_cta; ++c) m = max2(m, cluster.map_shared_rank(s_col, c)[pair]);
-            }
-            const int64_t c0 = (int64_t)pair * 2;
-            // fp32 bit patterns of non-negative values order like unsigned integers
-            if (c0 < p.cols && (m & 0xFFFFu)) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c0), m << 16);
-            if (c0 + 1 < p.cols && (m >> 16)) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c0 + 1), m & 0xFFFF0000u);
+    } else {
+        uint4 a[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) a[i] = make_uint4(0, 0, 0, 0);
+        for (int it = 0; it < n_iter; ++it) {
+            load_row(a);
+            process(a, it & 1);
         }
-        cluster.sync();  // nobody leaves while a peer may still read its shared memory
     }
+    if constexpr (COLABS) fold_column_maxima<TPR, VPT>(colmax, s_col, sub, t, p.cols, p.col_absmax);
 }
 
 // Any width, any alignment: one CTA per row, two passes (the second normally hits L2).
@@ -645,6 +789,9 @@ int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
     const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
     int64_t grid = want < cap ? want : cap;
     auto kfn = rowwise_kernel<TPR, VPT, COLABS, SR, UPD, SCATTER>;
+    if constexpr (UPD == 0 && !SCATTER) {
+        if (p.rows % RPC == 0 && p.rows < ((int64_t)1 << 30)) kfn = rowwise_full_kernel<TPR, VPT, COLABS, SR>;
+    }
     if constexpr (COLABS) {
         constexpr int csize = kClusterSize;
         grid = (grid + csize - 1) / csize * csize;
@@ -705,6 +852,19 @@ int launch_rowwise(const RowwiseParams& p, int x_dtype, bool colabs, cudaStream_
     return colabs ? launch_rowwise_generic<float, true>(p, stream) : launch_rowwise_generic<float, false>(p, stream);
 }
 
+// 1 x 128 tiles through the lean row kernel; -1 when the row count is not a multiple of the CTA's rows.
+template <int TPR, int VPT>
+int launch_tile_1x128(const RowwiseParams& p, cudaStream_t stream) {
+    constexpr int RPC = kThreads / TPR;
+    constexpr int CTAS_PER_SM = VPT <= 4 ? 4 : 2;
+    if (p.rows % RPC != 0) return -1;
+    const int64_t want = p.rows / RPC;
+    const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
+    rowwise_full_kernel<TPR, VPT, false, false, true><<<(unsigned)(want < cap ? want : cap), kThreads, 0, stream>>>(p);
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
 int check_quant_args(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t stride, const void* q,
                      int q_dtype, const void* scale, int scale_dtype) {
     QT_REQUIRE(x_dtype == QT_BF16 || x_dtype == QT_F32, "quantize: x_dtype must be QT_BF16 or QT_F32 (got %d)", x_dtype);
@@ -732,7 +892,7 @@ int quantize_rowwise_impl(const void* x, int x_dtype, int64_t rows, int64_t cols
     p.x = x; p.rows = rows; p.cols = cols; p.stride = stride;
     p.q = reinterpret_cast<uint8_t*>(q); p.scale = scale; p.col_absmax = col_absmax;
     p.q_dtype = q_dtype; p.scale_dtype = scale_dtype; p.eps = eps; p.stochastic = stochastic;
-    p.seed = seed; p.offset = offset;
+    p.seed = seed; p.offset = offset; p.keys = philox_keys(seed);
     const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
     p.vec_load = aligned_to(x, 16) && ((stride * esz) % 16 == 0);
     p.vec_store = aligned_to(q, 8) && (cols % 8 == 0);
@@ -1106,7 +1266,7 @@ __global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p
                 if (l16 == 0) store_scale(p.scale, p.scale_dtype, row * p.scale_cols + (col >> 7), sc);
                 uint2 bytes;
                 if constexpr (sizeof(XT) == 2 && !EXACT_DIV) {
-                    bytes = quantize_vec8<false>(v[j].raw, Divider2(div.d, div.r, div.d, div.r), p.q_dtype, 0, 0, 0);
+                    bytes = quantize_vec8<false>(v[j].raw, Divider2(div.d, div.r, div.d, div.r), p.q_dtype, 0, PhiloxKeys{}, 0);
                 } else {
                     divide8(f, div, p.q_dtype != QT_I8);
                     bytes = pack8(f, p.q_dtype, false, zero_u);
@@ -1159,7 +1319,7 @@ __global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams
         if (row < p.rows && col < p.cols) {
             uint2 bytes;
             if constexpr (sizeof(XT) == 2 && !EXACT_DIV) {
-                bytes = quantize_vec8<false>(v[i].raw, Divider2(div.d, div.r, div.d, div.r), p.q_dtype, 0, 0, 0);
+                bytes = quantize_vec8<false>(v[i].raw, Divider2(div.d, div.r, div.d, div.r), p.q_dtype, 0, PhiloxKeys{}, 0);
             } else {
                 float f[8];
                 v[i].unpack(f);
@@ -1168,80 +1328,6 @@ __global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams
             }
             store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
         }
-    }
-}
-
-// 1 x 128 tiles, the common case with everything that costs instructions removed: bf16 input, whole
-// tiles (cols a multiple of 128), 16-byte aligned rows, eps >= 1e-30. Eight lanes own one tile: lane l of
-// the group holds elements [8l, 8l + 8) and [64 + 8l, 64 + 8l + 8), so each of the two loads of a group
-// covers 128 contiguous bytes, the tile's absmax is one 8-lane reduction and the per-tile scalar work
-// (scale, reciprocal, scale store) is shared by 16 elements per thread. `tpr` threads (a power of two,
-// 8..256) span a chunk of tpr * 16 columns of one row, the CTA's other threads take further rows; an item
-// is two such row groups, and the next item's loads are issued before the current one is quantized.
-__global__ void __launch_bounds__(kThreads, 3) tile_1x128_fast_kernel(const TileParams p, int tpr_log2) {
-    constexpr int ROWS = 2;
-    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x);
-    const float qmax = qmax_of(p.q_dtype);
-    const float rqmax = p.q_dtype == QT_I8 ? (1.0f / 127.0f) : (p.q_dtype == QT_E4M3 ? (1.0f / 448.0f) : (1.0f / 57344.0f));
-    const int tpr = 1 << tpr_log2;
-    const int rpp = kThreads >> tpr_log2;            // rows per pass
-    const int sub = threadIdx.x >> tpr_log2, t = threadIdx.x & (tpr - 1);
-    const int l8 = threadIdx.x & 7;
-    const uint32_t gmask = 0xFFu << (threadIdx.x & 24);   // the 8 lanes of this thread's tile
-    const int chunk_cols = tpr * 16;
-    const uint32_t chunks = (uint32_t)((p.cols + chunk_cols - 1) / chunk_cols);
-    const uint32_t row_blocks = (uint32_t)((p.rows + ROWS * rpp - 1) / (ROWS * rpp));
-    const uint32_t items = row_blocks * chunks;
-    const int col_in_chunk = (t >> 3) * 128 + l8 * 8;
-
-    auto load_item = [&](uint4 (&v)[ROWS][2], uint32_t item) {
-        const uint32_t rblk = item / chunks, chunk = item - rblk * chunks;
-        const int64_t col = (int64_t)chunk * chunk_cols + col_in_chunk;
-#pragma unroll
-        for (int j = 0; j < ROWS; ++j) {
-            const int64_t row = ((int64_t)rblk * ROWS + j) * rpp + sub;
-            if (row < p.rows && col < p.cols) {
-                const uint4* src = reinterpret_cast<const uint4*>(x + row * p.stride + col);
-                v[j][0] = src[0];
-                v[j][1] = src[8];
-            } else {
-                v[j][0] = make_uint4(0, 0, 0, 0);
-                v[j][1] = make_uint4(0, 0, 0, 0);
-            }
-        }
-    };
-    auto process = [&](const uint4 (&v)[ROWS][2], uint32_t item) {
-        const uint32_t rblk = item / chunks, chunk = item - rblk * chunks;
-        const int64_t col = (int64_t)chunk * chunk_cols + col_in_chunk;
-#pragma unroll
-        for (int j = 0; j < ROWS; ++j) {
-            const int64_t row = ((int64_t)rblk * ROWS + j) * rpp + sub;
-            const uint32_t m2 = amax2(amax2(amax2(v[j][0].x, v[j][0].y), amax2(v[j][0].z, v[j][0].w)),
-                                      amax2(amax2(v[j][1].x, v[j][1].y), amax2(v[j][1].z, v[j][1].w)));
-            // all 8 lanes of a tile take part (out-of-range lanes hold zeros)
-            const float amax = __uint_as_float(__reduce_max_sync(gmask, fold_halves(m2)));
-            const float sc = scale_of(amax, qmax, rqmax);
-            const Divider2 div(fmaxf(sc, p.eps));
-            if (row < p.rows && col < p.cols) {
-                if (l8 == 0) store_scale(p.scale, p.scale_dtype, row * p.scale_cols + (col >> 7), sc);
-                uint8_t* dst = p.q + row * p.cols + col;
-                *reinterpret_cast<uint2*>(dst) = quantize_vec8<false>(v[j][0], div, p.q_dtype, 0, 0, 0);
-                *reinterpret_cast<uint2*>(dst + 64) = quantize_vec8<false>(v[j][1], div, p.q_dtype, 0, 0, 0);
-            }
-        }
-    };
-
-    uint4 a[ROWS][2], b[ROWS][2];
-    uint32_t item = blockIdx.x;
-    if (item < items) load_item(a, item);
-    while (item < items) {
-        if (item + gridDim.x < items) load_item(b, item + gridDim.x);
-        process(a, item);
-        item += gridDim.x;
-        if (item >= items) break;
-        if (item + gridDim.x < items) load_item(a, item + gridDim.x);
-        process(b, item);
-        item += gridDim.x;
     }
 }
 
@@ -1280,7 +1366,7 @@ __global__ void __launch_bounds__(kThreads, 2) tile_128x128_fast_kernel(const Ti
         uint8_t* dst = p.q + ((int64_t)tr * 128 + r16) * p.cols + (int64_t)tc * 128 + c16 * 8;
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<uint2*>(dst + (int64_t)i * 16 * p.cols) = quantize_vec8<false>(v[i], div, p.q_dtype, 0, 0, 0);
+            *reinterpret_cast<uint2*>(dst + (int64_t)i * 16 * p.cols) = quantize_vec8<false>(v[i], div, p.q_dtype, 0, PhiloxKeys{}, 0);
     };
 
     uint4 a[8], b[8];
@@ -1460,17 +1546,18 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
     p.vec_load = aligned_to(x, 16) && ((x_row_stride * esz) % 16 == 0);
     p.vec_store = aligned_to(q, 8) && (cols % 8 == 0);
     const bool fast = x_dtype == QT_BF16 && eps >= 1e-30f && p.vec_load && p.vec_store && cols % 128 == 0;
-    if (tile_r == 1 && fast) {
-        int tpr_log2 = 3;  // at least one 8-lane tile group per row
-        while (tpr_log2 < 8 && ((int64_t)16 << tpr_log2) < cols) ++tpr_log2;
-        const int tpr = 1 << tpr_log2, rpp = kThreads / tpr;
-        const int64_t items = ((rows + 2 * rpp - 1) / (2 * rpp)) * ((cols + tpr * 16 - 1) / (tpr * 16));
-        if (items < (int64_t)1 << 31) {
-            const int64_t cap = (int64_t)num_sms() * 3;
-            tile_1x128_fast_kernel<<<(unsigned)(items < cap ? items : cap), kThreads, 0, stream>>>(p, tpr_log2);
-            QT_CUDA_CHECK(cudaGetLastError());
-            return QT_OK;
-        }
+    if (tile_r == 1 && fast && cols <= 16384 && rows < ((int64_t)1 << 30)) {
+        RowwiseParams rp = {};
+        rp.x = x; rp.rows = rows; rp.cols = cols; rp.stride = x_row_stride; rp.q = p.q; rp.scale = scale;
+        rp.q_dtype = q_dtype; rp.scale_dtype = scale_dtype; rp.eps = eps;
+        int rc = -1;
+        if (cols <= 512) rc = launch_tile_1x128<32, 2>(rp, stream);
+        else if (cols <= 1024) rc = launch_tile_1x128<32, 4>(rp, stream);
+        else if (cols <= 2048) rc = launch_tile_1x128<64, 4>(rp, stream);
+        else if (cols <= 4096) rc = launch_tile_1x128<128, 4>(rp, stream);
+        else if (cols <= 8192) rc = launch_tile_1x128<256, 4>(rp, stream);
+        else rc = launch_tile_1x128<256, 8>(rp, stream);
+        if (rc >= 0) return rc;   // negative: the row count does not fit this kernel, fall through
     }
     if (tile_r == 128 && fast && rows % 128 == 0 && (rows / 128) * p.scale_cols < ((int64_t)1 << 31)) {
         const int64_t tiles = (rows / 128) * p.scale_cols;
@@ -1542,7 +1629,7 @@ extern "C" int qt_int8_weight_update(void* q, void* scale, int64_t rows, int64_t
     p.rows = rows; p.cols = cols; p.stride = cols;
     p.q = reinterpret_cast<uint8_t*>(q); p.scale = scale;
     p.q_dtype = QT_I8; p.scale_dtype = QT_BF16; p.eps = eps; p.stochastic = 1;
-    p.seed = seed; p.offset = offset; p.vec_load = 1; p.vec_store = 1;
+    p.seed = seed; p.offset = offset; p.keys = philox_keys(seed); p.vec_load = 1; p.vec_store = 1;
     p.t1 = reinterpret_cast<const __nv_bfloat16*>(t1); p.t2 = reinterpret_cast<const __nv_bfloat16*>(t2); p.value = value;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     return mode == 0 ? launch_rowwise_bf16<false, true, 1>(p, stream) : launch_rowwise_bf16<false, true, 2>(p, stream);

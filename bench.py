@@ -51,7 +51,7 @@ def parse_args():
                     help="a non-square problem for the gemm workload (profiling the layer shapes; the headline is --size 8192)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-quantize-lines", action="store_true", help="leave the quantize kernels' roofline entries out of the N=1 line")
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "quantize", "train-470m", "train-1b"],
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "quantize", "sweep", "train-470m", "train-1b"],
                     help="gemm: the headline quantize + scaled GEMM step; train-*: one INT8 mixed-precision Llama step (tok/s)")
     ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp"], help="train-* workloads with --gpus > 1: DDP, or FSDP2 with the INT8 weight all-gather")
     ap.add_argument("--quantize", default="mixed_precision", choices=["mixed_precision", "none", "int8_quantized_training", "bitnet"],
@@ -61,6 +61,8 @@ def parse_args():
                          "buffer over NVLink (symmetric memory); 'nccl' = quantize, then NCCL all-gather")
     ap.add_argument("--sm-margin", type=int, default=None,
                     help="SMs the GEMM leaves free when --gpus > 1 (default: 8 beside NCCL's all-gather kernel, 0 with the fused gather)")
+    ap.add_argument("--eager-elementwise", action="store_true",
+                    help="train-* workloads: leave RMSNorm, the gated activation and rotary embedding to the model's eager code")
     ap.add_argument("--layers", type=int, default=None, help="train-* workloads: number of decoder layers (default: the model's own)")
     ap.add_argument("--profile", default=None, metavar="FILE",
                     help="train-* workloads: after the timed steps, run two more under torch.profiler and write the kernel table "
@@ -324,6 +326,10 @@ def run_train(args, rank, local_rank, world):
     with torch.device(dev):
         model = LlamaForCausalLM(cfg).bfloat16()
     quantize_model(model.model, None if args.quantize == "none" else args.quantize)
+    if not args.eager_elementwise:
+        from train_utils import fuse_decoder_elementwise
+
+        fuse_decoder_elementwise(model)   # RMSNorm / silu * up / rotary embedding as single kernels; emits int8 activations where INT8 linears follow
     if world > 1 and args.parallel == "fsdp":
         from torch.distributed.fsdp import fully_shard
 
@@ -385,7 +391,8 @@ def run_train(args, rank, local_rank, world):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": f"{args.workload}: Llama-style decoder, {n_params / 1e6:.0f}M params, quantize={args.quantize} "
-                                   f"(LM head bf16), AdamWBF16SR, batch {bs} x {seq} random tokens per GPU",
+                                   f"(LM head bf16), AdamWBF16SR, batch {bs} x {seq} random tokens per GPU, "
+                                   f"{'eager' if args.eager_elementwise else 'fused'} element-wise kernels",
                        "parallelism": (f"fsdp{world}" if (world > 1 and args.parallel == "fsdp") else f"dp{world}")},
             "loss": float(loss.detach()), "max_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
         }), flush=True)
@@ -532,6 +539,74 @@ def quantize_lines(M: int, K: int, launches: int, dev, graph: bool = True, only:
     return out
 
 
+def run_sweep(args):
+    """The reference's GEMM benchmark grid (benchmark_mm.py:33-34,70-145): M = N = K in {1024, 2048, 4096, 8192}
+    x layouts {A@B.T, A@B, A.T@B} x {int8_mm, row-scaled INT8, row-scaled FP8 e4m3, tile-scaled INT8, tile-scaled
+    FP8}; 2*M*N*K / time (benchmark_mm.py:107). One JSON line per cell with the library GEMM of the same box
+    beside it where one exists (torch._int_mm; torch._scaled_mm with row-wise scales, A@B.T only). Operands are
+    random int8 / e4m3 values with random bf16 scales (timing only; parity is the tests' job). Launches rotate
+    through operand sets several times larger than L2 and are timed as CUDA-graph replays (_time_graph)."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    import gn_kernels
+
+    dev = torch.device("cuda", 0)
+    _, bf16_peak, peak_kind = measured_peaks()
+    peak = 2.0 * bf16_peak
+    sizes = [args.size] if args.size != 8192 or args.only else [1024, 2048, 4096, 8192]
+    if args.only and args.only.isdigit():
+        sizes = [int(args.only)]
+    launches = max(args.steps, 10)
+
+    def layout(t, col_major):
+        return t.T.contiguous().T if col_major else t.contiguous()
+
+    for S in sizes:
+        M = N = K = S
+        per_launch = 2 * S * S + 2 * S * S          # int8 operands + bf16 result
+        n_sets = min(48, max(3, -(-3 * 126 * (1 << 20) // per_launch) + 1))
+        for lname, a_col, b_col in (("A@B.T", False, True), ("A@B", False, False), ("A.T@B", True, False)):
+            A8 = [layout(torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev), a_col) for _ in range(n_sets)]
+            B8 = [layout(torch.randint(-128, 128, (K, N), dtype=torch.int8, device=dev), b_col) for _ in range(n_sets)]
+            Af = [t.to(torch.bfloat16).mul_(0.01).to(torch.float8_e4m3fn) for t in A8]
+            Bf = [t.to(torch.bfloat16).mul_(0.01).to(torch.float8_e4m3fn) for t in B8]
+            Af = [layout(t, a_col) for t in Af]
+            Bf = [layout(t, b_col) for t in Bf]
+            sa = (torch.rand(M, 1, device=dev) * 0.01 + 0.001).bfloat16()
+            sb = (torch.rand(1, N, device=dev) * 0.01 + 0.001).bfloat16()
+            ta = (torch.rand(M, K // 128, device=dev) * 0.01 + 0.001).bfloat16()
+            tb = (torch.rand(K // 128, N // 128, device=dev) * 0.01 + 0.001).bfloat16()
+            cases = [
+                ("int8_mm", lambda i: gn_kernels.int8_mm(A8[i], B8[i]), lambda i: torch._int_mm(A8[i], B8[i]), "torch._int_mm"),
+                ("scaled_mm int8", lambda i: gn_kernels.scaled_mm(A8[i], B8[i], sa, sb),
+                 lambda i: (torch._int_mm(A8[i], B8[i]).float().mul_(sa.float()).mul_(sb.float())).bfloat16(), "torch._int_mm + eager scaling"),
+                ("scaled_mm e4m3", lambda i: gn_kernels.scaled_mm(Af[i], Bf[i], sa, sb),
+                 (lambda i: torch._scaled_mm(Af[i], Bf[i], scale_a=sa.float(), scale_b=sb.float(), out_dtype=torch.bfloat16))
+                 if (not a_col and b_col) else None, "torch._scaled_mm row-wise"),
+                ("tile_scaled_mm int8 (1x128, 128x128)", lambda i: gn_kernels.scaled_mm(A8[i], B8[i], ta, tb), None, None),
+                ("tile_scaled_mm e4m3 (1x128, 128x128)", lambda i: gn_kernels.scaled_mm(Af[i], Bf[i], ta, tb), None, None),
+            ]
+            for name, fn, lib_fn, lib_name in cases:
+                if args.only and not args.only.isdigit() and args.only not in name:
+                    continue
+                ms = _time_graph(fn, n_sets, launches)
+                tops = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+                line = {"metric": "gemm_tops", "kernel": name, "layout": lname, "size": S, "value": round(tops, 1), "unit": "TOPS",
+                        "us_per_launch": round(ms * 1e3, 2), "frac_of_2x_measured_bf16": round(tops / peak, 3),
+                        "frac_of_nominal_4500": round(tops / NOMINAL_INT8_DENSE_TOPS, 3), "peak": peak, "peak_is": f"2 x {peak_kind} dense bf16 burst",
+                        "n_gpus": 1, "steps": launches, "higher_is_better": True, "data": "synthetic",
+                        "config": {"workload": f"{name} {lname} M=N=K={S}", "l2": f"{n_sets} operand sets in rotation, CUDA-graph replays"}}
+                if lib_fn is not None:
+                    try:
+                        lms = _time_graph(lib_fn, n_sets, launches)
+                        line["library"] = {"what": lib_name, "tops": round(2.0 * M * N * K / (lms * 1e-3) / 1e12, 1), "us_per_launch": round(lms * 1e3, 2)}
+                    except Exception as exc:   # a layout or shape the library refuses
+                        line["library"] = {"what": lib_name, "unavailable": f"{type(exc).__name__}: {str(exc)[:120]}"}
+                print(json.dumps(line), flush=True)
+            del A8, B8, Af, Bf
+            torch.cuda.empty_cache()
+
+
 def run_quantize(args):
     """The HBM-bound kernels of the path on one [M, K] bf16 tensor (--mnk M N K; N is ignored; default
     32768 x 2048, the activation of a 2048-wide layer at 32768 tokens): one JSON line per kernel."""
@@ -562,6 +637,10 @@ def main():
     if args.workload == "quantize":
         if rank == 0:
             run_quantize(args)
+        return
+    if args.workload == "sweep":
+        if rank == 0:
+            run_sweep(args)
         return
     if args.workload != "gemm":
         run_train(args, rank, local_rank, world)

@@ -136,6 +136,19 @@ int qt_quantize_colwise_t(const void* x, int x_dtype, int64_t rows, int64_t cols
                           uint64_t offset, void* stream);
 
 /*
+ * The same column-wise quantization without the transpose: q [rows, cols] contiguous with
+ * q[r][c] = round(x[r][c] / max(col_absmax[c] / qmax, eps)), scale [cols]. col_absmax is the caller's
+ * (for a row-sharded weight: the element-wise maximum of every rank's qt_col_absmax, which makes the
+ * gathered rows bit-identical to quantizing the whole weight). Stochastic rounding draws the uniform of
+ * element r * cols + c.
+ * replaces: quantize_int8(weight.T, dim=1) of the grad-input product (subclasses/mixed_precision.py:102
+ * called from :176-178), applied per FSDP2 shard; the reference has no sharded form of it.
+ */
+int qt_quantize_colwise(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                        const float* col_absmax, void* q, int q_dtype, void* scale, int scale_dtype,
+                        float eps, int stochastic, uint64_t seed, uint64_t offset, void* stream);
+
+/*
  * qt_col_absmax + qt_quantize_colwise_t in one call that allocates nothing, for hosts that cannot
  * give this library memory at call time: a serving or training runtime that has already claimed the
  * whole device for its own pool (a cudaMalloc from a plugin would fail or fragment it), or a caller
@@ -206,7 +219,10 @@ int qt_int8_mm(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t
 /*
  * C = cast( (fp32(A @ B) * scale_a[m]) * scale_b[n] ) with A, B both int8 (int32 accumulate) or
  * both fp8 (ab_dtype QT_E4M3 / QT_E5M2 per operand, fp32 accumulate). scale_a: [M]; scale_b: [N],
- * or one element when scale_b_is_scalar != 0. Scales and C share scale_dtype (QT_BF16 | QT_F32).
+ * or one element when bit 0 of scale_b_is_scalar is set. Bit 1 of scale_b_is_scalar swaps the order of
+ * the two multiplications to (acc * scale_b[n]) * scale_a[m]: a product computed in transposed form
+ * (C^T = B^T A^T, e.g. a grad-weight written directly in the weight's layout) then rounds exactly like the
+ * untransposed one. Scales and C share scale_dtype (QT_BF16 | QT_F32).
  * replaces: gn_kernels scaled_mm, kernels/gn_kernels/triton_mm.py:345,349-373,382-407
  * (_scaled_mm_kernel :146-220).
  */
@@ -326,6 +342,75 @@ int qt_adamw_bf16_sr_multi(int n_tensors, void* const* p, const void* const* gra
                            float lr, double beta1, double beta2, float weight_decay, float eps,
                            float bias_correction1, float sqrt_bias_correction2, int stochastic,
                            uint64_t seed, uint64_t offset, void* stream);
+
+/* ---- producer-fused activation quantize ------------------------------------------------------------ */
+
+/*
+ * RMSNorm with the activation quantize of the following INT8 linear layers folded in: one pass over x
+ * writes y = weight * bf16(x * rstd) (rstd = 1 / sqrt(mean(x^2) + norm_eps), the arithmetic of an eager
+ * RMSNorm module on bf16 input), rstd per row (may be NULL), and -- when q is not NULL -- the row-wise
+ * quantization of y exactly as qt_quantize_rowwise_colabsmax(y) would produce it: q, scale and the
+ * per-column |y| maxima (zeroed here, reached by atomic max). x, y bf16; y is [rows, cols] contiguous.
+ * Needs 16-byte aligned rows, cols a multiple of 8 and at most 16384, rows a multiple of the rows one
+ * CTA holds at that width (8 up to 1024 columns, 4 / 2 / 1 for up to 2048 / 4096 / more): otherwise
+ * QT_ERR_UNSUPPORTED and the caller runs the norm and the quantize separately.
+ * replaces: nothing the reference has as a kernel. It is the fusion its source names as the open
+ * optimisation ("output is not quantized ... optimization opportunity", subclasses/int8.py:155-156):
+ * RMSNorm (a module of the model, compiled by torch.compile at llm_pretrain.py:138) followed by
+ * quantize_int8 (subclasses/int8.py:12-26) at the entry of _Int8MixedPrecisionLinear.forward
+ * (subclasses/mixed_precision.py:146-160).
+ */
+int qt_rmsnorm_quantize(const void* x, int64_t rows, int64_t cols, int64_t x_row_stride, const void* weight,
+                        float norm_eps, void* y, float* rstd, void* q, int q_dtype, void* scale,
+                        int scale_dtype, float* col_absmax, float eps, void* stream);
+
+/*
+ * Number of rows of fp32 scratch ([partial_rows, cols]) qt_rmsnorm_backward needs for a [rows, cols] input.
+ */
+int64_t qt_rmsnorm_backward_partial_rows(int64_t rows, int64_t cols);
+
+/*
+ * Backward of the RMSNorm above: dx = rstd * (g - n * mean(g * n)) with g = dy * weight, n = x * rstd, and
+ * dweight[c] = sum over rows of dy * bf16(n), all in fp32 from the bf16 inputs; dx bf16 [rows, cols]
+ * contiguous, dweight [cols] of dweight_dtype (QT_BF16 | QT_F32). dw_partial is caller-provided scratch
+ * whose rows are summed in a fixed order (results do not depend on scheduling). Same shape limits as the
+ * forward, any row count.
+ * replaces: the autograd backward of the model's RMSNorm module (no kernel of the reference).
+ */
+int qt_rmsnorm_backward(const void* dy, int64_t dy_row_stride, const void* x, int64_t x_row_stride,
+                        const void* weight, const float* rstd, int64_t rows, int64_t cols, void* dx,
+                        float* dw_partial, int64_t partial_rows, void* dweight, int dweight_dtype, void* stream);
+
+/*
+ * y = bf16(bf16(silu(gate)) * up), the gated activation of a SwiGLU MLP, with the quantize of the
+ * following INT8 linear layer folded in like qt_rmsnorm_quantize (q, scale, col_absmax; q may be NULL).
+ * gate, up, y bf16; same shape limits.
+ * replaces: act_fn(gate_proj(x)) * up_proj(x) of the model's MLP followed by quantize_int8 at the entry
+ * of the down projection (subclasses/mixed_precision.py:146-160, subclasses/int8.py:155-156).
+ */
+int qt_silu_mul_quantize(const void* gate, const void* up, int64_t rows, int64_t cols, int64_t gate_row_stride,
+                         int64_t up_row_stride, void* y, void* q, int q_dtype, void* scale, int scale_dtype,
+                         float* col_absmax, float eps, void* stream);
+
+/*
+ * Backward of the gated activation: dup = dh * bf16(silu(gate)), dgate = dh * up * d silu(gate), fp32
+ * arithmetic, bf16 out ([rows, cols] contiguous). 16-byte aligned rows, cols a multiple of 8.
+ * replaces: the autograd backward of the model's MLP activation (no kernel of the reference).
+ */
+int qt_silu_mul_backward(const void* dh, int64_t dh_row_stride, const void* gate, int64_t gate_row_stride,
+                         const void* up, int64_t up_row_stride, int64_t rows, int64_t cols, void* dgate,
+                         void* dup, void* stream);
+
+/*
+ * Rotary position embedding of x [tokens, heads, head_dim] (bf16, contiguous) with cos / sin
+ * [batch or 1, seq_len, head_dim] (bf16; cos_batch_stride = 0 when one table serves every sequence):
+ * y1 = x1 * cos1 - x2 * sin1, y2 = x2 * cos2 + x1 * sin2 over the two halves of each head; inverse != 0
+ * applies the transpose (the backward pass). head_dim a multiple of 16.
+ * replaces: apply_rotary_pos_emb of the model code the reference trains (transformers' Llama, compiled by
+ * llm_pretrain.py:138); no kernel of the reference.
+ */
+int qt_rope(const void* x, int64_t tokens, int heads, int head_dim, const void* cos, const void* sin,
+            int64_t seq_len, int64_t cos_batch_stride, int inverse, void* y, void* stream);
 
 /* ---- self-tests ------------------------------------------------------------------------------ */
 

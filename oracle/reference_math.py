@@ -92,6 +92,46 @@ def e4m3_bits_to_f32(bits: np.ndarray) -> np.ndarray:
     return E4M3_VALUES[np.asarray(bits, dtype=np.uint8)]
 
 
+def _e5m2_table() -> np.ndarray:
+    """All 256 float8_e5m2 bit patterns decoded to fp32 (IEEE-like: exponent 31 is inf / NaN)."""
+    vals = np.empty(256, dtype=np.float32)
+    for b in range(256):
+        s = -1.0 if b & 0x80 else 1.0
+        e = (b >> 2) & 0x1F
+        m = b & 0x3
+        if e == 0x1F:
+            vals[b] = s * np.inf if m == 0 else np.nan
+        elif e == 0:
+            vals[b] = s * (m / 4.0) * 2.0 ** (-14)
+        else:
+            vals[b] = s * (1.0 + m / 4.0) * 2.0 ** (e - 15)
+    return vals
+
+
+E5M2_VALUES = _e5m2_table()
+
+
+def f32_to_e5m2_bits(x: np.ndarray) -> np.ndarray:
+    """fp32 -> float8_e5m2 bit patterns, round-to-nearest-even, saturating at +-57344 (the other FP8
+    format scaled_mm accepts, kernels/gn_kernels/triton_mm.py:359-361; its absmax constant is
+    DTYPE_AMAX_LUT, kernels/gn_kernels/utils.py:7-11)."""
+    x = np.asarray(x, dtype=np.float32)
+    sign = np.signbit(x)
+    a = np.minimum(np.abs(x).astype(np.float64), 57344.0)
+    grid = E5M2_VALUES[:0x7C].astype(np.float64)   # non-negative finite values, codes 0..0x7B
+    hi = np.searchsorted(grid, a, side="left").clip(0, 0x7B)
+    lo = (hi - 1).clip(0, 0x7B)
+    d_hi = np.abs(grid[hi] - a)
+    d_lo = np.abs(a - grid[lo])
+    pick_lo = (d_lo < d_hi) | ((d_lo == d_hi) & ((lo & 1) == 0))
+    codes = np.where(pick_lo, lo, hi).astype(np.uint8)
+    return np.where(sign, codes | 0x80, codes).astype(np.uint8)
+
+
+def e5m2_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    return E5M2_VALUES[np.asarray(bits, dtype=np.uint8)]
+
+
 # --------------------------------------------------------------------------------------------
 # Philox4x32-10 (the stream the CUDA kernels draw stochastic-rounding uniforms from)
 # --------------------------------------------------------------------------------------------
@@ -139,7 +179,7 @@ def philox_uniforms(n: int, seed: int, offset: int) -> np.ndarray:
 # quantize (subclasses/int8.py:12-26)
 # --------------------------------------------------------------------------------------------
 
-QMAX = {"int8": 127.0, "e4m3": 448.0}
+QMAX = {"int8": 127.0, "e4m3": 448.0, "e5m2": 57344.0}
 
 
 def quantize_absmax(x: np.ndarray, *, axis: int = -1, eps: float = 1e-12, out: str = "int8",
@@ -169,7 +209,7 @@ def quantize_absmax(x: np.ndarray, *, axis: int = -1, eps: float = 1e-12, out: s
     else:
         if uniforms is not None:
             raise ValueError("stochastic rounding is defined for int8 only")
-        q = f32_to_e4m3_bits(v)
+        q = f32_to_e4m3_bits(v) if out == "e4m3" else f32_to_e5m2_bits(v)
     return q, round_to(scale, scale_dtype)
 
 
@@ -198,7 +238,7 @@ def quantize_tile(x: np.ndarray, tile: tuple[int, int], *, eps: float = 1e-12, o
     qmax = np.float32(QMAX[out])
     scale = (np.abs(t).max(axis=(1, 3)) / qmax).astype(np.float32)
     v = (t / np.maximum(scale, np.float32(eps))[:, None, :, None]).astype(np.float32).reshape(nr * tr, nc * tc)[:R, :C]
-    q = np.clip(np.rint(v), -128, 127).astype(np.int8) if out == "int8" else f32_to_e4m3_bits(v)
+    q = np.clip(np.rint(v), -128, 127).astype(np.int8) if out == "int8" else (f32_to_e4m3_bits(v) if out == "e4m3" else f32_to_e5m2_bits(v))
     return q, round_to(scale, scale_dtype)
 
 
@@ -215,7 +255,18 @@ def int8_mm(A: np.ndarray, B: np.ndarray) -> np.ndarray:
 
 
 def _decode(a: np.ndarray, kind: str) -> np.ndarray:
-    return np.asarray(a, dtype=np.float64) if kind == "int8" else e4m3_bits_to_f32(a).astype(np.float64)
+    """Operand values as float64. kind: 'int8', 'e4m3', 'e5m2', or a pair 'e4m3/e5m2' (A / B formats)."""
+    if kind == "int8":
+        return np.asarray(a, dtype=np.float64)
+    if kind == "e4m3":
+        return e4m3_bits_to_f32(a).astype(np.float64)
+    if kind == "e5m2":
+        return e5m2_bits_to_f32(a).astype(np.float64)
+    raise ValueError(kind)
+
+
+def _kinds(kind: str) -> tuple[str, str]:
+    return tuple(kind.split("/")) if "/" in kind else (kind, kind)
 
 
 def scaled_mm(A, B, scale_a, scale_b, *, kind: str = "int8", out_dtype: str = "bf16") -> np.ndarray:
@@ -224,7 +275,8 @@ def scaled_mm(A, B, scale_a, scale_b, *, kind: str = "int8", out_dtype: str = "b
     (:386). For int8 the accumulator is the exact int32; for fp8 it is the fp32-rounded exact sum
     (tensor cores may differ in the last bits, hence a tolerance in the fp8 tests).
     scale_a [M,1], scale_b [1,N] or [1,1], given as fp32 values of the scale dtype."""
-    acc = _decode(A, kind) @ _decode(B, kind)
+    ka, kb_ = _kinds(kind)
+    acc = _decode(A, ka) @ _decode(B, kb_)
     acc32 = acc.astype(np.float32)
     sa = np.asarray(scale_a, dtype=np.float32).reshape(-1, 1)
     sb = np.asarray(scale_b, dtype=np.float32).reshape(1, -1)
@@ -241,7 +293,8 @@ def tile_scaled_mm(A, B, scale_a, scale_b, *, kind: str = "int8", out_dtype: str
     sa = np.asarray(scale_a, dtype=np.float32)
     sb = np.asarray(scale_b, dtype=np.float32)
     qm, qk, qn = M // sa.shape[0], K // sa.shape[1], N // sb.shape[1]
-    Ad, Bd = _decode(A, kind), _decode(B, kind)
+    ka, kb_ = _kinds(kind)
+    Ad, Bd = _decode(A, ka), _decode(B, kb_)
     acc = np.zeros((M, N), dtype=np.float32)
     rows = np.arange(M) // qm
     cols = np.arange(N) // qn

@@ -14,7 +14,7 @@ import sys
 from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent
-SOURCES = ["lib.cu", "quantize.cu", "gemm_sm100.cu", "gemm_tile_sm100.cu", "optim.cu", "bitnet.cu"]
+SOURCES = ["lib.cu", "quantize.cu", "producers.cu", "gemm_sm100.cu", "gemm_tile_sm100.cu", "optim.cu", "bitnet.cu"]
 HEADERS = ["common.cuh", "tcgen05.cuh", "../../include/qt_b200.h"]
 OUT = CSRC.parent / "gn_kernels" / "libqt_b200.so"
 

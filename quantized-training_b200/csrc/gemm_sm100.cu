@@ -82,6 +82,7 @@ struct GemmParams {
     const void* scale_a;
     const void* scale_b;
     int scale_b_is_scalar;
+    int col_scale_first;   // epilogue (acc * col_scale) * row_scale instead of (acc * row_scale) * col_scale
     int scale_dtype;  // QT_BF16 | QT_F32 ; also the output dtype of scaled epilogues
     // tile-scaled only
     int64_t sa_s0, sa_s1, sb_s0, sb_s1;
@@ -435,7 +436,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         for (int j = 0; j < 8; j += 2) {
                             const float a0 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j] : __uint_as_float(r[g * 8 + j]);
                             const float a1 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j + 1] : __uint_as_float(r[g * 8 + j + 1]);
-                            const float2 t = __fmul2_rn(__fmul2_rn(make_float2(a0, a1), rs2), make_float2(cs[j], cs[j + 1]));
+                            // fp32 multiplication is not associative: the order is the caller's (a product
+                            // computed in transposed form keeps the rounding of the untransposed one)
+                            const float2 t = p.col_scale_first ? __fmul2_rn(__fmul2_rn(make_float2(a0, a1), make_float2(cs[j], cs[j + 1])), rs2)
+                                                               : __fmul2_rn(__fmul2_rn(make_float2(a0, a1), rs2), make_float2(cs[j], cs[j + 1]));
                             v[j] = t.x; v[j + 1] = t.y;
                         }
                         if (esz == 2) {
@@ -631,7 +635,7 @@ __global__ void __launch_bounds__(256) splitk_finish_kernel(const GemmParams p) 
         } else {
             const float rs = load_scale(p.scale_a, p.scale_dtype, row);
             const float cs = load_scale(p.scale_b, p.scale_dtype, p.scale_b_is_scalar ? 0 : col);
-            const float o = __fmul_rn(__fmul_rn(v, rs), cs);
+            const float o = p.col_scale_first ? __fmul_rn(__fmul_rn(v, cs), rs) : __fmul_rn(__fmul_rn(v, rs), cs);
             if (p.scale_dtype == QT_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[row * p.ldc + col] = __float2bfloat16_rn(o);
             else reinterpret_cast<float*>(p.c)[row * p.ldc + col] = o;
         }
@@ -839,7 +843,9 @@ extern "C" int qt_scaled_mm_ws(const void* a, int a_dtype, int64_t a_sm, int64_t
     QT_REQUIRE((scale_a && scale_b) || M == 0 || N == 0, "scaled_mm: null scale pointer");
     GemmParams p = {};
     p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc;
-    p.scale_a = scale_a; p.scale_b = scale_b; p.scale_b_is_scalar = scale_b_is_scalar; p.scale_dtype = scale_dtype;
+    QT_REQUIRE(scale_b_is_scalar >= 0 && scale_b_is_scalar <= 3, "scaled_mm: scale_b_is_scalar holds flag bits 0 and 1 only (got %d)", scale_b_is_scalar);
+    p.scale_a = scale_a; p.scale_b = scale_b; p.scale_b_is_scalar = scale_b_is_scalar & 1; p.col_scale_first = (scale_b_is_scalar >> 1) & 1;
+    p.scale_dtype = scale_dtype;
     return gemm_dispatch(EPI_ROWCOL, a, a_dtype, a_sm, a_sk, b, b_dtype, b_sk, b_sn, p, workspace, workspace_bytes, stream);
 }
 

@@ -265,6 +265,15 @@ struct RowwiseParams {
     void* scale_dst[kMaxScatter];
     int n_dst;
     int64_t dst_row0;
+    // producer forms (PRODUCER != 0): the row that gets quantized is first computed from x -- RMSNorm of
+    // x with weight `w_norm`, or silu(x) * x2 -- and also written as bf16 to `y` (row pitch = cols); q may
+    // be null, in which case only y (and rstd) are produced
+    const __nv_bfloat16* w_norm;
+    const __nv_bfloat16* x2;
+    int64_t stride2;
+    __nv_bfloat16* y;
+    float* rstd;
+    float norm_eps;
 };
 
 // ---- packed bf16 helpers -----------------------------------------------------------------------
@@ -603,6 +612,33 @@ rowwise_kernel(const RowwiseParams p) {
     if constexpr (COLABS) fold_column_maxima<TPR, VPT>(colmax, s_col, sub, t, p.cols, p.col_absmax);
 }
 
+// ---- producer arithmetic ---------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+// bf16(a * b) per half: the product of two bf16 values is exact in fp32, so this is the single rounding
+// of an eager bf16 multiply.
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) { return as_u32(__hmul2(as_bf162(a), as_bf162(b))); }
+
+// RMSNorm of one word (two bf16 values) the way an eager module evaluates it
+// (transformers LlamaRMSNorm.forward): n = bf16(float(x) * rstd), y = bf16(weight * n).
+__device__ __forceinline__ uint32_t rmsnorm_word(uint32_t x, uint32_t w, float2 rstd2) {
+    const float2 n = __fmul2_rn(unpack_bf16x2(x), rstd2);
+    return mul_bf16x2(w, pack_bf16x2_rn(n.x, n.y));
+}
+
+// silu(g) * u of one word: s = bf16(g / (1 + exp(-g))) in fp32 (fast exponential and division: the
+// result is within a few fp32 ulp before the bf16 rounding), h = bf16(s * u).
+__device__ __forceinline__ uint32_t silu_mul_word(uint32_t g, uint32_t u) {
+    const float2 gf = unpack_bf16x2(g);
+    const float2 den = __fadd2_rn(make_float2(__expf(-gf.x), __expf(-gf.y)), make_float2(1.0f, 1.0f));
+    return mul_bf16x2(pack_bf16x2_rn(__fdividef(gf.x, den.x), __fdividef(gf.y, den.y)), u);
+}
+
 // The common case of the kernel above with everything that costs instructions removed: the row count is
 // a multiple of the rows per CTA and below 2^30, so rows are counted in 32 bits and need no bounds check;
 // which of a thread's vectors lie inside the row is decided once (those outside stay zero and are never
@@ -613,14 +649,19 @@ rowwise_kernel(const RowwiseParams p) {
 // group covers 128 contiguous bytes, the tile's absmax is one 8-lane reduction, and the per-tile scalar
 // work (scale, reciprocal, scale store) is shared by 16 elements per thread. Vectors 2j and 2j + 1 of a
 // thread are the two halves of its j-th tile.
-template <int TPR, int VPT, bool COLABS, bool SR, bool TILE = false>
-__global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1)))
+// PRODUCER selects what the row is: 0 = x itself; 1 = RMSNorm(x) * w_norm (also writes y and 1/rms per
+// row); 2 = silu(x) * x2 (also writes y). The producer forms fold the activation quantize of the INT8
+// linear layers into the kernel that produces the activation, so the activation is not read again.
+template <int TPR, int VPT, bool COLABS, bool SR, bool TILE = false, int PRODUCER = 0>
+__global__ void __launch_bounds__(kThreads, (PRODUCER != 0 ? (VPT <= 4 ? 2 : 1) : (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1))))
 rowwise_full_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;
     constexpr int WPR = TPR / 32;
-    constexpr bool PREFETCH = VPT <= 8 && !COLABS;
+    constexpr bool PREFETCH = VPT <= 8 && !COLABS && PRODUCER != 2 && (PRODUCER == 0 || VPT <= 4);
     static_assert(!TILE || (VPT % 2 == 0 && !COLABS && !SR), "tile form: vector pairs, no column maxima, round-to-nearest");
+    static_assert(PRODUCER == 0 || (!TILE && !SR), "producer forms: whole rows, round-to-nearest");
     __shared__ uint32_t s_red[2][kThreads / 32];
+    __shared__ float s_sum[2][kThreads / 32];
     __shared__ uint32_t s_col[COLABS ? TPR * VPT * 4 : 1];
 
     const int sub = threadIdx.x / TPR;
@@ -662,13 +703,87 @@ rowwise_full_kernel(const RowwiseParams p) {
         __syncthreads();
     }
 
+    // producer operands: the norm weight of this thread's columns stays in registers; the second input
+    // and the bf16 output advance like the first
+    uint4 wv[PRODUCER == 1 ? VPT : 1];
+    const uint4* src2 = nullptr;
+    int64_t src2_step = 0;
+    uint4* ydst = nullptr;
+    const bool quantizing = PRODUCER == 0 || p.q != nullptr;
+    if constexpr (PRODUCER == 1) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) wv[i] = ok[i] ? reinterpret_cast<const uint4*>(p.w_norm)[vpos[i]] : make_uint4(0, 0, 0, 0);
+    }
+    if constexpr (PRODUCER == 2) {
+        src2 = reinterpret_cast<const uint4*>(p.x2 + (int64_t)row * p.stride2);
+        src2_step = (int64_t)step * (p.stride2 / 8);
+    }
+    if constexpr (PRODUCER != 0) ydst = reinterpret_cast<uint4*>(p.y + (int64_t)row * p.cols);
+
+    uint4 u_buf[PRODUCER == 2 ? VPT : 1];   // second operand of the current row (silu-mul form)
     auto load_row = [&](uint4 (&v)[VPT]) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i)
             if (ok[i]) v[i] = src[vpos[i]];
         src += src_step;
+        if constexpr (PRODUCER == 2) {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) u_buf[i] = ok[i] ? src2[vpos[i]] : make_uint4(0, 0, 0, 0);
+            src2 += src2_step;
+        }
+    };
+    // Sum over the row of a per-thread partial (the TPR threads of the row), through the same slots and
+    // barrier as the absmax fold.
+    auto row_sum = [&](float v, int parity) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        if constexpr (WPR > 1) {
+            if ((threadIdx.x & 31) == 0) s_sum[parity][warp] = v;
+            if constexpr (RPC == 1) __syncthreads();
+            else row_barrier<TPR>(sub);
+            v = s_sum[parity][sub * WPR];
+#pragma unroll
+            for (int w = 1; w < WPR; ++w) v += s_sum[parity][sub * WPR + w];
+        }
+        return v;
     };
     auto process = [&](uint4 (&cur)[VPT], int parity) {
+        if constexpr (PRODUCER == 1) {
+            // sum of squares in fp32 (two lanes of partial sums per thread), 1/rms, then the normed row
+            // replaces x in `cur` and goes out as bf16
+            float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const uint32_t w[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { const float2 f = unpack_bf16x2(w[k]); acc = __ffma2_rn(f, f, acc); }
+            }
+            const float ss = row_sum(__fadd_rn(acc.x, acc.y), parity);
+            const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)p.cols), p.norm_eps));
+            if (t == 0 && p.rstd) p.rstd[row] = rstd;
+            const float2 rstd2 = make_float2(rstd, rstd);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                cur[i] = make_uint4(rmsnorm_word(cur[i].x, wv[i].x, rstd2), rmsnorm_word(cur[i].y, wv[i].y, rstd2),
+                                    rmsnorm_word(cur[i].z, wv[i].z, rstd2), rmsnorm_word(cur[i].w, wv[i].w, rstd2));
+                if (ok[i]) ydst[vpos[i]] = cur[i];
+            }
+            ydst += dst_step;
+        }
+        if constexpr (PRODUCER == 2) {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const uint4 u = u_buf[i];
+                cur[i] = make_uint4(silu_mul_word(cur[i].x, u.x), silu_mul_word(cur[i].y, u.y), silu_mul_word(cur[i].z, u.z),
+                                    silu_mul_word(cur[i].w, u.w));
+                if (ok[i]) ydst[vpos[i]] = cur[i];
+            }
+            ydst += dst_step;
+        }
+        if (!quantizing) {
+            row += step;
+            return;
+        }
         if constexpr (TILE) {
 #pragma unroll
             for (int j = 0; j < VPT / 2; ++j) {
@@ -862,6 +977,68 @@ int launch_tile_1x128(const RowwiseParams& p, cudaStream_t stream) {
     const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
     rowwise_full_kernel<TPR, VPT, false, false, true><<<(unsigned)(want < cap ? want : cap), kThreads, 0, stream>>>(p);
     QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
+// Producer forms through the lean row kernel (bf16, 16-byte aligned rows, cols a multiple of 8 and at most
+// 16384, rows a multiple of the CTA's rows). With q null only the bf16 result is written.
+template <int TPR, int VPT, int PRODUCER>
+int launch_producer_cfg(const RowwiseParams& p, cudaStream_t stream) {
+    constexpr int RPC = kThreads / TPR;
+    constexpr int CTAS_PER_SM = VPT <= 4 ? 2 : 1;
+    if (p.rows % RPC != 0)
+        return fail(QT_ERR_UNSUPPORTED, "fused producer: %lld rows are not a multiple of %d (rows per CTA at this width)", (long long)p.rows, RPC);
+    const int64_t want = p.rows / RPC;
+    const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
+    int64_t grid = want < cap ? want : cap;
+    if (p.q) {
+        grid = (grid + kClusterSize - 1) / kClusterSize * kClusterSize;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = kClusterSize;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        QT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, rowwise_full_kernel<TPR, VPT, true, false, false, PRODUCER>, p));
+    } else {
+        rowwise_full_kernel<TPR, VPT, false, false, false, PRODUCER><<<(unsigned)grid, kThreads, 0, stream>>>(p);
+        QT_CUDA_CHECK(cudaGetLastError());
+    }
+    return QT_OK;
+}
+
+template <int PRODUCER>
+int launch_producer(const RowwiseParams& p, cudaStream_t stream) {
+    const int64_t c = p.cols;
+    if (c <= 256) return launch_producer_cfg<32, 1, PRODUCER>(p, stream);
+    if (c <= 512) return launch_producer_cfg<32, 2, PRODUCER>(p, stream);
+    if (c <= 1024) return launch_producer_cfg<32, 4, PRODUCER>(p, stream);
+    if (c <= 2048) return launch_producer_cfg<64, 4, PRODUCER>(p, stream);
+    if (c <= 4096) return launch_producer_cfg<128, 4, PRODUCER>(p, stream);
+    if (c <= 8192) return launch_producer_cfg<256, 4, PRODUCER>(p, stream);
+    return launch_producer_cfg<256, 8, PRODUCER>(p, stream);
+}
+
+int producer_args(RowwiseParams& p, const void* x, int64_t rows, int64_t cols, int64_t stride, void* y, void* q, int q_dtype,
+                  void* scale, int scale_dtype, float* col_absmax, float eps, cudaStream_t stream, const char* who) {
+    QT_REQUIRE(rows >= 0 && cols >= 0 && stride >= cols, "%s: bad shape/stride", who);
+    QT_REQUIRE(q_dtype == QT_I8 || q_dtype == QT_E4M3 || q_dtype == QT_E5M2, "%s: q_dtype must be QT_I8, QT_E4M3 or QT_E5M2 (got %d)", who, q_dtype);
+    QT_REQUIRE(scale_dtype == QT_BF16 || scale_dtype == QT_F32, "%s: scale_dtype must be QT_BF16 or QT_F32 (got %d)", who, scale_dtype);
+    if (q) QT_REQUIRE(scale && col_absmax, "%s: q given without scale / col_absmax", who);
+    if (q && cols > 0) QT_CUDA_CHECK(cudaMemsetAsync(col_absmax, 0, sizeof(float) * cols, stream));
+    if (rows == 0 || cols == 0) return QT_OK;
+    QT_REQUIRE(x && y, "%s: null pointer", who);
+    if (cols % 8 != 0 || cols > 16384 || rows >= ((int64_t)1 << 30) || !aligned_to(x, 16) || (stride * 2) % 16 != 0 || !aligned_to(y, 16) ||
+        (q && !aligned_to(q, 8)) || eps < 1e-30f)
+        return fail(QT_ERR_UNSUPPORTED, "%s: needs 16-byte aligned bf16 rows, cols a multiple of 8 and at most 16384, eps >= 1e-30", who);
+    p.x = x; p.rows = rows; p.cols = cols; p.stride = stride;
+    p.y = reinterpret_cast<__nv_bfloat16*>(y); p.q = reinterpret_cast<uint8_t*>(q); p.scale = scale; p.col_absmax = col_absmax;
+    p.q_dtype = q_dtype; p.scale_dtype = scale_dtype; p.eps = eps; p.vec_load = 1; p.vec_store = 1;
     return QT_OK;
 }
 
@@ -1194,6 +1371,36 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_fast_kernel(const Colwi
             quantize_tile(b, s_tile[1]);
             __syncthreads();
             store_tile(s_tile[1]);
+        }
+    }
+}
+
+// Column-wise quantize WITHOUT the transpose: q[r][c] = round(x[r][c] / max(absmax[c] / qmax, eps)),
+// one scale per column. This is the form a row-sharded weight takes for the grad-input GEMM (the
+// reference quantizes the weight along its output dimension there, subclasses/mixed_precision.py:176-178
+// through :102): every rank quantizes its own rows with column maxima agreed across the ranks, and the
+// gathered rows are then bit-identical to quantizing the whole weight. Weights are small next to the
+// activations, so this kernel is plain: one thread per 8 consecutive columns of a row, IEEE divisions.
+template <typename XT>
+__global__ void __launch_bounds__(kThreads) colwise_kernel(const ColwiseParams p) {
+    const XT* x = reinterpret_cast<const XT*>(p.x);
+    const float qmax = qmax_of(p.q_dtype);
+    const int64_t nv = (p.cols + 7) / 8;
+    const int64_t total = (p.rows > 0 ? p.rows : 1) * nv;
+    for (int64_t idx = (int64_t)blockIdx.x * kThreads + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * kThreads) {
+        const int64_t row = idx / nv, c0 = (idx - row * nv) * 8;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int64_t c = c0 + k;
+            if (c >= p.cols) break;
+            const float sc = div_rn(p.col_absmax[c], qmax);
+            if (row == 0) store_scale(p.scale, p.scale_dtype, c, sc);
+            if (row < p.rows) {
+                const float v = div_rn(to_float<XT>(x[row * p.stride + c]), fmaxf(sc, p.eps));
+                const int64_t at = row * p.cols + c;
+                const float u = p.stochastic ? uniform1(at, p.seed, p.offset) : 0.0f;
+                p.qt[at] = (uint8_t)quantize_byte(v, p.q_dtype, p.stochastic != 0, u);
+            }
         }
     }
 }
@@ -1531,6 +1738,27 @@ extern "C" int qt_quantize_colwise_t(const void* x, int x_dtype, int64_t rows, i
     return QT_OK;
 }
 
+extern "C" int qt_quantize_colwise(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                                   const float* col_absmax, void* q, int q_dtype, void* scale, int scale_dtype, float eps,
+                                   int stochastic, uint64_t seed, uint64_t offset, void* stream_) {
+    if (int rc = check_quant_args(x, x_dtype, rows, cols, x_row_stride, q, q_dtype, scale, scale_dtype)) return rc;
+    QT_REQUIRE(!stochastic || q_dtype == QT_I8, "quantize: stochastic rounding is defined for int8 output only");
+    if (cols == 0) return QT_OK;
+    QT_REQUIRE(col_absmax && scale, "quantize_colwise: null pointer");
+    ColwiseParams p = {};
+    p.x = x; p.rows = rows; p.cols = cols; p.stride = x_row_stride; p.col_absmax = col_absmax;
+    p.qt = reinterpret_cast<uint8_t*>(q); p.scale = scale; p.q_dtype = q_dtype; p.scale_dtype = scale_dtype;
+    p.eps = eps; p.stochastic = stochastic; p.seed = seed; p.offset = offset;
+    const int64_t work = (rows > 0 ? rows : 1) * ((cols + 7) / 8);
+    const int64_t want = (work + kThreads - 1) / kThreads, cap = (int64_t)num_sms() * 8;
+    const unsigned grid = (unsigned)(want < cap ? want : cap);
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (x_dtype == QT_BF16) colwise_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(p);
+    else colwise_kernel<float><<<grid, kThreads, 0, stream>>>(p);
+    QT_CUDA_CHECK(cudaGetLastError());
+    return QT_OK;
+}
+
 extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
                                 int tile_r, int tile_c, void* q, int q_dtype, void* scale, int scale_dtype, float eps,
                                 void* stream_) {
@@ -1586,6 +1814,34 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
     }
     QT_CUDA_CHECK(cudaGetLastError());
     return QT_OK;
+}
+
+// ---- producer-fused activation quantize ---------------------------------------------------------------
+
+extern "C" int qt_rmsnorm_quantize(const void* x, int64_t rows, int64_t cols, int64_t x_row_stride, const void* weight,
+                                   float norm_eps, void* y, float* rstd, void* q, int q_dtype, void* scale, int scale_dtype,
+                                   float* col_absmax, float eps, void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    RowwiseParams p = {};
+    if (int rc = producer_args(p, x, rows, cols, x_row_stride, y, q, q_dtype, scale, scale_dtype, col_absmax, eps, stream, "rmsnorm_quantize")) return rc;
+    if (rows == 0 || cols == 0) return QT_OK;
+    QT_REQUIRE(weight, "rmsnorm_quantize: weight is null");
+    if (!aligned_to(weight, 16)) return fail(QT_ERR_UNSUPPORTED, "rmsnorm_quantize: weight must be 16-byte aligned");
+    p.w_norm = reinterpret_cast<const __nv_bfloat16*>(weight); p.norm_eps = norm_eps; p.rstd = rstd;
+    return launch_producer<1>(p, stream);
+}
+
+extern "C" int qt_silu_mul_quantize(const void* gate, const void* up, int64_t rows, int64_t cols, int64_t gate_row_stride,
+                                    int64_t up_row_stride, void* y, void* q, int q_dtype, void* scale, int scale_dtype,
+                                    float* col_absmax, float eps, void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    RowwiseParams p = {};
+    if (int rc = producer_args(p, gate, rows, cols, gate_row_stride, y, q, q_dtype, scale, scale_dtype, col_absmax, eps, stream, "silu_mul_quantize")) return rc;
+    if (rows == 0 || cols == 0) return QT_OK;
+    QT_REQUIRE(up && up_row_stride >= cols, "silu_mul_quantize: bad second operand");
+    if (!aligned_to(up, 16) || (up_row_stride * 2) % 16 != 0) return fail(QT_ERR_UNSUPPORTED, "silu_mul_quantize: the second operand's rows must be 16-byte aligned");
+    p.x2 = reinterpret_cast<const __nv_bfloat16*>(up); p.stride2 = up_row_stride;
+    return launch_producer<2>(p, stream);
 }
 
 // ---- row-wise quantize fused with the all-gather of a row-sharded weight ---------------------------

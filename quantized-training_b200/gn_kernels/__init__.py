@@ -3,18 +3,20 @@
 Ops of the hot path keep the reference's names and signatures (kernels/gn_kernels/__init__.py:1-25).
 Ops outside it (int4, fp4, conv2d, MX/NVFP4 utilities) raise NotImplementedError.
 """
-from .mm import int8_mm, scaled_mm
+from .mm import int8_mm, scaled_mm, scaled_mm_t
 from .quantize import (
     col_absmax,
     int8_weight_update_,
     int8_weight_update_supported,
     next_philox_key,
+    quantize_colwise,
     quantize_colwise_t,
     quantize_rowwise,
     quantize_rowwise_colabsmax,
     quantize_tile,
 )
 from ._lib import lib, lib_ops
+from . import fused
 
 
 def _out_of_scope(name: str):

@@ -40,6 +40,8 @@ SIGNATURES = {
     "qt_col_absmax": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "qt_quantize_colwise_t": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                                       c_int, c_float, c_int, c_uint64, c_uint64, c_void_p]),
+    "qt_quantize_colwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p,
+                                    c_int, c_float, c_int, c_uint64, c_uint64, c_void_p]),
     "qt_quantize_colwise_t_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int,
                                               c_float, c_int, c_uint64, c_uint64, c_void_p]),
     "qt_quantize_tile": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int, c_void_p,
@@ -70,6 +72,16 @@ SIGNATURES = {
     "qt_adamw_bf16_sr_multi": (c_int, [c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                        ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), c_int, c_int, c_float, ctypes.c_double,
                                        ctypes.c_double, c_float, c_float, c_float, c_float, c_int, c_uint64, c_uint64, c_void_p]),
+    "qt_rmsnorm_quantize": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int,
+                                    c_void_p, c_int, c_void_p, c_float, c_void_p]),
+    "qt_rmsnorm_backward_partial_rows": (c_int64, [c_int64, c_int64]),
+    "qt_rmsnorm_backward": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                                    c_int64, c_void_p, c_int, c_void_p]),
+    "qt_silu_mul_quantize": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p,
+                                     c_int, c_void_p, c_float, c_void_p]),
+    "qt_silu_mul_backward": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                     c_void_p]),
+    "qt_rope": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "qt_selftest_wait_timeout": (c_int, [ctypes.POINTER(c_int), c_int]),
     "qt_selftest_division": (c_int, [c_int, c_float, ctypes.POINTER(ctypes.c_ulonglong)]),
 }

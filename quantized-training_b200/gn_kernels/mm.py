@@ -128,8 +128,20 @@ def _scale_dtype_ok(scale: Tensor) -> None:
         raise TypeError(f"scales must be bfloat16 or float32, got {scale.dtype}")
 
 
+def scaled_mm_t(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor) -> Tensor:
+    """(B^T @ A^T) written directly, rounding like (A @ B)^T: returns C^T [N, M] for A [M, K] with row scales
+    `scale_A` [M, 1] and B [K, N] with column scales `scale_B` [1, N]. The epilogue multiplies by the scale
+    of A first, as scaled_mm does, so the result is bit-identical to `scaled_mm(A, B, scale_A, scale_B).T`
+    without the strided layout (used for grad-weight, which has to land in the weight's own layout)."""
+    assert A.ndim == B.ndim == 2 and A.shape[1] == B.shape[0]
+    assert scale_A.shape == (A.shape[0], 1) and scale_B.shape == (1, B.shape[1])
+    if _direct(A, B, scale_A, scale_B):
+        return _scaled_mm_cuda(B.T, A.T, scale_B.reshape(-1, 1), scale_A.reshape(1, -1), col_scale_first=True)
+    return scaled_mm(A, B, scale_A, scale_B).T
+
+
 @torch.library.impl(lib, "scaled_mm", "CUDA")
-def _scaled_mm_cuda(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor):
+def _scaled_mm_cuda(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor, col_scale_first: bool = False):
     dev = nv.require_cuda(A, B, row_scale, col_scale)
     _scale_dtype_ok(row_scale)
     M, K = A.shape
@@ -145,7 +157,7 @@ def _scaled_mm_cuda(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor):
         ws, ws_bytes = _workspace(M, N, K, dev)
         nv.check(nv.load().qt_scaled_mm_ws(
             A.data_ptr(), nv.code(A.dtype), A.stride(0), A.stride(1), B.data_ptr(), nv.code(B.dtype), B.stride(0),
-            B.stride(1), row_scale.data_ptr(), col_scale.data_ptr(), int(col_scale.numel() == 1 and N != 1),
+            B.stride(1), row_scale.data_ptr(), col_scale.data_ptr(), int(col_scale.numel() == 1 and N != 1) | (2 if col_scale_first else 0),
             nv.code(row_scale.dtype), C.data_ptr(), C.stride(0), M, N, K, ws, ws_bytes, nv.stream_ptr(dev)))
         nv.raise_if_device_failed()
     return C

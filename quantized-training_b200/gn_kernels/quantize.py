@@ -216,6 +216,25 @@ def quantize_colwise_t(x: Tensor, out_dtype: torch.dtype = torch.int8, stochasti
     return fn(x, col_absmax_, out_dtype, scale_dtype or x.dtype, stochastic_rounding, eps, seed, offset)
 
 
+def quantize_colwise(x: Tensor, col_absmax_: Tensor, out_dtype: torch.dtype = torch.int8, stochastic_rounding: bool = False, *,
+                     eps: float = 1e-12, scale_dtype: torch.dtype | None = None, key: tuple[int, int] | None = None):
+    """Per-column absmax quantize WITHOUT the transpose, from given column maxima: returns (q [R,C],
+    scale [C,1]). For a row shard of a weight whose column maxima were agreed across the ranks."""
+    x = _rows_view(x)
+    dev = nv.require_cuda(x, col_absmax_)
+    rows, cols = x.shape
+    if col_absmax_.dtype != torch.float32 or col_absmax_.numel() != cols or not col_absmax_.is_contiguous():
+        raise ValueError("col_absmax must be a contiguous float32 tensor with one entry per column of x")
+    seed, offset = key if key is not None else (next_philox_key(dev) if stochastic_rounding else (0, 0))
+    q = torch.empty((rows, cols), dtype=out_dtype, device=dev)
+    scale = torch.empty((cols, 1), dtype=scale_dtype or x.dtype, device=dev)
+    with nv.on_device(dev):
+        nv.check(nv.load().qt_quantize_colwise(
+            x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), col_absmax_.data_ptr(), q.data_ptr(), nv.code(out_dtype),
+            scale.data_ptr(), nv.code(scale.dtype), eps, int(stochastic_rounding), seed, offset, nv.stream_ptr(dev)))
+    return q, scale
+
+
 def quantize_tile(x: Tensor, tile_shape: tuple[int, int], out_dtype: torch.dtype = torch.int8, *, eps: float = 1e-12,
                   scale_dtype: torch.dtype | None = None):
     """Per-tile absmax quantize (tiles 1x128 or 128x128): returns (q [R,C], scale [R/tr, C/tc])."""

@@ -1,7 +1,9 @@
-"""FSDP2 with the INT8 weight all-gather on two GPUs (skipped with fewer): every rank holds a row
-shard of each Linear weight, `fsdp_pre_all_gather` quantizes the shard row-wise, NCCL gathers int8
-rows + bf16 scales, and the forward must equal the unsharded INT8 mixed-precision forward bit for
-bit (row-wise quantization commutes with row sharding)."""
+"""FSDP2 with the INT8 weight all-gather, on one GPU (a process group of one rank: the hooks, the gather
+buffers and the backward re-gather all run) and on two (skipped with fewer): every rank holds a row
+shard of each Linear weight, `fsdp_pre_all_gather` quantizes the shard, NCCL gathers int8 rows + bf16
+scales, and forward, grad-input and grad-weight must equal the unsharded INT8 mixed-precision layer bit
+for bit (row-wise quantization commutes with row sharding; the backward gather quantizes along the
+output dimension with column maxima agreed by an all-reduce(MAX))."""
 import os
 import socket
 
@@ -24,7 +26,7 @@ def _build(seed=0):
     ).bfloat16()
 
 
-def _worker(rank: int, world: int, port: int, out_path: str, mode: str = "int8_mp"):
+def _worker(rank: int, world: int, port: int, out_path: str, mode: str = "int8_mp", variant: str = ""):
     import sys
     from pathlib import Path
 
@@ -33,20 +35,26 @@ def _worker(rank: int, world: int, port: int, out_path: str, mode: str = "int8_m
     import torch.distributed as dist
     from torch.distributed.fsdp import fully_shard
 
-    from subclasses import MixedPrecisionConfig, convert_bitnet, convert_mixed_precision
+    from subclasses import MixedPrecisionConfig, MixedPrecisionLinearWeight, convert_bitnet, convert_mixed_precision
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         model = _build().cuda()
+        kwargs = {}
         if mode == "bitnet":
             convert_bitnet(model)
         else:
-            convert_mixed_precision(model, config=MixedPrecisionConfig())
+            convert_mixed_precision(model, config=MixedPrecisionConfig(grad_input=variant != "bf16_grad_input"))
+            MixedPrecisionLinearWeight.backward_gather = "row" if variant == "row_backward" else "col"
+            if variant == "fp32_reduce":
+                from torch.distributed.fsdp import MixedPrecisionPolicy
+
+                kwargs["mp_policy"] = MixedPrecisionPolicy(reduce_dtype=torch.float32)
         for layer in (model[0], model[2]):
-            fully_shard(layer)
-        fully_shard(model)
+            fully_shard(layer, **kwargs)
+        fully_shard(model, **kwargs)
         g = torch.Generator().manual_seed(100)              # same batch on both ranks: grads must agree
         x = torch.randn(64, 256, generator=g).bfloat16().cuda().requires_grad_()
         y = model(x)
@@ -67,34 +75,65 @@ def _worker(rank: int, world: int, port: int, out_path: str, mode: str = "int8_m
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_fsdp2_int8_all_gather_matches_unsharded(tmp_path):
-    import torch.multiprocessing as mp
-
+def _unsharded(grad_input=True):
     from subclasses import MixedPrecisionConfig, convert_mixed_precision
 
-    out_path = str(tmp_path / "fsdp.pt")
-    mp.spawn(_worker, args=(2, _free_port(), out_path), nprocs=2, join=True)
-    got = torch.load(out_path)
-    # the all-gather moved int8 rows and bf16 scales, not bf16 weights
-    assert all(ds == ["torch.int8", "torch.bfloat16"] for ds in got["gathered"]), got["gathered"]
-
     model = _build().cuda()
-    convert_mixed_precision(model, config=MixedPrecisionConfig())
+    convert_mixed_precision(model, config=MixedPrecisionConfig(grad_input=grad_input))
     g = torch.Generator().manual_seed(100)
     x = torch.randn(64, 256, generator=g).bfloat16().cuda().requires_grad_()
     y = model(x)
     y.float().square().mean().backward()
-    assert torch.equal(y.detach().float().cpu(), got["y"])                     # forward: bit-exact
-    ref_grads = [p.grad.float().cpu() for p in model.parameters()]
-    for a, b in zip(got["grads"], ref_grads):                                   # grad_weight: same INT8 matmul
-        assert (a - b).norm() / b.norm() < 2e-2
-    # grad_input uses the gathered int8 weight (scale folded into dY): within quantization error
-    assert (got["gx"] - x.grad.float().cpu()).norm() / x.grad.float().norm().cpu() < 3e-2
+    return y.detach().float().cpu(), x.grad.float().cpu(), [p.grad.float().cpu() for p in model.parameters()]
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_fsdp2_bitnet_2bit_all_gather_matches_unsharded(tmp_path):
+@pytest.mark.parametrize("world", [1, 2])
+def test_fsdp2_int8_all_gather_matches_unsharded(tmp_path, world):
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs two GPUs")
+    out_path = str(tmp_path / "fsdp.pt")
+    mp.spawn(_worker, args=(world, _free_port(), out_path), nprocs=world, join=True)
+    got = torch.load(out_path)
+    if world > 1:   # the all-gather moved int8 rows and bf16 scales, not bf16 weights
+        assert all(ds == ["torch.int8", "torch.bfloat16"] for ds in got["gathered"]), got["gathered"]
+    else:           # one rank: nothing crosses a link, the hook hands FSDP2 the bf16 shard
+        assert all(ds == ["torch.bfloat16"] for ds in got["gathered"]), got["gathered"]
+    y, gx, grads = _unsharded()
+    assert torch.equal(got["y"], y)                       # forward: the gathered rows are the unsharded quantization
+    assert torch.equal(got["gx"], gx)                     # grad_input: same for the column-wise backward gather
+    for a, b in zip(got["grads"], grads):                 # grad_weight: the same INT8 product on every rank
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("variant", ["row_backward", "bf16_grad_input", "fp32_reduce"])
+def test_fsdp2_int8_all_gather_variants(tmp_path, variant):
+    """Two ranks when the box has them, else one. row_backward: the forward's row-wise quantization also serves backward,
+    its row scales folded into dY (within quantization error of the reference's product). bf16_grad_input:
+    a config that keeps grad-input in bf16 gathers the bf16 weight, so every product is the unsharded one.
+    fp32_reduce: gradients are reduce-scattered in fp32 (torch's MixedPrecisionPolicy) with the INT8 gather."""
+    import torch.multiprocessing as mp
+
+    world = 2 if torch.cuda.device_count() >= 2 else 1   # with one rank the gather is bf16 and all variants are exact
+    out_path = str(tmp_path / "fsdp.pt")
+    mp.spawn(_worker, args=(world, _free_port(), out_path, "int8_mp", variant), nprocs=world, join=True)
+    got = torch.load(out_path)
+    y, gx, grads = _unsharded(grad_input=variant != "bf16_grad_input")
+    assert torch.equal(got["y"], y)
+    if variant == "bf16_grad_input" or world == 1:
+        assert all(ds == ["torch.bfloat16"] for ds in got["gathered"]), got["gathered"]
+    folded = variant == "row_backward" and world > 1
+    if folded:
+        assert (got["gx"] - gx).norm() / gx.norm() < 3e-2
+    else:
+        assert torch.equal(got["gx"], gx)
+    for a, b in zip(got["grads"], grads):
+        assert (a - b).norm() / b.norm() < (3e-2 if folded else 1e-6)
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_fsdp2_bitnet_2bit_all_gather_matches_unsharded(tmp_path, world):
     """BitNet weights cross NVLink as packed 2-bit ternaries (4 per byte); the tensor-wide abs-mean is
     the average of the two equal-size shards' abs-means, equal to the unsharded one up to fp32 rounding,
     so the forward agrees within a few weights flipping between ternary levels."""
@@ -102,8 +141,10 @@ def test_fsdp2_bitnet_2bit_all_gather_matches_unsharded(tmp_path):
 
     from subclasses import convert_bitnet
 
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs two GPUs")
     out_path = str(tmp_path / "fsdp_bitnet.pt")
-    mp.spawn(_worker, args=(2, _free_port(), out_path, "bitnet"), nprocs=2, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), out_path, "bitnet"), nprocs=world, join=True)
     got = torch.load(out_path)
     assert all(ds == ["torch.int8"] for ds in got["gathered"]), got["gathered"]
     # 512x256 and 384x512 weights, four ternaries per byte

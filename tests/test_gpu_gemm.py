@@ -279,3 +279,107 @@ def test_a_recorded_wait_failure_raises_from_the_next_gemm_call():
     out = gn_kernels.scaled_mm(a, a.T, sa, sb)
     ref = torch._int_mm(a.cpu(), a.cpu().T.contiguous()).float().bfloat16()
     assert torch.equal(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("kinds", [("e5m2", "e5m2"), ("e4m3", "e5m2"), ("e5m2", "e4m3")])
+@pytest.mark.parametrize("layout", ["A@B.T", "A.T@B.T"])
+def test_scaled_mm_fp8_e5m2_and_mixed_formats(kinds, layout):
+    """The other FP8 format scaled_mm accepts (kernels/gn_kernels/triton_mm.py:359-361), alone and mixed
+    with e4m3, against the oracle's decode + fp32 product; also the layout with both operands MN-major."""
+    M, N, K = 256, 384, 512
+    g = torch.Generator().manual_seed(77)
+    td = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+    A8 = torch.randn(M, K, generator=g).to(td[kinds[0]]).cuda()
+    B8 = torch.randn(K, N, generator=g).to(td[kinds[1]]).cuda()
+    sa = (torch.rand(M, 1, generator=g) / 64 + 1e-3).bfloat16().cuda()
+    sb = (torch.rand(1, N, generator=g) / 64 + 1e-3).bfloat16().cuda()
+    a, b = to_layout(A8, B8, layout)
+    out = gn_kernels.scaled_mm(a, b, sa, sb)
+    want = om.scaled_mm(bits_of(A8), bits_of(B8), values_of(sa), values_of(sb), kind="/".join(kinds))
+    np.testing.assert_allclose(values_of(out), want, rtol=1e-2, atol=1e-4)
+
+
+def test_scaled_mm_fp8_both_operands_mn_major():
+    M, N, K = 384, 256, 640
+    g = torch.Generator().manual_seed(78)
+    A8 = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn).cuda()
+    B8 = torch.randn(K, N, generator=g).to(torch.float8_e4m3fn).cuda()
+    sa = (torch.rand(M, 1, generator=g) / 64 + 1e-3).bfloat16().cuda()
+    sb = (torch.rand(1, N, generator=g) / 64 + 1e-3).bfloat16().cuda()
+    a, b = to_layout(A8, B8, "A.T@B.T")
+    want = om.scaled_mm(bits_of(A8), bits_of(B8), values_of(sa), values_of(sb), kind="e4m3")
+    np.testing.assert_allclose(values_of(gn_kernels.scaled_mm(a, b, sa, sb)), want, rtol=1e-2, atol=1e-4)
+
+
+@pytest.mark.parametrize("size", [2048, 4096])
+@pytest.mark.parametrize("layout", ["A@B.T", "A@B", "A.T@B"])
+def test_sweep_sizes_int32_exact_on_sampled_rows(size, layout):
+    """The middle sizes of the reference's benchmark grid (benchmark_mm.py:70-76): exact int32 accumulators
+    on sampled rows against the oracle, the scaled output equal to the accumulator times power-of-two
+    scales, and the same bits on a second run."""
+    A, B = rand_i8((size, size), 5 + size), rand_i8((size, size), 6 + size)
+    a, b = to_layout(A, B, layout)
+    acc = gn_kernels.int8_mm(a, b)
+    rows = torch.tensor([0, 127, 128, size // 2 + 3, size - 1], device="cuda")
+    np.testing.assert_array_equal(acc[rows].cpu().numpy(), om.int8_mm(A[rows].cpu().numpy(), B.cpu().numpy()))
+    sa = torch.full((size, 1), 2.0 ** -6, dtype=torch.bfloat16, device="cuda")
+    sb = torch.full((1, size), 2.0 ** -8, dtype=torch.bfloat16, device="cuda")
+    out = gn_kernels.scaled_mm(a, b, sa, sb)
+    assert torch.equal(out, (acc.float() * 2.0 ** -14).bfloat16())
+    assert torch.equal(gn_kernels.scaled_mm(a, b, sa, sb), out)
+    assert torch.equal(gn_kernels.int8_mm(a, b), acc)
+
+
+def test_transposed_output_form_is_bit_identical():
+    """scaled_mm_t writes (A @ B)^T directly with the column scale applied first: same bits as transposing
+    the ordinary result (grad-weight lands in the weight's layout without a strided copy), split-K shapes included."""
+    for (M, N, K) in [(256, 384, 512), (1024, 512, 8192), (2048, 256, 32768)]:
+        A, B = rand_i8((M, K), 91 + M), rand_i8((N, K), 92 + N)
+        g = torch.Generator().manual_seed(M + N)
+        sa = (torch.rand(M, 1, generator=g) / 64 + 1e-3).bfloat16().cuda()
+        sb = (torch.rand(1, N, generator=g) / 64 + 1e-3).bfloat16().cuda()
+        ref = gn_kernels.scaled_mm(A, B.T, sa, sb)
+        out_t = gn_kernels.scaled_mm_t(A, B.T, sa, sb)
+        assert out_t.shape == (N, M) and out_t.is_contiguous()
+        assert torch.equal(out_t, ref.T)
+
+
+def test_outputs_stay_inside_their_buffers():
+    """Guard bands around every output of a GEMM and of the quantize kernels stay untouched (the check a
+    memory checker would make), on shapes that exercise ragged edges."""
+    def guarded(shape, dtype, fill):
+        n = int(np.prod(shape))
+        pad = 4096 // torch.empty((), dtype=dtype).element_size()
+        buf = torch.full((n + 2 * pad,), fill, dtype=dtype, device="cuda")
+        return buf, buf[pad:pad + n].view(shape), pad
+
+    import ctypes
+
+    M, N, K = 300, 520, 272
+    A, B = rand_i8((M, K + 16 - K % 16), 3)[:, :K], rand_i8((N, K + 16 - K % 16), 4)[:, :K]
+    cbuf, C, pad = guarded((M, N), torch.int32, 0x5A5A5A5A)
+    nv.check(nv.load().qt_int8_mm(A.data_ptr(), A.stride(0), 1, B.data_ptr(), 1, B.stride(0), C.data_ptr(), N, M, N, K,
+                                  nv.stream_ptr(A.device)))
+    torch.cuda.synchronize()
+    assert (cbuf[:pad] == 0x5A5A5A5A).all() and (cbuf[-pad:] == 0x5A5A5A5A).all()
+    np.testing.assert_array_equal(C.cpu().numpy(), om.int8_mm(A.cpu().numpy(), B.cpu().numpy().T))
+
+    x = randn_bf16((333, 776), seed=8)
+    qbuf, q, qpad = guarded((333, 776), torch.int8, 0x5A)
+    sbuf, s, spad = guarded((333, 1), torch.bfloat16, 7.0)
+    nv.check(nv.load().qt_quantize_rowwise(x.data_ptr(), nv.QT_BF16, 333, 776, 776, q.data_ptr(), nv.QT_I8, s.data_ptr(), nv.QT_BF16,
+                                           1e-12, 0, 0, 0, nv.stream_ptr(x.device)))
+    tbuf, qt, tpad = guarded((776, 333), torch.int8, 0x5A)
+    cs_buf, cs, cpad = guarded((776, 1), torch.bfloat16, 7.0)
+    colmax = gn_kernels.col_absmax(x)
+    nv.check(nv.load().qt_quantize_colwise_t(x.data_ptr(), nv.QT_BF16, 333, 776, 776, colmax.data_ptr(), qt.data_ptr(), nv.QT_I8,
+                                             cs.data_ptr(), nv.QT_BF16, 1e-12, 0, 0, 0, nv.stream_ptr(x.device)))
+    torch.cuda.synchronize()
+    for buf, p_, fill in ((qbuf, qpad, 0x5A), (tbuf, tpad, 0x5A)):
+        assert (buf[:p_] == fill).all() and (buf[-p_:] == fill).all()
+    for buf, p_ in ((sbuf, spad), (cs_buf, cpad)):
+        assert (buf[:p_] == 7.0).all() and (buf[-p_:] == 7.0).all()
+    oq, os_ = om.quantize_rowwise(values_of(x))
+    np.testing.assert_array_equal(q.cpu().numpy(), oq)
+    oqt, _ = om.quantize_colwise_t(values_of(x))
+    np.testing.assert_array_equal(qt.cpu().numpy(), oqt)

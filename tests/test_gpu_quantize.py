@@ -213,3 +213,57 @@ def test_full_size_properties():
     # idempotence on already-quantized values: quantizing q * scale with the same absmax gives q
     deq_err_t = (qt.float().cpu() * (cm.cpu() / 127).view(-1, 1) - x.float().cpu().T).abs()
     assert (deq_err_t <= 0.5 * (cm.cpu() / 127).view(-1, 1) * (1 + 1e-3) + 1e-30).all()
+
+
+@pytest.mark.parametrize("shape", [(192, 256), (100, 333), (1, 64), (64, 5), (0, 32)])
+def test_colwise_without_transpose_matches_oracle(shape):
+    """Column-wise scales, rows left in place (the backward weight gather of a row-sharded weight): equal to
+    quantize_int8(x, dim=0) of the reference's definition, for bf16 and fp32 input."""
+    for dtype in (torch.bfloat16, torch.float32):
+        x = randn_bf16(shape, seed=shape[0] + shape[1]).to(dtype)
+        colmax = gn_kernels.col_absmax(x)
+        q, s = gn_kernels.quantize_colwise(x, colmax)
+        assert q.shape == x.shape and s.shape == (shape[1], 1) and s.dtype == dtype
+        if shape[0] == 0:
+            assert torch.count_nonzero(s) == 0
+            continue
+        oq, os_ = om.quantize_absmax(values_of(x), axis=0, scale_dtype="bf16" if dtype is torch.bfloat16 else "f32")
+        np.testing.assert_array_equal(q.cpu().numpy(), oq)
+        np.testing.assert_array_equal(values_of(s).reshape(-1), os_.reshape(-1))
+
+
+@pytest.mark.parametrize("shape", [(256, 512), (100, 333), (64, 4096)])
+def test_rowwise_e5m2_matches_oracle(shape):
+    x = randn_bf16(shape, seed=shape[1] + 1)
+    q, s = gn_kernels.quantize_rowwise(x, torch.float8_e5m2)
+    oq, os_ = om.quantize_rowwise(values_of(x), out="e5m2")
+    np.testing.assert_array_equal(bits_of(q), oq)
+    np.testing.assert_array_equal(values_of(s), os_)
+
+
+@pytest.mark.parametrize("shape", [(256, 256), (384, 1024), (130, 200)])
+@pytest.mark.parametrize("out", ["e4m3", "e5m2"])
+def test_tile_128x128_fp8_matches_oracle(shape, out):
+    x = randn_bf16(shape, seed=shape[0] + 3)
+    dt = torch.float8_e4m3fn if out == "e4m3" else torch.float8_e5m2
+    q, s = gn_kernels.quantize_tile(x, (128, 128), dt)
+    oq, os_ = om.quantize_tile(values_of(x), (128, 128), out=out)
+    np.testing.assert_array_equal(bits_of(q), oq)
+    np.testing.assert_array_equal(values_of(s), os_)
+    q1, s1 = gn_kernels.quantize_tile(x, (1, 128), dt)
+    oq1, os1 = om.quantize_tile(values_of(x), (1, 128), out=out)
+    np.testing.assert_array_equal(bits_of(q1), oq1)
+    np.testing.assert_array_equal(values_of(s1), os1)
+
+
+def test_quantize_kernels_give_the_same_bits_twice():
+    x = randn_bf16((4096, 2048), seed=12)
+    a = gn_kernels.quantize_rowwise_colabsmax(x)
+    b = gn_kernels.quantize_rowwise_colabsmax(x)
+    assert all(torch.equal(u, v) for u, v in zip(a, b))
+    k = (2024, 5)
+    a = gn_kernels.quantize_rowwise(x, torch.int8, True, key=k)
+    b = gn_kernels.quantize_rowwise(x, torch.int8, True, key=k)
+    assert torch.equal(a[0], b[0])
+    c = gn_kernels.quantize_rowwise(x, torch.int8, True, key=(2024, 6))
+    assert not torch.equal(a[0], c[0])

@@ -115,14 +115,33 @@ def test_int8_gathered_weight_forward_backward():
     yb = F.linear(xb, mp)
     assert torch.equal(ya, yb)
     gy = randn_bf16(tuple(ya.shape), seed=6)
+    # backward with only the forward's (row-wise) quantization at hand: within quantization error
     ya.backward(gy)
     ref_gx = gy.float() @ w.float()
     assert (xa.grad.float() - ref_gx).norm() / ref_gx.norm() < 3e-2
+    # the unsharded layer's backward is the reference for the column-wise backward gather
+    yb.backward(gy)
+    # backward gather: two shards quantized along the output dimension with the agreed column maxima
+    colmax = torch.maximum(gn_kernels.col_absmax(w[:192]), gn_kernels.col_absmax(w[192:]))
+    assert torch.equal(colmax, gn_kernels.col_absmax(w))
+    c0, cs0 = gn_kernels.quantize_colwise(w[:192], colmax)
+    c1, cs1 = gn_kernels.quantize_colwise(w[192:], colmax)
+    qt_full, cs_full = gn_kernels.quantize_colwise_t(w)
+    assert torch.equal(torch.cat([c0, c1]).T.contiguous(), qt_full) and torch.equal(cs0, cs_full) and torch.equal(cs1, cs_full)
+    gathered2 = Int8RowScaledLinearWeight(qf.clone(), sf, MixedPrecisionConfig())
+    xc = x.clone().requires_grad_()
+    yc = F.linear(xc, gathered2)
+    assert torch.equal(yc, yb)
+    with torch.autograd._unsafe_preserve_version_counter(gathered2.int_data):   # FSDP2 refills the same buffers this way
+        gathered2.int_data.copy_(torch.cat([c0, c1]))
+    gathered2.mode, gathered2.col_scale = "col", cs0
+    yc.backward(gy)
+    assert torch.equal(xc.grad, xb.grad)                 # grad_input: bit-identical to the unsharded layer
     # hooks: pre returns int8 rows + scales, post rebuilds the gathered weight
     (wi8, wsc), meta = mp.fsdp_pre_all_gather(None)
     assert wi8.dtype is torch.int8 and torch.equal(wi8, qf) and torch.equal(wsc, sf)
     rebuilt, inner = mp.fsdp_post_all_gather((wi8, wsc), meta, torch.bfloat16)
-    assert isinstance(rebuilt, Int8RowScaledLinearWeight) and inner[0] is wi8
+    assert isinstance(rebuilt, Int8RowScaledLinearWeight) and inner[0] is wi8 and rebuilt.mode == "row"
 
 
 def test_int8_weight_only_subclass(golden_dir):

@@ -186,3 +186,20 @@ def test_cpu_path_matches_reference_fixtures(golden_dir):
     np.testing.assert_array_equal(out.float().numpy(), om.scaled_mm(oqa, oqb.T, osa, osb.T))
     if dig(bits(A)) == ref["A"] and dig(bits(B)) == ref["B"]:
         assert dig(bits(out)) == ref["out"] and dig(qa.numpy()) == ref["qa"]
+
+
+def test_e5m2_codec_roundtrip_and_rounding():
+    """The second FP8 format: decode table, round-to-nearest-even with saturation at 57344, pinned against
+    the casts of the framework the reference runs on (torch.float8_e5m2 on CPU)."""
+    import torch
+
+    codes = np.arange(256, dtype=np.uint8)
+    vals = om.e5m2_bits_to_f32(codes)
+    finite = np.isfinite(vals)
+    np.testing.assert_array_equal(om.f32_to_e5m2_bits(vals[finite]), codes[finite])
+    assert om.f32_to_e5m2_bits(np.float32([0.0, 1e9, -1e9, 57344.0, 1.25, 1.125, 1.375])).tolist() == [0, 0x7B, 0xFB, 0x7B, 0x3D, 0x3C, 0x3E]
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(100000, generator=g) * torch.logspace(-7, 4.5, 100000)
+    ref = x.clamp(-57344, 57344).to(torch.float8_e5m2).view(torch.uint8).numpy()
+    np.testing.assert_array_equal(om.f32_to_e5m2_bits(x.numpy()), ref)
+    np.testing.assert_array_equal(np.nan_to_num(vals, nan=7.0), np.nan_to_num(torch.from_numpy(codes).view(torch.float8_e5m2).float().numpy(), nan=7.0))

@@ -53,7 +53,7 @@ def parse_args():
     ap.add_argument("--no-quantize-lines", action="store_true", help="leave the quantize kernels' roofline entries out of the N=1 line")
     ap.add_argument("--workload", default="gemm", choices=["gemm", "quantize", "sweep", "train-470m", "train-1b"],
                     help="gemm: the headline quantize + scaled GEMM step; train-*: one INT8 mixed-precision Llama step (tok/s)")
-    ap.add_argument("--parallel", default="ddp", choices=["ddp", "fsdp"], help="train-* workloads with --gpus > 1: DDP, or FSDP2 with the INT8 weight all-gather")
+    ap.add_argument("--parallel", default="fsdp", choices=["ddp", "fsdp"], help="train-* workloads with --gpus > 1: DDP, or FSDP2 with the INT8 weight all-gather")
     ap.add_argument("--quantize", default="mixed_precision", choices=["mixed_precision", "none", "int8_quantized_training", "bitnet"],
                     help="train-* workloads: which weight subclass the decoder's Linear layers get (none = bf16 baseline)")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
@@ -63,10 +63,15 @@ def parse_args():
                     help="SMs the GEMM leaves free when --gpus > 1 (default: 8 beside NCCL's all-gather kernel, 0 with the fused gather)")
     ap.add_argument("--eager-elementwise", action="store_true",
                     help="train-* workloads: leave RMSNorm, the gated activation and rotary embedding to the model's eager code")
+    ap.add_argument("--train-data", default="fixed", choices=["fixed", "markov"],
+                    help="train-* workloads: one fixed random batch (throughput), or a fresh batch of learnable synthetic streams per step (loss curves)")
+    ap.add_argument("--reduce-fp32", action="store_true", help="train-* workloads with FSDP2: reduce-scatter gradients in fp32")
+    ap.add_argument("--no-train-line", action="store_true", help="leave the training throughput measurement out of the default line")
     ap.add_argument("--layers", type=int, default=None, help="train-* workloads: number of decoder layers (default: the model's own)")
     ap.add_argument("--profile", default=None, metavar="FILE",
                     help="train-* workloads: after the timed steps, run two more under torch.profiler and write the kernel table "
                          "(device time per kernel, share of the step) to FILE")
+    ap.add_argument("--lead-in-seconds", type=float, default=0.25, help="--workload sweep: untimed replays of a case before it is timed")
     ap.add_argument("--plain-launches", action="store_true", help="--workload quantize: plain launches instead of CUDA-graph replays (for a profiler run)")
     ap.add_argument("--only", default=None, help="--workload quantize: only the kernels whose name contains this text")
     ap.add_argument("--no-clock-sampler", action="store_true", help="do not run nvidia-smi beside the timed region")
@@ -303,61 +308,77 @@ LLAMA_SHAPES = {
 }
 
 
-def run_train(args, rank, local_rank, world):
-    """Secondary workload: one INT8 mixed-precision training step of a random-init Llama-style decoder
-    (forward, grad-input and grad-weight GEMMs all row-wise INT8; LM head in bf16; AdamWBF16SR), batch
-    16 x 2048 random tokens per GPU, tok/s as the reference computes it (llm_pretrain.py:229-234).
-    Data parallel over ranks with DDP-style gradient all-reduce when launched with torchrun."""
+def _markov_tokens(n_seq: int, seq: int, vocab: int, gen: torch.Generator, dev) -> torch.Tensor:
+    """Synthetic token streams a model can learn (stand-in for the text corpora the reference trains on, which
+    are not available offline): token t+1 = (a * token t + b + noise) mod vocab with a small noise alphabet,
+    so the next-token entropy is log(8) instead of log(vocab)."""
+    start = torch.randint(0, vocab, (n_seq, 1), generator=gen)
+    noise = torch.randint(0, 8, (n_seq, seq), generator=gen)
+    out = torch.empty((n_seq, seq + 1), dtype=torch.long)
+    out[:, :1] = start
+    for t in range(seq):
+        out[:, t + 1] = (out[:, t] * 31 + 7 + noise[:, t]) % vocab
+    return out.to(dev)
+
+
+def train_measure(workload: str, quantize: str, parallel: str, steps: int, warmup: int, rank: int, local_rank: int, world: int, *,
+                  layers=None, eager_elementwise=False, data="fixed", profile=None, reduce_fp32=False) -> dict:
+    """One measurement of the training workload (the process group, if any, is already up): returns the fields of
+    the JSON line. INT8 mixed-precision training step of a random-init Llama-style decoder (forward, grad-input
+    and grad-weight GEMMs all row-wise INT8; LM head in bf16; AdamWBF16SR), batch 16 x 2048 tokens per GPU,
+    tok/s as the reference computes it (llm_pretrain.py:229-234). With several ranks: FSDP2 per decoder layer
+    (llm_pretrain.py:134-139) with the INT8 weight all-gather, or DDP."""
     from transformers import LlamaConfig, LlamaForCausalLM
 
-    from train_utils import get_optimizer, quantize_model
+    from train_utils import fuse_decoder_elementwise, get_optimizer, quantize_model
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
     bs, seq = 16, 2048
     torch.manual_seed(2024)
-    shape = dict(LLAMA_SHAPES[args.workload])
-    if args.layers is not None:
-        shape["num_hidden_layers"] = args.layers
+    shape = dict(LLAMA_SHAPES[workload])
+    if layers is not None:
+        shape["num_hidden_layers"] = layers
     cfg = LlamaConfig(vocab_size=32000, max_position_embeddings=seq, attn_implementation="sdpa", tie_word_embeddings=False, **shape)
     with torch.device(dev):
         model = LlamaForCausalLM(cfg).bfloat16()
-    quantize_model(model.model, None if args.quantize == "none" else args.quantize)
-    if not args.eager_elementwise:
-        from train_utils import fuse_decoder_elementwise
+    quantize_model(model.model, None if quantize == "none" else quantize)
+    if not eager_elementwise:
+        # RMSNorm / silu * up / rotary embedding as single kernels; they emit the int8 activations where INT8 linears follow
+        fuse_decoder_elementwise(model)
+    if world > 1 and parallel == "fsdp":
+        from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
-        fuse_decoder_elementwise(model)   # RMSNorm / silu * up / rotary embedding as single kernels; emits int8 activations where INT8 linears follow
-    if world > 1 and args.parallel == "fsdp":
-        from torch.distributed.fsdp import fully_shard
-
+        kw = {"mp_policy": MixedPrecisionPolicy(reduce_dtype=torch.float32)} if reduce_fp32 else {}
         for layer in model.model.layers:   # per decoder layer, then the root (llm_pretrain.py:134-139)
-            fully_shard(layer)
-        fully_shard(model)
+            fully_shard(layer, **kw)
+        fully_shard(model, **kw)
     elif world > 1:
         model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
-    optim = get_optimizer("other_optim.AdamWBF16SR", model, lr=1e-4, weight_decay=0.01)
-    torch.manual_seed(2024 + rank)
-    tokens = torch.randint(0, 32000, (bs, seq + 1), device=dev)
+    optim = get_optimizer("other_optim.AdamWBF16SR", model, lr=1e-4 if data == "fixed" else 3e-4, weight_decay=0.01)
+    gen = torch.Generator().manual_seed(2024 + rank)
+    fixed = torch.randint(0, 32000, (bs, seq + 1), generator=gen).to(dev)
+    losses = []
 
     def step():
+        tokens = fixed if data == "fixed" else _markov_tokens(bs, seq, 1024, gen, dev)   # a 1024-token alphabet of the 32000
         logits = model(input_ids=tokens[:, :-1]).logits.float()
         loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), tokens[:, 1:].reshape(-1))
         loss.backward()
         optim.step()
         optim.zero_grad(set_to_none=True)
+        losses.append(loss.detach())
         return loss
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(warmup, 3)
+    for _ in range(warmup):
         loss = step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         loss = step()
     e1.record()
     torch.cuda.synchronize()
@@ -367,10 +388,11 @@ def run_train(args, rank, local_rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
         dist.barrier()
-    if args.profile and rank == 0:
-        from torch.profiler import ProfilerActivity, profile
+    if profile and rank == 0 and world == 1:
+        from torch.profiler import ProfilerActivity
+        from torch.profiler import profile as torch_profile
 
-        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+        with torch_profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
             for _ in range(2):
                 step()
             torch.cuda.synchronize()
@@ -378,29 +400,45 @@ def run_train(args, rank, local_rank, world):
                 for k in prof.key_averages() if getattr(k, "device_type", None) is not None and "cuda" in str(k.device_type).lower()]
         total = sum(r[2] for r in rows) or 1.0
         rows.sort(key=lambda r: -r[2])
-        with open(args.profile, "w") as f:
-            f.write(f"# {args.workload} layers={shape['num_hidden_layers']} quantize={args.quantize}: device time per kernel over 2 steps "
-                    f"(torch.profiler); step {ms / args.steps:.2f} ms by CUDA events, kernels sum to {total / 2e3:.2f} ms per step\n")
+        with open(profile, "w") as f:
+            f.write(f"# {workload} layers={shape['num_hidden_layers']} quantize={quantize}: device time per kernel over 2 steps "
+                    f"(torch.profiler); step {ms / steps:.2f} ms by CUDA events, kernels sum to {total / 2e3:.2f} ms per step\n")
             f.write("share%  total_us  launches  kernel\n")
             for name, count, us in rows[:60]:
                 f.write(f"{100 * us / total:6.2f} {us:9.0f} {count:9d}  {name[:150]}\n")
+    n_params = sum(p.numel() for p in model.parameters())
+    out = {
+        "metric": "int8_mixed_precision_train_tok_per_s", "value": world * bs * seq * steps / (ms * 1e-3), "unit": "tok/s",
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8" if quantize != "none" else "bf16", "data": "synthetic",
+        "config": {"workload": f"{workload}: Llama-style decoder, {n_params / 1e6:.0f}M params, {shape['num_hidden_layers']} layers, quantize={quantize} "
+                               f"(LM head bf16), AdamWBF16SR, batch {bs} x {seq} tokens per GPU "
+                               f"({'one fixed random batch' if data == 'fixed' else 'a fresh batch of learnable synthetic streams per step'}), "
+                               f"{'eager' if eager_elementwise else 'fused'} element-wise kernels",
+                   "parallelism": (f"fsdp{world}" + (" fp32 reduce-scatter" if reduce_fp32 else "") if (world > 1 and parallel == "fsdp") else f"dp{world}")},
+        "loss": float(loss.detach()), "losses": [round(float(x), 4) for x in losses], "max_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
+    }
+    del model, optim
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_train(args, rank, local_rank, world):
+    """`--workload train-*`: see train_measure."""
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    line = train_measure(args.workload, args.quantize, args.parallel, args.steps, args.warmup, rank, local_rank, world, layers=args.layers,
+                         eager_elementwise=args.eager_elementwise, data=args.train_data, profile=args.profile, reduce_fp32=args.reduce_fp32)
     if rank == 0:
-        n_params = sum(p.numel() for p in model.parameters())
-        print(json.dumps({
-            "metric": "int8_mixed_precision_train_tok_per_s", "value": world * bs * seq * args.steps / (ms * 1e-3), "unit": "tok/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: Llama-style decoder, {n_params / 1e6:.0f}M params, quantize={args.quantize} "
-                                   f"(LM head bf16), AdamWBF16SR, batch {bs} x {seq} random tokens per GPU, "
-                                   f"{'eager' if args.eager_elementwise else 'fused'} element-wise kernels",
-                       "parallelism": (f"fsdp{world}" if (world > 1 and args.parallel == "fsdp") else f"dp{world}")},
-            "loss": float(loss.detach()), "max_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
-        }), flush=True)
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def _time_graph(launch, n_sets: int, launches: int, reps: int = 5, graph: bool = True) -> float:
+def _time_graph(launch, n_sets: int, launches: int, reps: int = 5, graph: bool = True, lead_in_s: float = 0.0) -> float:
     """Milliseconds per launch of `launch(i)` (i = which buffer set), measured over a CUDA graph of
     `launches` back-to-back launches that rotate through `n_sets` buffer sets. The sets together are several
     times larger than L2, so every launch reads its input from HBM and the dirty lines it displaces are a
@@ -423,6 +461,14 @@ def _time_graph(launch, n_sets: int, launches: int, reps: int = 5, graph: bool =
             launch(i % n_sets)
     g.replay()
     torch.cuda.synchronize()
+    if lead_in_s > 0.0:
+        # untimed replays first, so that every case is timed in the same loaded (power-capped) state instead of
+        # whatever state the previous case left behind
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < lead_in_s:
+            for _ in range(4):
+                g.replay()
+            torch.cuda.synchronize()
     times = []
     for _ in range(reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -589,16 +635,17 @@ def run_sweep(args):
             for name, fn, lib_fn, lib_name in cases:
                 if args.only and not args.only.isdigit() and args.only not in name:
                     continue
-                ms = _time_graph(fn, n_sets, launches)
+                ms = _time_graph(fn, n_sets, launches, lead_in_s=args.lead_in_seconds)
                 tops = 2.0 * M * N * K / (ms * 1e-3) / 1e12
                 line = {"metric": "gemm_tops", "kernel": name, "layout": lname, "size": S, "value": round(tops, 1), "unit": "TOPS",
                         "us_per_launch": round(ms * 1e3, 2), "frac_of_2x_measured_bf16": round(tops / peak, 3),
                         "frac_of_nominal_4500": round(tops / NOMINAL_INT8_DENSE_TOPS, 3), "peak": peak, "peak_is": f"2 x {peak_kind} dense bf16 burst",
                         "n_gpus": 1, "steps": launches, "higher_is_better": True, "data": "synthetic",
-                        "config": {"workload": f"{name} {lname} M=N=K={S}", "l2": f"{n_sets} operand sets in rotation, CUDA-graph replays"}}
+                        "config": {"workload": f"{name} {lname} M=N=K={S}", "l2": f"{n_sets} operand sets in rotation, CUDA-graph replays",
+                                   "lead_in_seconds": args.lead_in_seconds}}
                 if lib_fn is not None:
                     try:
-                        lms = _time_graph(lib_fn, n_sets, launches)
+                        lms = _time_graph(lib_fn, n_sets, launches, lead_in_s=args.lead_in_seconds)
                         line["library"] = {"what": lib_name, "tops": round(2.0 * M * N * K / (lms * 1e-3) / 1e12, 1), "us_per_launch": round(lms * 1e3, 2)}
                     except Exception as exc:   # a layout or shape the library refuses
                         line["library"] = {"what": lib_name, "unavailable": f"{type(exc).__name__}: {str(exc)[:120]}"}
@@ -931,6 +978,21 @@ def main():
     e2e_ms = statistics.median(e2e_regions)
     clocks = sampler.stop() if rank == 0 else None
 
+    # The metric's second half on the same ranks: INT8 mixed-precision training throughput of the 1.1B decoder
+    # (FSDP2 with the INT8 weight all-gather when there are several ranks). A failure here must not lose the line.
+    train_obj = None
+    if not args.no_train_line and (gM, gN, gK) == (8192, 8192, 8192):
+        try:
+            del a_bufs, w_bufs, keep, wq_full, ws_full
+            sym = None
+            gc.collect()
+            torch.cuda.empty_cache()
+            _native.check(_native.load().qt_set_gemm_sm_margin(0))
+            t = train_measure("train-1b", "mixed_precision", "fsdp", 3, 3, rank, local_rank, world)
+            train_obj = {k: t[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "loss", "max_memory_gb", "config")}
+        except Exception as exc:   # noqa: BLE001
+            train_obj = {"error": f"{type(exc).__name__}: {str(exc)[:300]}"}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -990,6 +1052,8 @@ def main():
     }
     if cpu_baseline is not None:
         line["cpu_baseline"] = cpu_baseline
+    if train_obj is not None:
+        line["train"] = train_obj
     if world == 1 and not args.no_quantize_lines:
         # the HBM-bound kernels of the path, each against the measured copy bandwidth (same entries as --workload quantize)
         del A, W, out

@@ -232,6 +232,18 @@ int qt_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const v
                  int64_t K, void* stream);
 
 /*
+ * C = bf16( bf16(A @ B^T) * col_scale[n] ) for bf16 A [M, K] (row pitch lda) and B [N, K] (row pitch ldb), bf16
+ * col_scale [N], bf16 C: a bf16 matmul (fp32 accumulate on tcgen05 kind::f16, rounded to bf16) followed by
+ * the bf16 multiply with a per-column scale, fused into the epilogue with both roundings kept. K, lda and ldb
+ * multiples of 8.
+ * replaces: the INT8 weight-only forward `(input @ weight.int_data.T.to(input.dtype)) * weight.scale.T`
+ * (subclasses/int8.py:147) once the int8 weight has been widened to bf16 (exact): the reference runs it as a
+ * bf16 cuBLAS matmul plus an element-wise multiply over the output.
+ */
+int qt_bf16_mm_colscale(const void* a, int64_t lda, const void* b, int64_t ldb, const void* col_scale, void* c,
+                        int64_t ldc, int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
  * Split-K forms. When the output is small and the reduction long (the grad-weight GEMMs: a
  * [hidden, hidden] result reduced over tens of thousands of tokens) there are too few output tiles
  * to occupy the GPU; given a workspace, these variants let several CTA pairs share one tile, each

@@ -91,6 +91,52 @@ __global__ void __launch_bounds__(kThreads) ternary_kernel(const XT* __restrict_
     }
 }
 
+// The same quantization for bf16 weights without a division per element. clip(round_half_even(w / d), -1, 1)
+// is sign(w) when fl(|w| / d) > 0.5 and 0 otherwise, and fl(|w| / d) > 0.5 exactly when |w| > d / 2: d / 2 is
+// exact, the next float above it already divides to more than 0.5 + 2^-25 (which rounds up), and rounding is
+// monotonic. A bf16 |w| exceeds the fp32 value d / 2 exactly when its 15 magnitude bits exceed the upper 16
+// bits of d / 2, so one packed bf16 comparison per two weights decides everything. Requires d >= 2^-100.
+// A thread takes 16 weights (two 16-byte loads) and writes 4 packed bytes, or 16 int8 values.
+__global__ void __launch_bounds__(kThreads) ternary_bf16_kernel(const __nv_bfloat16* __restrict__ w, int64_t n, const float* __restrict__ scale,
+                                                                 float eps, int8_t* __restrict__ out, int pack) {
+    const float half_d = 0.5f * fmaxf(scale[0], eps);
+    const uint32_t t16 = __float_as_uint(half_d) >> 16;
+    const uint32_t thr = t16 | (t16 << 16);
+    const __nv_bfloat162 thr2 = *reinterpret_cast<const __nv_bfloat162*>(&thr);
+    const int64_t n16 = n / 16;
+    for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < n16; v += (int64_t)gridDim.x * kThreads) {
+        const uint4 a = reinterpret_cast<const uint4*>(w)[2 * v], b = reinterpret_cast<const uint4*>(w)[2 * v + 1];
+        const uint32_t words[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        uint32_t code[8];   // per word: 2-bit code (0, 1 = +1, 3 = -1) of the low half in bits 0-1, of the high half in bits 16-17
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t mag = words[k] & 0x7FFF7FFFu;
+            const uint32_t nz = __hgt2_mask(*reinterpret_cast<const __nv_bfloat162*>(&mag), thr2);
+            code[k] = nz & (((words[k] >> 14) & 0x00020002u) | 0x00010001u);
+        }
+        if (pack) {
+            uint32_t bytes = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {   // byte j holds weights 4j .. 4j+3, the first in the top bits
+                const uint32_t c0 = code[2 * j], c1 = code[2 * j + 1];
+                const uint32_t byte = (((c0 << 6) | (c0 >> 12)) & 0xF0u) | (((c1 << 2) | (c1 >> 16)) & 0x0Fu);
+                bytes |= byte << (8 * j);
+            }
+            reinterpret_cast<uint32_t*>(out)[v] = bytes;
+        } else {
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // 2-bit two's complement -> int8: 0 -> 0x00, 1 -> 0x01, 3 -> 0xFF
+                const uint32_t c0 = code[2 * j], c1 = code[2 * j + 1];
+                const uint32_t e0 = c0 & 3u, e1 = (c0 >> 16) & 3u, e2 = c1 & 3u, e3 = (c1 >> 16) & 3u;
+                o[j] = ((e0 ^ 2u) - 2u & 0xFFu) | (((e1 ^ 2u) - 2u & 0xFFu) << 8) | (((e2 ^ 2u) - 2u & 0xFFu) << 16) | (((e3 ^ 2u) - 2u & 0xFFu) << 24);
+            }
+            reinterpret_cast<uint4*>(out)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) unpack_i2_kernel(const int8_t* __restrict__ packed, int64_t n_packed, int8_t* __restrict__ out) {
     for (int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x; q < n_packed; q += (int64_t)gridDim.x * kThreads) {
         const int b = (int)packed[q];  // sign-extended
@@ -145,6 +191,19 @@ extern "C" int qt_bitnet_quantize_weight(const void* w, int w_dtype, int64_t num
     QT_REQUIRE(!pack_2bit || numel % 4 == 0, "bitnet_quantize_weight: packing needs a multiple of 4 elements");
     QT_REQUIRE(aligned_to(out, 4), "bitnet_quantize_weight: output must be 4-byte aligned");
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (w_dtype == QT_BF16 && aligned_to(w, 16) && aligned_to(out, 16) && numel >= 16 && eps >= 1e-30f) {
+        // whole groups of 16 weights by the comparison kernel, the ragged tail (fewer than 16) by the dividing one
+        const int64_t body = numel / 16 * 16;
+        ternary_bf16_kernel<<<grid_for(body / 16), kThreads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(w), body, scale, eps,
+                                                                        reinterpret_cast<int8_t*>(out), pack_2bit);
+        QT_CUDA_CHECK(cudaGetLastError());
+        if (body == numel) return QT_OK;
+        const int64_t rest = numel - body;
+        ternary_kernel<__nv_bfloat16><<<1, kThreads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(w) + body, rest, scale, eps,
+                                                                  reinterpret_cast<int8_t*>(out) + (pack_2bit ? body / 4 : body), pack_2bit);
+        QT_CUDA_CHECK(cudaGetLastError());
+        return QT_OK;
+    }
     const int grid = grid_for(numel / 4 + 1);
     if (w_dtype == QT_BF16) ternary_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(w), numel, scale, eps, reinterpret_cast<int8_t*>(out), pack_2bit);
     else ternary_kernel<float><<<grid, kThreads, 0, stream>>>(reinterpret_cast<const float*>(w), numel, scale, eps, reinterpret_cast<int8_t*>(out), pack_2bit);

@@ -83,6 +83,7 @@ struct GemmParams {
     const void* scale_b;
     int scale_b_is_scalar;
     int col_scale_first;   // epilogue (acc * col_scale) * row_scale instead of (acc * row_scale) * col_scale
+    int round_acc_first;   // the accumulator is rounded to bf16 before it is scaled (a bf16 matmul followed by a bf16 multiply)
     int scale_dtype;  // QT_BF16 | QT_F32 ; also the output dtype of scaled epilogues
     // tile-scaled only
     int64_t sa_s0, sa_s1, sb_s0, sb_s1;
@@ -332,7 +333,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         bool next_cs_packed = false;
         auto request_scales = [&](const WorkItem& w) {
             const int64_t r = (int64_t)w.m * (BM * CG) + (int64_t)cta_rank * BM + ew * 32 + lane;
-            next_row_scale = (r < p.M) ? load_scale(p.scale_a, p.scale_dtype, r) : 0.0f;
+            next_row_scale = (r < p.M) ? (p.scale_a ? load_scale(p.scale_a, p.scale_dtype, r) : 1.0f) : 0.0f;
             next_cs_packed = load_col_scales8(next_cs, p, (int64_t)w.n * BN + lane * 8);
         };
         uint32_t work = first_tile + (uint32_t)grp * tile_step;
@@ -434,8 +435,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         const float2 rs2 = make_float2(row_scale, row_scale);
 #pragma unroll
                         for (int j = 0; j < 8; j += 2) {
-                            const float a0 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j] : __uint_as_float(r[g * 8 + j]);
-                            const float a1 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j + 1] : __uint_as_float(r[g * 8 + j + 1]);
+                            float a0 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j] : __uint_as_float(r[g * 8 + j]);
+                            float a1 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j + 1] : __uint_as_float(r[g * 8 + j + 1]);
+                            if constexpr (KIND == 2) {
+                                if (p.round_acc_first) {
+                                    const uint32_t rb = pack_bf16x2(a0, a1);
+                                    a0 = __uint_as_float(rb << 16);
+                                    a1 = __uint_as_float(rb & 0xFFFF0000u);
+                                }
+                            }
                             // fp32 multiplication is not associative: the order is the caller's (a product
                             // computed in transposed form keeps the rounding of the untransposed one)
                             const float2 t = p.col_scale_first ? __fmul2_rn(__fmul2_rn(make_float2(a0, a1), make_float2(cs[j], cs[j + 1])), rs2)
@@ -633,7 +641,8 @@ __global__ void __launch_bounds__(256) splitk_finish_kernel(const GemmParams p) 
         if constexpr (EPI == EPI_RAW) {
             reinterpret_cast<uint32_t*>(p.c)[row * p.ldc + col] = (KIND == 0) ? (uint32_t)isum : __float_as_uint(v);
         } else {
-            const float rs = load_scale(p.scale_a, p.scale_dtype, row);
+            const float rs = p.scale_a ? load_scale(p.scale_a, p.scale_dtype, row) : 1.0f;
+            if (KIND == 2 && p.round_acc_first) v = __bfloat162float(__float2bfloat16_rn(v));
             const float cs = load_scale(p.scale_b, p.scale_dtype, p.scale_b_is_scalar ? 0 : col);
             const float o = p.col_scale_first ? __fmul_rn(__fmul_rn(v, cs), rs) : __fmul_rn(__fmul_rn(v, rs), cs);
             if (p.scale_dtype == QT_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[row * p.ldc + col] = __float2bfloat16_rn(o);
@@ -683,12 +692,21 @@ int pick_cta_group(int64_t M, int64_t K) {
 int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype, int64_t b_sk,
                   int64_t b_sn, GemmParams p, void* workspace, int64_t workspace_bytes, void* stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const bool is_bf16 = a_dtype == QT_BF16 && b_dtype == QT_BF16;
+    if (is_bf16) {
+        // 16-bit operands ride the same pipeline measured in bytes: a K-major tile is [rows][128 B of K] whatever
+        // the element size, and one kind::f16 instruction consumes 32 reduction bytes like kind::i8. Only the
+        // K-major layouts (A@B.T) are wired up; strides arrive in elements and turn into bytes here.
+        QT_REQUIRE(a_sk == 1 && b_sk == 1, "gemm: bf16 operands must both be K-major (A [M,K] and B^T [N,K] with unit inner stride)");
+        QT_REQUIRE(p.K < (1ll << 30), "gemm: dimension exceeds 2^30");
+        p.K *= 2; a_sm *= 2; b_sn *= 2;
+    }
     const int64_t M = p.M, N = p.N, K = p.K;
     QT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative dimension");
     QT_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "gemm: dimension exceeds 2^31");
     const bool is_i8 = a_dtype == QT_I8 && b_dtype == QT_I8;
     const bool is_f8 = (a_dtype == QT_E4M3 || a_dtype == QT_E5M2) && (b_dtype == QT_E4M3 || b_dtype == QT_E5M2);
-    QT_REQUIRE(is_i8 || is_f8, "gemm: operands must both be int8 or both be fp8 (got %d, %d)", a_dtype, b_dtype);
+    QT_REQUIRE(is_i8 || is_f8 || is_bf16, "gemm: operands must both be int8, both fp8 or both bf16 (got %d, %d)", a_dtype, b_dtype);
     if (M == 0 || N == 0) return QT_OK;
     QT_REQUIRE(a && b && p.c, "gemm: null operand");
     QT_REQUIRE(K > 0, "gemm: K must be positive (zero-length reductions are handled by the caller)");
@@ -742,8 +760,10 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
 
     const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + BN - 1) / BN) * p.splits;  // work items
     QT_REQUIRE(tiles < (1ll << 30), "gemm: %lld work items exceed the kernel's 32-bit tile index", (long long)tiles);
+    // kind::f16 operand formats: 0 = f16, 1 = bf16
     const uint32_t idesc = is_i8 ? make_idesc(2, 1, 1, a_mn, b_mn, BM * cg, BN)
-                                 : make_idesc(1, fp8_format(a_dtype), fp8_format(b_dtype), a_mn, b_mn, BM * cg, BN);
+                           : is_bf16 ? make_idesc(1, 1, 1, false, false, BM * cg, BN)
+                                     : make_idesc(1, fp8_format(a_dtype), fp8_format(b_dtype), a_mn, b_mn, BM * cg, BN);
 #define QT_DISPATCH(KIND, EPI)                                                                               \
     do {                                                                                                     \
         const int rc_ = cg == 2 ? launch_layout<KIND, EPI, 2>(a_mn, b_mn, ta, tb, tc, p, idesc, tiles, stream)   \
@@ -754,6 +774,13 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
     if (is_i8) {
         if (epi == EPI_RAW) { QT_DISPATCH(0, EPI_RAW); }
         if (epi == EPI_ROWCOL) { QT_DISPATCH(0, EPI_ROWCOL); }
+    } else if (is_bf16) {
+        if (epi == EPI_ROWCOL) {
+            const int rc_ = cg == 2 ? launch_one<2, EPI_ROWCOL, false, false, 2>(ta, tb, tc, p, idesc, tiles, stream)
+                                    : launch_one<2, EPI_ROWCOL, false, false, 1>(ta, tb, tc, p, idesc, tiles, stream);
+            if (rc_ != QT_OK || p.splits == 1) return rc_;
+            return launch_finish<2, EPI_ROWCOL>(p, stream);
+        }
     } else {
         if (epi == EPI_ROWCOL) { QT_DISPATCH(1, EPI_ROWCOL); }
     }
@@ -847,6 +874,19 @@ extern "C" int qt_scaled_mm_ws(const void* a, int a_dtype, int64_t a_sm, int64_t
     p.scale_a = scale_a; p.scale_b = scale_b; p.scale_b_is_scalar = scale_b_is_scalar & 1; p.col_scale_first = (scale_b_is_scalar >> 1) & 1;
     p.scale_dtype = scale_dtype;
     return gemm_dispatch(EPI_ROWCOL, a, a_dtype, a_sm, a_sk, b, b_dtype, b_sk, b_sn, p, workspace, workspace_bytes, stream);
+}
+
+extern "C" int qt_bf16_mm_colscale(const void* a, int64_t lda, const void* b, int64_t ldb, const void* col_scale, void* c, int64_t ldc,
+                                   int64_t M, int64_t N, int64_t K, void* stream) {
+    QT_REQUIRE(col_scale || M == 0 || N == 0, "bf16_mm_colscale: null scale pointer");
+    QT_REQUIRE(lda >= K && ldb >= K, "bf16_mm_colscale: leading dimension smaller than K");
+    if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0)
+        return fail(QT_ERR_UNSUPPORTED, "bf16_mm_colscale: K and the leading dimensions must be multiples of 8 (16-byte rows)");
+    GemmParams p = {};
+    p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc;
+    p.scale_a = nullptr; p.scale_b = col_scale; p.scale_b_is_scalar = 0; p.col_scale_first = 0; p.round_acc_first = 1;
+    p.scale_dtype = QT_BF16;
+    return gemm_dispatch(EPI_ROWCOL, a, QT_BF16, lda, 1, b, QT_BF16, 1, ldb, p, nullptr, 0, stream);
 }
 
 extern "C" int qt_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, const void* b, int b_dtype, int64_t b_sk,

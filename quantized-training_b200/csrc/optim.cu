@@ -25,6 +25,7 @@ struct AdamParams {
     float lr_wd, lr, w1, w2, bc1, sqrt_bc2, eps;
     int stochastic;
     uint64_t seed, offset;
+    PhiloxKeys keys;   // round keys of `seed`
     int vec;  // p and g are 16-byte, m and v 8-byte aligned: four elements move as one vector
 };
 
@@ -62,7 +63,7 @@ __device__ __forceinline__ void adam_quad(const AdamParams& a, int64_t q) {
     {
         const int64_t i0 = q * 4;
         Philox4 r = {0, 0, 0, 0};
-        if (a.stochastic) r = philox4x32_10((uint64_t)q, a.offset, a.seed);
+        if (a.stochastic) r = philox4x32_10((uint64_t)q, a.offset, a.keys);
         const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
         if (a.vec && i0 + 4 <= a.n) {
             float pv[4], gv[4], mv[4], vv[4];
@@ -201,7 +202,7 @@ extern "C" int qt_adamw_bf16_sr(void* p, int p_dtype, const void* grad, int grad
     // lerp weights: the Python doubles (1 - beta) rounded to fp32, as ATen does for an fp32 tensor
     a.w1 = (float)(1.0 - beta1); a.w2 = (float)(1.0 - beta2);
     a.bc1 = bias_correction1; a.sqrt_bc2 = sqrt_bias_correction2; a.eps = eps;
-    a.stochastic = stochastic; a.seed = seed; a.offset = offset;
+    a.stochastic = stochastic; a.seed = seed; a.offset = offset; a.keys = philox_keys(seed);
     a.vec = aligned_to(p, 16) && aligned_to(grad, 16) && aligned_to(exp_avg, 8) && aligned_to(exp_avg_sq, 8);
     const int64_t want = ((numel + 3) / 4 + kThreads - 1) / kThreads;
     const int64_t cap = (int64_t)num_sms() * 16;
@@ -230,7 +231,7 @@ extern "C" int qt_adamw_bf16_sr_multi(int n_tensors, void* const* p, const void*
     a.lr = lr; a.lr_wd = lr * weight_decay;
     a.w1 = (float)(1.0 - beta1); a.w2 = (float)(1.0 - beta2);
     a.bc1 = bias_correction1; a.sqrt_bc2 = sqrt_bias_correction2; a.eps = eps;
-    a.stochastic = stochastic; a.seed = seed; a.offset = offset;
+    a.stochastic = stochastic; a.seed = seed; a.offset = offset; a.keys = philox_keys(seed);
 
     MultiTable tab;
     tab.n = 0;

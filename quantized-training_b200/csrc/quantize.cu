@@ -653,11 +653,13 @@ __device__ __forceinline__ uint32_t silu_mul_word(uint32_t g, uint32_t u) {
 // row); 2 = silu(x) * x2 (also writes y). The producer forms fold the activation quantize of the INT8
 // linear layers into the kernel that produces the activation, so the activation is not read again.
 template <int TPR, int VPT, bool COLABS, bool SR, bool TILE = false, int PRODUCER = 0>
-__global__ void __launch_bounds__(kThreads, (PRODUCER != 0 ? (VPT <= 4 ? 2 : 1) : (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1))))
+__global__ void __launch_bounds__(kThreads, (PRODUCER != 0 ? (VPT <= 4 ? 2 : 1) : (VPT <= 4 ? ((SR || COLABS) ? 3 : 4) : (VPT <= 8 ? 2 : 1))))
 rowwise_full_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;
     constexpr int WPR = TPR / 32;
-    constexpr bool PREFETCH = VPT <= 8 && !COLABS && PRODUCER != 2 && (PRODUCER == 0 || VPT <= 4);
+    // the register double buffer: always for plain rows of up to 8 vectors per thread; with the column maxima
+    // (which take VPT * 4 registers of their own) for up to 4; the producer forms spend theirs on operands
+    constexpr bool PREFETCH = PRODUCER == 0 ? (COLABS ? VPT <= 4 : VPT <= 8) : (PRODUCER == 1 && !COLABS && VPT <= 4);
     static_assert(!TILE || (VPT % 2 == 0 && !COLABS && !SR), "tile form: vector pairs, no column maxima, round-to-nearest");
     static_assert(PRODUCER == 0 || (!TILE && !SR), "producer forms: whole rows, round-to-nearest");
     __shared__ uint32_t s_red[2][kThreads / 32];
@@ -899,7 +901,7 @@ constexpr int kClusterSize = 2;
 template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0, bool SCATTER = false>
 int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
     constexpr int RPC = kThreads / TPR;
-    constexpr int CTAS_PER_SM = (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1));
+    constexpr int CTAS_PER_SM = (VPT <= 4 ? ((SR || COLABS) ? 3 : 4) : (VPT <= 8 ? 2 : 1));
     const int64_t want = (p.rows + RPC - 1) / RPC;
     const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
     int64_t grid = want < cap ? want : cap;

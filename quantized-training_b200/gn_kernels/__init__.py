@@ -3,7 +3,7 @@
 Ops of the hot path keep the reference's names and signatures (kernels/gn_kernels/__init__.py:1-25).
 Ops outside it (int4, fp4, conv2d, MX/NVFP4 utilities) raise NotImplementedError.
 """
-from .mm import int8_mm, scaled_mm, scaled_mm_t
+from .mm import bf16_mm_colscale, bf16_mm_colscale_supported, int8_mm, scaled_mm, scaled_mm_t
 from .quantize import (
     col_absmax,
     int8_weight_update_,

@@ -52,6 +52,7 @@ SIGNATURES = {
                            c_int64, c_void_p]),
     "qt_scaled_mm": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
                              c_int, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "qt_bf16_mm_colscale": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "qt_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "qt_int8_mm_ws": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
                               c_int64, c_void_p, c_int64, c_void_p]),

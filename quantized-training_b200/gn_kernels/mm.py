@@ -184,3 +184,27 @@ def _tile_scaled_mm_cuda(A: Tensor, B: Tensor, scale_A: Tensor, scale_B: Tensor)
             nv.stream_ptr(dev)))
         nv.raise_if_device_failed()
     return C
+
+
+def bf16_mm_colscale_supported(x2d: Tensor, w: Tensor, scale: Tensor) -> bool:
+    return (x2d.is_cuda and x2d.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and scale.dtype is torch.bfloat16
+            and x2d.ndim == 2 and w.ndim == 2 and x2d.shape[1] == w.shape[1] and scale.numel() == w.shape[0]
+            and x2d.shape[1] % 8 == 0 and x2d.stride(1) == 1 and w.stride(1) == 1 and x2d.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x2d.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and x2d.shape[0] > 0 and w.shape[0] > 0
+            and not torch.compiler.is_compiling())
+
+
+def bf16_mm_colscale(x2d: Tensor, w: Tensor, scale: Tensor) -> Tensor:
+    """bf16(bf16(x2d @ w.T) * scale[None, :]) in one kernel: x2d [M, K], w [N, K], scale [N] (all bf16). The
+    INT8 weight-only forward of the reference (subclasses/int8.py:147) with the per-channel multiply folded
+    into the GEMM epilogue; both bf16 roundings of the two-step form are kept."""
+    dev = nv.require_cuda(x2d, w, scale)
+    M, K = x2d.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    scale = scale.reshape(-1).contiguous()
+    with nv.on_device(dev):
+        nv.check(nv.load().qt_bf16_mm_colscale(x2d.data_ptr(), x2d.stride(0), w.data_ptr(), w.stride(0), scale.data_ptr(), out.data_ptr(),
+                                               N, M, N, K, nv.stream_ptr(dev)))
+        nv.raise_if_device_failed()
+    return out

@@ -252,8 +252,15 @@ class _Int8Linear(torch.autograd.Function):
         ctx.bias = bias is not None
 
         if weight.config.activation == "none":
-            # weight-only: bf16 GEMM on the up-cast int8 weight, then the per-output-row scale
-            out = (input @ weight.int_data.T.to(input.dtype)) * weight.scale.T
+            # weight-only: bf16 GEMM on the up-cast int8 weight, then the per-output-row scale -- as one
+            # tcgen05 GEMM whose epilogue applies the scale (both bf16 roundings kept) where the shapes allow
+            x2d = input.reshape(-1, weight.shape[1])
+            w_bf16 = weight.int_data.to(input.dtype)            # exact: every int8 value is a bf16 value
+            scale = weight.scale.reshape(-1)
+            if gn_kernels.bf16_mm_colscale_supported(x2d, w_bf16, scale):
+                out = gn_kernels.bf16_mm_colscale(x2d, w_bf16, scale).view(*input.shape[:-1], weight.shape[0])
+            else:
+                out = (input @ w_bf16.T) * weight.scale.T
         else:
             # dynamic activation quantization + INT8 tensor cores
             batch_dims = input.shape[:-1]

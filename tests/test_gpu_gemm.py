@@ -383,3 +383,30 @@ def test_outputs_stay_inside_their_buffers():
     np.testing.assert_array_equal(q.cpu().numpy(), oq)
     oqt, _ = om.quantize_colwise_t(values_of(x))
     np.testing.assert_array_equal(qt.cpu().numpy(), oqt)
+
+
+@pytest.mark.parametrize("mnk", [(256, 512, 256), (1024, 1536, 1024), (300, 200, 264), (16448, 1536, 1536), (128, 256, 4096)])
+def test_bf16_mm_with_column_scale_epilogue(mnk, cta_group):
+    """The INT8 weight-only forward (reference: subclasses/int8.py:147): a bf16 matmul on the widened int8 weight,
+    then a bf16 multiply by the per-channel scale, as one tcgen05 GEMM. Against the two-step form evaluated in
+    fp32 with both roundings: identical up to the fp32 summation order (1e-2 relative, most elements equal)."""
+    M, N, K = mnk
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w_i8 = torch.randint(-127, 128, (N, K), dtype=torch.int8, generator=g).cuda()
+    scale = (torch.rand(N, generator=g) / 64 + 1e-3).bfloat16().cuda()
+    w = w_i8.to(torch.bfloat16)
+    assert gn_kernels.bf16_mm_colscale_supported(x, w, scale)
+    out = gn_kernels.bf16_mm_colscale(x, w, scale)
+    ref = ((x.float() @ w.float().T).bfloat16().float() * scale.float()).bfloat16()
+    eager = (x @ w.T) * scale
+    # A different fp32 summation order can move the first rounding by one bf16 step, which the second rounding
+    # can turn into two (2^-6 relative at most); that happens to a handful of elements per million. The
+    # north-star tolerance of 1e-2 relative holds for all but those, and the mean error is far below it.
+    floor = 1e-4 * ref.float().abs().max().item()
+    for other in (ref, eager):
+        torch.testing.assert_close(out.float(), other.float(), rtol=2.0 ** -6, atol=floor)
+        rel = (out.float() - other.float()).abs() / (other.float().abs() + floor)
+        assert (rel > 1e-2).float().mean().item() < 1e-5
+    assert (out == ref).float().mean().item() > 0.97
+    assert nv.device_status() == 0

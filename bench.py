@@ -51,7 +51,7 @@ def parse_args():
                     help="a non-square problem for the gemm workload (profiling the layer shapes; the headline is --size 8192)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-quantize-lines", action="store_true", help="leave the quantize kernels' roofline entries out of the N=1 line")
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "quantize", "sweep", "train-470m", "train-1b"],
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "quantize", "sweep", "train-470m", "train-1b", "vit-g"],
                     help="gemm: the headline quantize + scaled GEMM step; train-*: one INT8 mixed-precision Llama step (tok/s)")
     ap.add_argument("--parallel", default="fsdp", choices=["ddp", "fsdp"], help="train-* workloads with --gpus > 1: DDP, or FSDP2 with the INT8 weight all-gather")
     ap.add_argument("--quantize", default="mixed_precision", choices=["mixed_precision", "none", "int8_quantized_training", "bitnet"],
@@ -438,6 +438,121 @@ def run_train(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+VIT_G14 = dict(dim=1536, depth=40, heads=24, mlp=6144, image=224, patch=14, classes=45)
+
+
+def _build_vit(cfg: dict, dev):
+    """ViT-giant/14 as the reference fine-tunes it (timm_finetune.py:136-139 creates timm's
+    vit_giant_patch14_224 with 45 classes): patch embedding, class token, learned positions, pre-norm blocks
+    (LayerNorm, fused-QKV attention, GELU MLP), final norm, linear head. Random init: the pretrained
+    checkpoint and the dataset are not available offline."""
+    nn = torch.nn
+
+    class Block(nn.Module):
+        def __init__(self, dim, heads, mlp):
+            super().__init__()
+            self.norm1, self.norm2 = nn.LayerNorm(dim, eps=1e-6), nn.LayerNorm(dim, eps=1e-6)
+            self.qkv, self.proj = nn.Linear(dim, 3 * dim), nn.Linear(dim, dim)
+            self.fc1, self.fc2 = nn.Linear(dim, mlp), nn.Linear(mlp, dim)
+            self.heads = heads
+
+        def forward(self, x):
+            b, n, d = x.shape
+            qkv = self.qkv(self.norm1(x)).view(b, n, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4)
+            a = torch.nn.functional.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
+            x = x + self.proj(a.transpose(1, 2).reshape(b, n, d))
+            return x + self.fc2(torch.nn.functional.gelu(self.fc1(self.norm2(x))))
+
+    class ViT(nn.Module):
+        def __init__(self, dim, depth, heads, mlp, image, patch, classes):
+            super().__init__()
+            self.patch = patch
+            n = (image // patch) ** 2
+            self.embed = nn.Linear(3 * patch * patch, dim)
+            self.cls = nn.Parameter(torch.zeros(1, 1, dim))
+            self.pos = nn.Parameter(torch.randn(1, n + 1, dim) * 0.02)
+            self.blocks = nn.ModuleList(Block(dim, heads, mlp) for _ in range(depth))
+            self.norm = nn.LayerNorm(dim, eps=1e-6)
+            self.head = nn.Linear(dim, classes)
+
+        def forward(self, img):
+            b, c, h, w = img.shape
+            p = self.patch
+            x = img.view(b, c, h // p, p, w // p, p).permute(0, 2, 4, 1, 3, 5).reshape(b, (h // p) * (w // p), c * p * p)
+            x = torch.cat((self.cls.expand(b, -1, -1), self.embed(x)), dim=1) + self.pos
+            for blk in self.blocks:
+                x = blk(x)
+            return self.head(self.norm(x)[:, 0])
+
+    with torch.device(dev):
+        return ViT(**cfg).bfloat16()
+
+
+def run_vit(args, rank, local_rank, world):
+    """`--workload vit-g`: one training step of ViT-giant/14 (dim 1536, 40 layers, 24 heads, MLP 6144, 224x224,
+    patch 14, 45 classes), batch 64 random images per GPU, with the INT8 weight-only subclass
+    (int8 row-scaled weights, stochastic-rounding update; --quantize int8_quantized_training), the BitNet b1.58
+    variant (--quantize bitnet) or bf16 (--quantize none); DDP over the ranks. Images per second."""
+    from train_utils import quantize_model
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = dict(VIT_G14)
+    if args.layers is not None:
+        cfg["depth"] = args.layers
+    torch.manual_seed(2024)
+    model = _build_vit(cfg, dev)
+    quantize = None if args.quantize == "none" else args.quantize
+    quantize_model(model.blocks, quantize)      # the transformer blocks; patch embedding and head stay bf16
+    n_params = sum(p.numel() for p in model.parameters())
+    if world > 1:
+        model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
+    optim = torch.optim.AdamW(model.parameters(), lr=1e-5, weight_decay=0.01)
+    bs = 64
+    gen = torch.Generator().manual_seed(2024 + rank)
+    images = torch.randn(bs, 3, cfg["image"], cfg["image"], generator=gen).bfloat16().to(dev)
+    labels = torch.randint(0, cfg["classes"], (bs,), generator=gen).to(dev)
+
+    def step():
+        loss = torch.nn.functional.cross_entropy(model(images).float(), labels)
+        loss.backward()
+        optim.step()
+        optim.zero_grad(set_to_none=True)
+        return loss
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        loss = step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({
+            "metric": "vit_train_images_per_s", "value": world * bs * args.steps / (ms * 1e-3), "unit": "img/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8" if quantize else "bf16", "data": "synthetic",
+            "config": {"workload": f"ViT-giant/14, {n_params / 1e6:.0f}M params, {cfg['depth']} layers, quantize={args.quantize}, torch AdamW, "
+                                   f"batch {bs} x 3 x {cfg['image']} x {cfg['image']} random images per GPU, random labels",
+                       "parallelism": f"dp{world}"},
+            "loss": float(loss.detach()), "max_memory_gb": torch.cuda.max_memory_allocated() / 1e9}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def _time_graph(launch, n_sets: int, launches: int, reps: int = 5, graph: bool = True, lead_in_s: float = 0.0) -> float:
     """Milliseconds per launch of `launch(i)` (i = which buffer set), measured over a CUDA graph of
     `launches` back-to-back launches that rotate through `n_sets` buffer sets. The sets together are several
@@ -688,6 +803,9 @@ def main():
     if args.workload == "sweep":
         if rank == 0:
             run_sweep(args)
+        return
+    if args.workload == "vit-g":
+        run_vit(args, rank, local_rank, world)
         return
     if args.workload != "gemm":
         run_train(args, rank, local_rank, world)

@@ -91,7 +91,17 @@ def _local(t: Tensor) -> Tensor:
     to_local = getattr(t, "to_local", None)
     t = to_local() if callable(to_local) else t
     inner = getattr(t, "_data", None)  # wrapper subclasses over a plain bf16 tensor
-    return inner if isinstance(inner, Tensor) else t
+    if isinstance(inner, Tensor):
+        return inner
+    if type(t) is not Tensor and type(t) is not torch.nn.Parameter and t.data_ptr() == 0:
+        # e.g. an INT8 weight-only parameter (subclasses.Int8LinearWeight): its storage is int8 + scales, which
+        # this kernel cannot update. The reference's AdamWBF16SR reaches such parameters through their own
+        # in-place ops; here they take a stock optimizer, whose add_/addcdiv_ land in the fused INT8 update.
+        raise TypeError(
+            f"AdamWBF16SR cannot update a {type(t).__name__} parameter: it has no bf16 storage. Use torch.optim.AdamW "
+            "(or another stock optimizer) for INT8 weight-only models; its in-place updates run the fused "
+            "de-quantize / update / stochastic re-quantize kernel.")
+    return t
 
 
 def adamw(p: Tensor, grad: Tensor, step: Tensor, exp_avg: Tensor, exp_avg_sq: Tensor, lr: Tensor, beta1: float,

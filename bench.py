@@ -280,12 +280,12 @@ def run_reference(args, rank: int):
     t0 = time.perf_counter()
     time_cpu_path(size, 1, 0)
     one = time.perf_counter() - t0
-    budget_passes = max(2, int(120.0 / max(one, 1e-3)))
+    budget_passes = max(2, int(75.0 / max(one, 1e-3)))
     warmup = max(0, min(args.warmup, budget_passes // 4))
     steps = max(1, min(args.steps, budget_passes - warmup))
     tops, threads, dt = time_cpu_path(size, steps, warmup)
     sample = (f"{steps} full passes of the {size}^3 workload after {warmup + 1} warm-up passes "
-              f"(requested --steps {args.steps} --warmup {args.warmup}; cut to a two-minute budget at {one:.1f} s per pass)")
+              f"(requested --steps {args.steps} --warmup {args.warmup}; cut to a 75 s budget at {one:.1f} s per pass)")
     line = {
         "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup + 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

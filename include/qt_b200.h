@@ -267,9 +267,9 @@ int qt_scaled_mm_ws(const void* a, int a_dtype, int64_t a_sm, int64_t a_sk, cons
  * Tile-scaled GEMM: for each block kb of qk reduction elements
  *   acc[m,n] += fp32(A[m,kb] @ B[kb,n]) * scale_a[m/qm, kb] * scale_b[kb, n/qn]
  * scale_a: [ceil(M/qm), K/qk] with strides (sa_s0, sa_s1); scale_b: [K/qk, ceil(N/qn)] with strides
- * (sb_s0, sb_s1). Supported: qk = 128 with K % 128 == 0, any qm >= 1, qn a multiple of 128 (the
- * reference benchmark's 1x128 activation / 128x128 weight tiles, benchmark_mm.py:87-89); other
- * shapes return QT_ERR_UNSUPPORTED. The per-block term is evaluated as one fused multiply-add with
+ * (sb_s0, sb_s1). Supported: qk a multiple of 128 with K % qk == 0, any qm >= 1, qn one of 16, 32, 64
+ * or a multiple of 128 (the reference benchmark's 1x128 activation / 128x128 weight tiles,
+ * benchmark_mm.py:87-89, take the fastest instantiation); other shapes return QT_ERR_UNSUPPORTED. The per-block term is evaluated as one fused multiply-add with
  * the product of the two scales, so results agree with the reference's two multiplies to rounding.
  * replaces: gn_kernels tile_scaled_mm, kernels/gn_kernels/triton_mm.py:346,410-441
  * (_tile_scaled_mm_kernel :223-342).

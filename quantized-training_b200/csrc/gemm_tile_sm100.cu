@@ -38,11 +38,14 @@ struct TileGemmParams {
     const void* scale_b;
     int64_t sa_s0, sa_s1, sb_s0, sb_s1;
     int qm, qn;
+    int kq;   // 128-byte reduction blocks per scale block (qk / 128)
     int scale_dtype;
     int* status;
 };
 
-template <int KIND, bool A_MN, bool B_MN>
+// NARROW: the scale blocks of B are narrower than a thread's 128 columns (qn = 16, 32, 64); the common wide case
+// keeps its own instantiation (the extra scale fetches cost registers the promotion loop has none to spare of).
+template <int KIND, bool A_MN, bool B_MN, bool NARROW>
 __global__ void __launch_bounds__(T_THREADS, 1)
 tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TileGemmParams p,
                  const uint32_t idesc) {
@@ -158,13 +161,20 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             float2 acc2[HN / 2];   // accumulators in pairs: the promotion uses packed fp32x2 instructions
 #pragma unroll
             for (int j = 0; j < HN / 2; ++j) acc2[j] = make_float2(0.0f, 0.0f);
+            // Scale blocks of B narrower than this thread's 128 columns (qn = 16, 32 or 64): one scale per
+            // 16-column chunk, fetched per reduction block. Otherwise one scale serves the whole row segment.
+            constexpr bool narrow = NARROW;
+            auto chunk_scale = [&](int kb, int c) {
+                const int64_t col = n0 + half * HN + c * 16;
+                return load_scale(p.scale_b, p.scale_dtype, (int64_t)(kb / p.kq) * p.sb_s0 + ((col < p.N ? col : n0) / p.qn) * p.sb_s1);
+            };
             // scale of K block 0, then always one block ahead
-            float s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0) * load_scale(p.scale_b, p.scale_dtype, sb_col * p.sb_s1);
+            float s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0) * (narrow ? 1.0f : load_scale(p.scale_b, p.scale_dtype, sb_col * p.sb_s1));
             for (int kb = 0; kb < num_kb; ++kb) {
                 const float s = s_next;
                 if (kb + 1 < num_kb)
-                    s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0 + (int64_t)(kb + 1) * p.sa_s1) *
-                             load_scale(p.scale_b, p.scale_dtype, (int64_t)(kb + 1) * p.sb_s0 + sb_col * p.sb_s1);
+                    s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0 + (int64_t)((kb + 1) / p.kq) * p.sa_s1) *
+                             (narrow ? 1.0f : load_scale(p.scale_b, p.scale_dtype, (int64_t)((kb + 1) / p.kq) * p.sb_s0 + sb_col * p.sb_s1));
                 ok = mbar_wait(part_full_bar(buf), buf_phase, s_abort, p.status, 0x800 | buf);
                 if (!ok) break;
                 tcgen05_fence_after();
@@ -174,8 +184,9 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 // converted by the integer-to-float instruction (another pipe) and the multiply-add is the
                 // packed fp32x2 form (half the issue slots); measured 1.37 -> 1.56 POPS at 8192^3 against a
                 // magic-number conversion that spent a second fp32 operation per element.
-                const float2 s2 = make_float2(s, s);
                 auto promote = [&](const uint32_t (&r)[16], int c) {
+                    const float sc = narrow ? s * chunk_scale(kb, c) : s;
+                    const float2 s2 = make_float2(sc, sc);
 #pragma unroll
                     for (int j = 0; j < 16; j += 2) {
                         float2 x;
@@ -239,9 +250,9 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
 }
 
-template <int KIND, bool A_MN, bool B_MN>
+template <int KIND, bool A_MN, bool B_MN, bool NARROW>
 int launch_tile(const CUtensorMap& ta, const CUtensorMap& tb, const TileGemmParams& p, uint32_t idesc, int grid, cudaStream_t stream) {
-    auto kfn = tile_gemm_kernel<KIND, A_MN, B_MN>;
+    auto kfn = tile_gemm_kernel<KIND, A_MN, B_MN, NARROW>;
     static bool attr_set[64] = {false};
     int dev = 0;
     QT_CUDA_CHECK(cudaGetDevice(&dev));
@@ -257,10 +268,16 @@ int launch_tile(const CUtensorMap& ta, const CUtensorMap& tb, const TileGemmPara
 template <int KIND>
 int launch_tile_layout(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const TileGemmParams& p, uint32_t idesc,
                        int grid, cudaStream_t stream) {
-    if (!a_mn && !b_mn) return launch_tile<KIND, false, false>(ta, tb, p, idesc, grid, stream);
-    if (!a_mn && b_mn) return launch_tile<KIND, false, true>(ta, tb, p, idesc, grid, stream);
-    if (a_mn && b_mn) return launch_tile<KIND, true, true>(ta, tb, p, idesc, grid, stream);
-    return launch_tile<KIND, true, false>(ta, tb, p, idesc, grid, stream);
+    if (p.qn < TBN / 2) {
+        if (!a_mn && !b_mn) return launch_tile<KIND, false, false, true>(ta, tb, p, idesc, grid, stream);
+        if (!a_mn && b_mn) return launch_tile<KIND, false, true, true>(ta, tb, p, idesc, grid, stream);
+        if (a_mn && b_mn) return launch_tile<KIND, true, true, true>(ta, tb, p, idesc, grid, stream);
+        return launch_tile<KIND, true, false, true>(ta, tb, p, idesc, grid, stream);
+    }
+    if (!a_mn && !b_mn) return launch_tile<KIND, false, false, false>(ta, tb, p, idesc, grid, stream);
+    if (!a_mn && b_mn) return launch_tile<KIND, false, true, false>(ta, tb, p, idesc, grid, stream);
+    if (a_mn && b_mn) return launch_tile<KIND, true, true, false>(ta, tb, p, idesc, grid, stream);
+    return launch_tile<KIND, true, false, false>(ta, tb, p, idesc, grid, stream);
 }
 
 }  // namespace
@@ -284,10 +301,10 @@ extern "C" int qt_tile_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64
     QT_REQUIRE(scale_dtype == QT_BF16 || scale_dtype == QT_F32, "tile_scaled_mm: scale_dtype must be QT_BF16 or QT_F32 (got %d)", scale_dtype);
     if (M == 0 || N == 0) return QT_OK;
     QT_REQUIRE(a && b && c && scale_a && scale_b, "tile_scaled_mm: null pointer");
-    if (qk != TBK || K % TBK != 0 || K == 0)
-        return fail(QT_ERR_UNSUPPORTED, "tile_scaled_mm: the reduction block must be 128 and K a positive multiple of it (qk=%d, K=%lld)", qk, (long long)K);
-    if (qm < 1 || qn < 128 || qn % 128 != 0)
-        return fail(QT_ERR_UNSUPPORTED, "tile_scaled_mm: qm must be >= 1 and qn a multiple of 128 (qm=%d, qn=%d)", qm, qn);
+    if (qk < TBK || qk % TBK != 0 || K % qk != 0 || K == 0)
+        return fail(QT_ERR_UNSUPPORTED, "tile_scaled_mm: the reduction block must be a multiple of 128 and K a positive multiple of it (qk=%d, K=%lld)", qk, (long long)K);
+    if (qm < 1 || !(qn == 16 || qn == 32 || qn == 64 || (qn >= 128 && qn % 128 == 0)))
+        return fail(QT_ERR_UNSUPPORTED, "tile_scaled_mm: qm must be >= 1 and qn one of 16, 32, 64 or a multiple of 128 (qm=%d, qn=%d)", qm, qn);
     QT_REQUIRE((a_sk == 1) != (a_sm == 1) || M == 1, "tile_scaled_mm: exactly one stride of A must be 1");
     QT_REQUIRE((b_sk == 1) != (b_sn == 1) || N == 1, "tile_scaled_mm: exactly one stride of B must be 1");
     const bool a_mn = (a_sk != 1), b_mn = (b_sk != 1);
@@ -304,7 +321,7 @@ extern "C" int qt_tile_scaled_mm(const void* a, int a_dtype, int64_t a_sm, int64
 
     TileGemmParams p = {};
     p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.scale_a = scale_a; p.scale_b = scale_b;
-    p.sa_s0 = sa_s0; p.sa_s1 = sa_s1; p.sb_s0 = sb_s0; p.sb_s1 = sb_s1; p.qm = qm; p.qn = qn; p.scale_dtype = scale_dtype;
+    p.sa_s0 = sa_s0; p.sa_s1 = sa_s1; p.sb_s0 = sb_s0; p.sb_s1 = sb_s1; p.qm = qm; p.qn = qn; p.kq = qk / TBK; p.scale_dtype = scale_dtype;
     if (int rc = device_status_ptr(&p.status)) return rc;
     const int64_t tiles = ((M + TBM - 1) / TBM) * ((N + TBN - 1) / TBN);
     const int sms = num_sms();

@@ -240,6 +240,12 @@ class Int8LinearWeight(Tensor):
                     return dst
             return dst.copy_(func(dst.dequantize(), *args[1:], **kwargs))
 
+        # decoupled weight decay of stock optimizers (param.mul_(1 - lr * wd)): the same three steps. The
+        # reference's dispatch has no entry for it, which leaves the weights undecayed there.
+        if func in (aten.mul_.Tensor, aten.mul_.Scalar):
+            dst = args[0]
+            return dst.copy_(dst.dequantize() * args[1])
+
         raise NotImplementedError(f"{cls.__name__} dispatch: attempting to run {func}, this is not supported")
 
 

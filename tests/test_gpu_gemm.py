@@ -209,8 +209,35 @@ def test_tile_scaled_mm_rejects_unsupported_blocks():
     A, B = rand_i8((128, 256), 1), rand_i8((256, 128), 2)
     sa = torch.ones((128, 4), dtype=torch.bfloat16, device="cuda")   # qk = 64
     sb = torch.ones((4, 1), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(RuntimeError, match="reduction block must be 128"):
+    with pytest.raises(RuntimeError, match="reduction block must be a multiple of 128"):
         gn_kernels.scaled_mm(A, B, sa, sb)
+    sa = torch.ones((128, 2), dtype=torch.bfloat16, device="cuda")   # qk = 128, qn = 8
+    sb = torch.ones((2, 16), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="qn one of 16, 32, 64"):
+        gn_kernels.scaled_mm(A, B, sa, sb)
+
+
+@pytest.mark.parametrize("blocks", [(1, 256, 128), (128, 256, 256), (1, 128, 64), (4, 128, 32), (1, 512, 16), (128, 128, 256)])
+@pytest.mark.parametrize("kind", ["int8", "e4m3"])
+def test_tile_scaled_mm_infers_other_block_shapes(blocks, kind):
+    """The reference infers (QM, QK, QN) from the scale shapes (kernels/gn_kernels/triton_mm.py:419,434-437).
+    Here: any QM, QK a multiple of 128, QN one of 16 / 32 / 64 or a multiple of 128."""
+    qm, qk, qn = blocks
+    M, N, K = 256, 512, 1024
+    g = torch.Generator().manual_seed(qm + qk + qn)
+    if kind == "int8":
+        A, B = rand_i8((M, K), 61), rand_i8((K, N), 62)
+    else:
+        A = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn).cuda()
+        B = torch.randn(K, N, generator=g).to(torch.float8_e4m3fn).cuda()
+    sa = (torch.rand(M // qm, K // qk, generator=g) / 64 + 1e-3).bfloat16().cuda()
+    sb = (torch.rand(K // qk, N // qn, generator=g) / 64 + 1e-3).bfloat16().cuda()
+    out = gn_kernels.scaled_mm(A, B.T.contiguous().T, sa, sb)
+    a_np = A.cpu().numpy() if kind == "int8" else bits_of(A)
+    b_np = B.cpu().numpy() if kind == "int8" else bits_of(B)
+    want = om.tile_scaled_mm(a_np, b_np, values_of(sa), values_of(sb), kind=kind)
+    np.testing.assert_allclose(values_of(out), want, rtol=1e-2 if kind == "int8" else 1.6e-2, atol=1e-4)
+    assert nv.device_status() == 0
 
 
 @pytest.mark.parametrize("mnk", [(1024, 1024, 32768), (256, 256, 8192), (2048, 256, 16384), (300, 520, 12288), (128, 256, 8192)])

@@ -67,3 +67,30 @@ def test_no_alloc_rejects_more_columns_than_its_scratch_holds():
     got_q, got_s = _no_alloc_form(x)
     want_q, want_s = _two_call_form(x)
     assert torch.equal(got_q, want_q) and torch.equal(got_s, want_s)
+
+
+def test_no_alloc_leaves_the_device_memory_accounting_unchanged():
+    """What the name promises: with the outputs allocated beforehand and the scratch already looked up (first
+    call), a call neither takes nor returns device memory. Free memory as the driver reports it, and what the
+    framework's allocator has reserved, are the same before and after."""
+    x = (torch.randn(2048, 1024, device="cuda") * 2.0).bfloat16()
+    qt = torch.empty((1024, 2048), dtype=torch.int8, device="cuda")
+    scale = torch.empty((1024, 1), dtype=torch.bfloat16, device="cuda")
+    lib, stream = nv.load(), nv.stream_ptr(x.device)
+
+    def call():
+        nv.check(lib.qt_quantize_colwise_t_noalloc(x.data_ptr(), nv.QT_BF16, 2048, 1024, 1024, qt.data_ptr(), nv.QT_I8,
+                                                   scale.data_ptr(), nv.QT_BF16, 1e-12, 0, 0, 0, stream))
+
+    call()                                   # the first call on a device looks the scratch address up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert torch.cuda.memory_reserved() == reserved_before
+    want_q, want_s = _two_call_form(x)
+    assert torch.equal(qt, want_q) and torch.equal(scale, want_s)

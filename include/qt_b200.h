@@ -195,7 +195,8 @@ int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_t cols, int
 
 /*
  * How many CTAs cooperate on one MMA in the GEMMs below: 0 = chosen per problem (a 2-CTA pair
- * sharing a 256 x 256 tile when M > 128 and K > 1024, else one CTA per 128 x 256 tile), 1 or 2 = forced.
+ * sharing a 256 x 256 tile when M > 128 and the reduction is at least 512 bytes long, else one CTA per
+ * 128 x 256 tile), 1 or 2 = forced.
  * Process-wide; meant for tests and tuning. Results are identical either way for int8.
  * No counterpart in the reference (Triton autotunes its own tile shapes, triton_mm.py:9-43).
  */

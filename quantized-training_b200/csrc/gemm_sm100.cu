@@ -680,9 +680,9 @@ void choose_splits(int64_t M, int64_t N, int64_t K, int cg, int* splits, int* kb
     *splits = (num_kb + per - 1) / per;
 }
 
-// CTA pairs pay off when the reduction is long enough to amortise the per-tile hand-overs across the
-// pair (measured: better from K = 2048 up, slightly worse at K = 1024) and there is more than one row
-// block.
+// CTA pairs pay off when there is more than one row block and the reduction is at least two stages long
+// (512 bytes: int8 / fp8 K >= 512, bf16 K >= 256). With the current epilogue the pair form measured faster
+// than the single-CTA form from that length up.
 int pick_cta_group(int64_t M, int64_t K) {
     int cg = g_forced_cta_group;
     if (cg != 1 && cg != 2) cg = (M > BM && K >= 512) ? 2 : 1;

@@ -462,6 +462,19 @@ __device__ __forceinline__ void fold_column_maxima(uint32_t (&colmax)[VPT][4], u
 // With UPD != 0 the kernel re-quantizes an int8 weight in place: the "row" is the updated weight formed
 // by updated_vec8 from q, scale and the operand tensors; q and scale are then overwritten (each row
 // is complete in registers before its bytes are stored, and a prefetched row is a different row).
+// CTAs per SM of the row kernel with up to 4 vectors per thread. Fewer CTAs leave the compiler more registers:
+// the stochastic form measured 51.5 / 55.6 / 58.9 us per launch on [32768, 2048] with 2 / 3 / 4 CTAs per SM, the
+// column-maxima form 43.5 / 41.7 / 45.7; round-to-nearest is indifferent (35.1 - 35.5).
+#ifndef QT_SR_CTAS
+#define QT_SR_CTAS 2
+#endif
+#ifndef QT_COLABS_CTAS
+#define QT_COLABS_CTAS 3
+#endif
+#ifndef QT_RNE_CTAS
+#define QT_RNE_CTAS 4
+#endif
+
 // Barrier among the TPR threads of row group `sub` (at most four groups of several warps per CTA). The
 // barrier number is an immediate so that the CTA reserves five hardware barriers, not all sixteen.
 template <int TPR>
@@ -475,7 +488,7 @@ __device__ __forceinline__ void row_barrier(int sub) {
 }
 
 template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0, bool SCATTER = false>
-__global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (SR ? 3 : 4) : (VPT <= 8 ? 2 : 1)))
+__global__ void __launch_bounds__(kThreads, (VPT <= 4 ? (UPD != 0 ? 3 : (SR ? QT_SR_CTAS : (COLABS ? QT_COLABS_CTAS : QT_RNE_CTAS))) : (VPT <= 8 ? 2 : 1)))
 rowwise_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;  // rows per CTA per iteration
     constexpr int WPR = TPR / 32;        // warps per row
@@ -653,7 +666,7 @@ __device__ __forceinline__ uint32_t silu_mul_word(uint32_t g, uint32_t u) {
 // row); 2 = silu(x) * x2 (also writes y). The producer forms fold the activation quantize of the INT8
 // linear layers into the kernel that produces the activation, so the activation is not read again.
 template <int TPR, int VPT, bool COLABS, bool SR, bool TILE = false, int PRODUCER = 0>
-__global__ void __launch_bounds__(kThreads, (PRODUCER != 0 ? (VPT <= 4 ? 2 : 1) : (VPT <= 4 ? ((SR || COLABS) ? 3 : 4) : (VPT <= 8 ? 2 : 1))))
+__global__ void __launch_bounds__(kThreads, (PRODUCER != 0 ? (VPT <= 4 ? 2 : 1) : (VPT <= 4 ? (SR ? QT_SR_CTAS : (COLABS ? QT_COLABS_CTAS : QT_RNE_CTAS)) : (VPT <= 8 ? 2 : 1))))
 rowwise_full_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;
     constexpr int WPR = TPR / 32;
@@ -901,7 +914,9 @@ constexpr int kClusterSize = 2;
 template <int TPR, int VPT, bool COLABS, bool SR, int UPD = 0, bool SCATTER = false>
 int launch_rowwise_cfg(const RowwiseParams& p, cudaStream_t stream) {
     constexpr int RPC = kThreads / TPR;
-    constexpr int CTAS_PER_SM = (VPT <= 4 ? ((SR || COLABS) ? 3 : 4) : (VPT <= 8 ? 2 : 1));
+    // the in-place weight update computes its row while loading it, so it hides latency with occupancy (3 CTAs:
+    // 133 us against 163 us with 2 on [32768, 2048])
+    constexpr int CTAS_PER_SM = (VPT <= 4 ? (UPD != 0 ? 3 : (SR ? QT_SR_CTAS : (COLABS ? QT_COLABS_CTAS : QT_RNE_CTAS))) : (VPT <= 8 ? 2 : 1));
     const int64_t want = (p.rows + RPC - 1) / RPC;
     const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
     int64_t grid = want < cap ? want : cap;

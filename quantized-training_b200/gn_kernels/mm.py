@@ -36,17 +36,19 @@ def _direct(*tensors: Tensor) -> bool:
     return all(type(t) is Tensor and t.is_cuda for t in tensors)
 
 
-def _workspace(M: int, N: int, K: int, dev: torch.device) -> tuple[int, int]:
-    """(pointer, bytes) of the split-K scratch the library asks for; (0, 0) for most shapes. Only
-    small outputs with long reductions (M * N up to a few hundred tiles) ever split, so this is cheap."""
+def _workspace(M: int, N: int, K: int, dev: torch.device):
+    """(tensor or None, pointer, bytes) of the split-K scratch the library asks for; (None, 0, 0) for most
+    shapes. Only small outputs with long reductions (M * N up to a few hundred tiles) ever split, so this is
+    cheap. The caller holds the tensor until its launch is enqueued; after that the caching allocator may hand
+    the block to later work of the same stream only, which runs after the kernel (no state is shared between
+    the threads that call into this module)."""
     if M * N > (1 << 23) or K < 2048:
-        return 0, 0
+        return None, 0, 0
     need = nv.load().qt_gemm_workspace_bytes(M, N, K)
     if need <= 0:
-        return 0, 0
+        return None, 0, 0
     buf = torch.empty(need, dtype=torch.uint8, device=dev)
-    _workspace.keep = buf  # stays referenced until the next call; the caching allocator is stream-ordered anyway
-    return buf.data_ptr(), need
+    return buf, buf.data_ptr(), need
 
 
 lib.define("int8_mm(Tensor A, Tensor B) -> Tensor")
@@ -78,10 +80,11 @@ def _int8_mm_cuda(A: Tensor, B: Tensor):
         return C.zero_()
     A, B = _operand(A, 1), _operand(B, 0)
     with nv.on_device(dev):
-        ws, ws_bytes = _workspace(M, N, K, dev)
+        ws_buf, ws, ws_bytes = _workspace(M, N, K, dev)
         nv.check(nv.load().qt_int8_mm_ws(A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1),
                                          C.data_ptr(), C.stride(0), M, N, K, ws, ws_bytes, nv.stream_ptr(dev)))
         nv.raise_if_device_failed()
+        del ws_buf
     return C
 
 
@@ -154,12 +157,13 @@ def _scaled_mm_cuda(A: Tensor, B: Tensor, row_scale: Tensor, col_scale: Tensor, 
     A, B = _operand(A, 1), _operand(B, 0)
     row_scale, col_scale = row_scale.contiguous(), col_scale.contiguous()
     with nv.on_device(dev):
-        ws, ws_bytes = _workspace(M, N, K, dev)
+        ws_buf, ws, ws_bytes = _workspace(M, N, K, dev)
         nv.check(nv.load().qt_scaled_mm_ws(
             A.data_ptr(), nv.code(A.dtype), A.stride(0), A.stride(1), B.data_ptr(), nv.code(B.dtype), B.stride(0),
             B.stride(1), row_scale.data_ptr(), col_scale.data_ptr(), int(col_scale.numel() == 1 and N != 1) | (2 if col_scale_first else 0),
             nv.code(row_scale.dtype), C.data_ptr(), C.stride(0), M, N, K, ws, ws_bytes, nv.stream_ptr(dev)))
         nv.raise_if_device_failed()
+        del ws_buf
     return C
 
 

@@ -41,7 +41,9 @@ class _QuantCache:
 
     @staticmethod
     def cacheable(t: Tensor) -> bool:
-        return not t.is_inference()
+        # plain tensors only: fake / functional tensors (torch.compile's tracing) have no data pointer, and
+        # tensors made under inference_mode no version counter
+        return type(t) is Tensor and not t.is_inference()
 
     @staticmethod
     def key(t: Tensor, eps: float):
@@ -68,9 +70,14 @@ class _QuantCache:
 
     def clear_after_backward(self):
         """Called from inside a backward function: drop every entry once the running backward pass is over."""
+        if torch.compiler.is_compiling() or not self.entries:
+            return   # nothing to drop (the cache is not used under tracing, where no backward pass is running either)
         if not self._clear_queued:
-            self._clear_queued = True
-            torch.autograd.Variable._execution_engine.queue_callback(self.clear)
+            try:
+                torch.autograd.Variable._execution_engine.queue_callback(self.clear)
+                self._clear_queued = True
+            except RuntimeError:   # not inside a backward pass (a backward function being traced): drop now
+                self.clear()
 
 
 _quant_cache = _QuantCache()

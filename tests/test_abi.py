@@ -78,6 +78,38 @@ def test_argument_errors_do_not_need_a_gpu(lib):
     assert rc == 1 and b"mode" in lib.qt_last_error()
 
 
+def test_producer_and_gather_entry_points_check_their_arguments_on_the_host(lib):
+    buf = ctypes.create_string_buffer(4096)
+    addr = (ctypes.addressof(buf) + 15) & ~15
+    # producers: bad quantized dtype; q without scale; a width the kernel does not take
+    rc = lib.qt_rmsnorm_quantize(addr, 8, 64, 64, addr, 1e-6, addr, None, addr, 0, addr, 0, addr, 1e-12, None)
+    assert rc == 1 and b"q_dtype" in lib.qt_last_error()
+    rc = lib.qt_silu_mul_quantize(addr, addr, 8, 64, 64, 64, addr, addr, 2, None, 0, None, 1e-12, None)
+    assert rc == 1 and b"without scale" in lib.qt_last_error()
+    rc = lib.qt_rmsnorm_quantize(addr, 8, 60, 64, addr, 1e-6, addr, None, None, 2, None, 0, None, 1e-12, None)
+    assert rc == 3 and b"multiple of 8" in lib.qt_last_error()
+    # backward: scratch too small is an argument error, before any launch
+    assert lib.qt_rmsnorm_backward_partial_rows(0, 64) == 0
+    rc = lib.qt_rmsnorm_backward(addr, 64, addr, 64, addr, addr, 8, 64, addr, addr, 0, addr, 0, None)
+    assert rc == 1 and b"dw_partial" in lib.qt_last_error()
+    rc = lib.qt_silu_mul_backward(addr, 64, addr, 64, addr, 32, 8, 64, addr, addr, None)
+    assert rc == 1 and b"stride" in lib.qt_last_error()
+    # rotary embedding: tokens must be whole sequences; head size a multiple of 16
+    rc = lib.qt_rope(addr, 10, 2, 64, addr, addr, 4, 0, 0, addr, None)
+    assert rc == 1 and b"sequences" in lib.qt_last_error()
+    rc = lib.qt_rope(addr, 8, 2, 24, addr, addr, 4, 0, 0, addr, None)
+    assert rc == 3
+    # bf16 GEMM with the scale in its epilogue: 16-byte rows
+    rc = lib.qt_bf16_mm_colscale(addr, 20, addr, 20, addr, addr, 16, 16, 16, 20, None)
+    assert rc == 3 and b"multiples of 8" in lib.qt_last_error()
+    # scaled_mm flag bits beyond the two that are defined
+    rc = lib.qt_scaled_mm(addr, 2, 16, 1, addr, 2, 1, 16, addr, addr, 4, 0, addr, 16, 16, 16, 16, None)
+    assert rc == 1 and b"flag bits" in lib.qt_last_error()
+    # column-wise quantize without the transpose: stochastic rounding is int8 only
+    rc = lib.qt_quantize_colwise(addr, 0, 4, 8, 8, addr, addr, 3, addr, 0, 1e-12, 1, 0, 0, None)
+    assert rc == 1 and b"stochastic" in lib.qt_last_error()
+
+
 def test_python_ops_refuse_cpu_tensors():
     import torch
     import gn_kernels

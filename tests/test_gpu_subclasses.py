@@ -404,3 +404,66 @@ def test_activation_quantization_cache_is_exact_and_invalidates():
         outs.append(lin(x))
     for a, b in zip(with_cache, outs):
         assert torch.equal(a, b)
+
+
+def test_real_layer_shape_forward_backward_on_sampled_rows_and_columns():
+    """One linear layer of the 1.1B model at the benchmark's token count (32768 x 2048 -> 5632): the oracle is
+    evaluated on sampled rows (forward, grad-input: row-wise quantization makes rows independent) and on
+    sampled weight entries (grad-weight: columns of the activation and of dY), bit for bit."""
+    M, K, N = 32768, 2048, 5632
+    x = randn_bf16((M, K), seed=71)
+    w = randn_bf16((N, K), std=0.02, seed=72)
+    gy = randn_bf16((M, N), std=0.01, seed=73)
+    weight = MixedPrecisionLinearWeight(w.clone(), MixedPrecisionConfig()).requires_grad_()
+    xr = x.clone().requires_grad_()
+    y = F.linear(xr, weight)
+    y.backward(gy)
+    rows = [0, 1, 4097, 20000, M - 1]
+    xs, gs = values_of(x[rows]), values_of(gy[rows])
+    wv = values_of(w)
+    want_y = om.dynamic_int8_mm(xs, wv.T)
+    np.testing.assert_array_equal(values_of(y[rows]), want_y)
+    want_gx = om.dynamic_int8_mm(gs, wv)
+    np.testing.assert_array_equal(values_of(xr.grad[rows]), want_gx)
+    # grad_weight[n, k] = ((x^T dY)^T)[n, k]: needs column k of x and column n of dY over all tokens
+    ks, ns = [0, 5, 1023, K - 1], [0, 77, 4000, N - 1]
+    xt = values_of(x[:, ks])            # [M, 4]
+    gt = values_of(gy[:, ns])           # [M, 4]
+    want_gw = om.dynamic_int8_mm(np.ascontiguousarray(xt.T), gt).T      # [4 (n), 4 (k)]
+    gw = getattr(weight.grad, "_data", weight.grad)
+    assert gw.is_contiguous()                                           # written in the weight's layout, not as a transposed view
+    got_gw = values_of(gw)[np.ix_(ns, ks)]
+    np.testing.assert_array_equal(got_gw, want_gw)
+
+
+def test_converted_linear_traces_under_torch_compile_without_freezing_the_noise():
+    """The ops carry Meta implementations and the wrappers route through the dispatcher when traced. With the
+    `aot_eager` backend (tracing, functionalisation and the autograd split of torch.compile, no code
+    generation) a converted Linear gives the eager result bit for bit, forward and backward; with stochastic
+    rounding two consecutive calls of the same compiled module differ, i.e. the Philox key is drawn when the op
+    runs, not frozen into the graph."""
+    torch._dynamo.reset()
+    lin = torch.nn.Linear(256, 384, bias=False).bfloat16().cuda()
+    convert_mixed_precision(lin, config=MixedPrecisionConfig())
+    x = randn_bf16((128, 256), seed=81)
+    xe = x.clone().requires_grad_()
+    ye = lin(xe)
+    ye.float().square().mean().backward()
+    ge, gwe = xe.grad.clone(), getattr(lin.weight.grad, "_data", lin.weight.grad).clone()
+    lin.weight.grad = None
+    compiled = torch.compile(lin, backend="aot_eager", fullgraph=False)
+    xc = x.clone().requires_grad_()
+    yc = compiled(xc)
+    yc.float().square().mean().backward()
+    assert torch.equal(yc, ye)
+    assert torch.equal(xc.grad, ge)
+    assert torch.equal(getattr(lin.weight.grad, "_data", lin.weight.grad), gwe)
+
+    torch._dynamo.reset()
+    lin_sr = torch.nn.Linear(256, 384, bias=False).bfloat16().cuda()
+    convert_mixed_precision(lin_sr, config=MixedPrecisionConfig(stochastic_rounding=True))
+    compiled_sr = torch.compile(lin_sr, backend="aot_eager", fullgraph=False)
+    with torch.no_grad():
+        a, b = compiled_sr(x), compiled_sr(x)
+    assert not torch.equal(a, b)
+    assert (a.float() - b.float()).abs().max().item() < 0.1 * a.float().abs().max().item()

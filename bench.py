@@ -243,6 +243,11 @@ class ClockSampler:
         return out
 
 
+def workload_name(M: int, N: int, K: int) -> str:
+    """config.workload, spelled the same by both arms."""
+    return f"rowwise dynamic INT8 quantize (activation + weight) + scaled INT8 GEMM A@B.T, M={M} N={N} K={K} per GPU, bf16 in/out"
+
+
 def _bind_near_gpu(gpu_index: int):
     """Run this rank on the CPU cores NVML names as closest to its GPU, so that the pinned host buffers it
     allocates next are first touched, hence placed, on that socket's memory. With eight ranks copying 400 MB
@@ -312,7 +317,7 @@ def run_reference(args, rank: int):
         "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup + 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
-        "config": {"workload": f"rowwise dynamic INT8 quantize + scaled INT8 GEMM A@B.T, M=N=K={size}, bf16 in/out",
+        "config": {"workload": workload_name(size, size, size),
                    "where": "host CPU cores, torch eager quantize + torch._int_mm + scale (oracle/cpu_path.py)"},
         "cpu_baseline": {"value": tops, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -1165,7 +1170,7 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
         "config": {
-            "workload": f"rowwise dynamic INT8 quantize (activation + weight shard) + scaled INT8 GEMM A@B.T, M={gM} N={gN} K={gK} per GPU, bf16 in/out",
+            "workload": workload_name(gM, gN, gK),
             "weight_all_gather": ("none (1 GPU)" if world == 1 else
                                   "fused into the quantize kernel: int8 rows + bf16 scales stored into every rank's buffer over NVLink (peer-to-peer stores, symmetric memory), one step ahead on a side stream" if fused_gather else
                                   "int8 rows + bf16 scales over NCCL, prefetched one step ahead on a side stream"),

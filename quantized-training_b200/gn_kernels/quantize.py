@@ -56,6 +56,19 @@ def _row_stride(x: Tensor) -> int:
     return x.stride(0) if x.shape[0] > 1 else max(x.shape[1], 1)
 
 
+# Offset value that tells an op implementation to draw its (seed, offset) pair when it RUNS. Under
+# torch.compile the Python wrapper is traced (by dynamo, or executed on fake / functional tensors by the later
+# stages), and a pair drawn at trace time would be baked into the graph as constants: every step would then
+# round with the same noise. The sentinel is what gets baked instead.
+_DRAW_AT_RUN_TIME = -1
+
+
+def _resolve_key(dev: torch.device, stochastic: bool, seed: int, offset: int) -> tuple[int, int]:
+    if stochastic and offset == _DRAW_AT_RUN_TIME:
+        return next_philox_key(dev)
+    return seed, offset
+
+
 # ---- op definitions ---------------------------------------------------------------------------
 
 lib.define("quantize_rowwise(Tensor x, ScalarType out_dtype, ScalarType scale_dtype, bool stochastic, float eps, int seed, int offset) -> (Tensor, Tensor)")
@@ -77,6 +90,7 @@ def _rowwise_cuda(x, out_dtype, scale_dtype, stochastic, eps, seed, offset):
     rows, cols = x.shape
     q = torch.empty((rows, cols), dtype=out_dtype, device=dev)
     scale = torch.empty((rows, 1), dtype=scale_dtype, device=dev)
+    seed, offset = _resolve_key(dev, stochastic, seed, offset)
     with nv.on_device(dev):
         nv.check(nv.load().qt_quantize_rowwise(
             x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), q.data_ptr(), nv.code(out_dtype),
@@ -98,6 +112,7 @@ def _rowwise_colabsmax_cuda(x, out_dtype, scale_dtype, stochastic, eps, seed, of
     q = torch.empty((rows, cols), dtype=out_dtype, device=dev)
     scale = torch.empty((rows, 1), dtype=scale_dtype, device=dev)
     colmax = torch.empty((cols,), dtype=torch.float32, device=dev)
+    seed, offset = _resolve_key(dev, stochastic, seed, offset)
     with nv.on_device(dev):
         nv.check(nv.load().qt_quantize_rowwise_colabsmax(
             x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), q.data_ptr(), nv.code(out_dtype),
@@ -137,6 +152,7 @@ def _colwise_t_cuda(x, col_absmax, out_dtype, scale_dtype, stochastic, eps, seed
         raise ValueError("col_absmax must be a contiguous float32 tensor with one entry per column of x")
     qt = torch.empty((cols, rows), dtype=out_dtype, device=dev)
     scale = torch.empty((cols, 1), dtype=scale_dtype, device=dev)
+    seed, offset = _resolve_key(dev, stochastic, seed, offset)
     with nv.on_device(dev):
         nv.check(nv.load().qt_quantize_colwise_t(
             x.data_ptr(), nv.code(x.dtype), rows, cols, _row_stride(x), col_absmax.data_ptr(), qt.data_ptr(),
@@ -168,7 +184,11 @@ def _tile_cuda(x, tile_r, tile_c, out_dtype, scale_dtype, eps):
 # ---- Python wrappers --------------------------------------------------------------------------
 
 def _key(x: Tensor, stochastic: bool) -> tuple[int, int]:
-    return next_philox_key(x.device) if stochastic else (0, 0)
+    if not stochastic:
+        return 0, 0
+    if torch.compiler.is_compiling() or type(x) is not Tensor:
+        return 0, _DRAW_AT_RUN_TIME
+    return next_philox_key(x.device)
 
 
 def _direct(x: Tensor) -> bool:

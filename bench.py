@@ -59,6 +59,7 @@ def parse_args():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="--gpus > 1: 'fused' = one kernel quantizes the weight shard and stores it into every rank's gathered "
                          "buffer over NVLink (symmetric memory); 'nccl' = quantize, then NCCL all-gather")
+    ap.add_argument("--group-m", type=int, default=0, help="force the GEMM's rasterisation group height (0 = the library's choice)")
     ap.add_argument("--sm-margin", type=int, default=None,
                     help="SMs the GEMM leaves free when --gpus > 1 (default: 8 beside NCCL's all-gather kernel, 0 with the fused gather)")
     ap.add_argument("--eager-elementwise", action="store_true",
@@ -845,6 +846,8 @@ def main():
     from gn_kernels import _native
 
     _native.load()
+    if args.group_m:
+        _native.check(_native.load().qt_set_gemm_group_m(args.group_m))
     fused_gather = world > 1 and args.gather == "fused"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

@@ -203,6 +203,15 @@ int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_t cols, int
 int qt_set_gemm_cta_group(int cta_group);
 
 /*
+ * Rasterisation of the persistent GEMM grids: `group_m` row-tiles sweep all column-tiles before the next group
+ * starts, so the group's A panel stays in L2 while B streams past once per group. 0 = the default of 8,
+ * otherwise forced. Process-wide; for tests and tuning.
+ * Results do not depend on it. No counterpart in the reference (Triton's kernels use a fixed GROUP_M = 8,
+ * kernels/gn_kernels/triton_mm.py:66,72-77).
+ */
+int qt_set_gemm_group_m(int group_m);
+
+/*
  * Number of SMs the persistent GEMM grids leave unused (default 0), so that a kernel which has to
  * run at the same time -- an NCCL collective prefetching the next weight -- finds free SMs instead
  * of queueing behind a grid that holds every SM until it finishes. Process-wide.

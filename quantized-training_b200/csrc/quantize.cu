@@ -474,6 +474,9 @@ __device__ __forceinline__ void fold_column_maxima(uint32_t (&colmax)[VPT][4], u
 #ifndef QT_RNE_CTAS
 #define QT_RNE_CTAS 4
 #endif
+#ifndef QT_PRODUCER_CTAS
+#define QT_PRODUCER_CTAS 3   // the RMSNorm / silu * up forms: silu * up + quantize on [32768, 5632] 248 us with 3, 314 us with 2
+#endif
 
 // Barrier among the TPR threads of row group `sub` (at most four groups of several warps per CTA). The
 // barrier number is an immediate so that the CTA reserves five hardware barriers, not all sixteen.
@@ -666,7 +669,7 @@ __device__ __forceinline__ uint32_t silu_mul_word(uint32_t g, uint32_t u) {
 // row); 2 = silu(x) * x2 (also writes y). The producer forms fold the activation quantize of the INT8
 // linear layers into the kernel that produces the activation, so the activation is not read again.
 template <int TPR, int VPT, bool COLABS, bool SR, bool TILE = false, int PRODUCER = 0>
-__global__ void __launch_bounds__(kThreads, (PRODUCER != 0 ? (VPT <= 4 ? 2 : 1) : (VPT <= 4 ? (SR ? QT_SR_CTAS : (COLABS ? QT_COLABS_CTAS : QT_RNE_CTAS)) : (VPT <= 8 ? 2 : 1))))
+__global__ void __launch_bounds__(kThreads, (PRODUCER != 0 ? (VPT <= 4 ? QT_PRODUCER_CTAS : 1) : (VPT <= 4 ? (SR ? QT_SR_CTAS : (COLABS ? QT_COLABS_CTAS : QT_RNE_CTAS)) : (VPT <= 8 ? 2 : 1))))
 rowwise_full_kernel(const RowwiseParams p) {
     constexpr int RPC = kThreads / TPR;
     constexpr int WPR = TPR / 32;
@@ -1002,7 +1005,7 @@ int launch_tile_1x128(const RowwiseParams& p, cudaStream_t stream) {
 template <int TPR, int VPT, int PRODUCER>
 int launch_producer_cfg(const RowwiseParams& p, cudaStream_t stream) {
     constexpr int RPC = kThreads / TPR;
-    constexpr int CTAS_PER_SM = VPT <= 4 ? 2 : 1;
+    constexpr int CTAS_PER_SM = VPT <= 4 ? QT_PRODUCER_CTAS : 1;
     if (p.rows % RPC != 0)
         return fail(QT_ERR_UNSUPPORTED, "fused producer: %lld rows are not a multiple of %d (rows per CTA at this width)", (long long)p.rows, RPC);
     const int64_t want = p.rows / RPC;

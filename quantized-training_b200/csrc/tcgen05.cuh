@@ -265,12 +265,12 @@ struct TileCoord {
 // that run together share A and B panels in L2.
 // 32-bit arithmetic throughout (the host checks that the tile count fits): 64-bit divisions are
 // emulated and cost hundreds of cycles each, on the critical path of every role once per tile.
-__device__ __forceinline__ TileCoord tile_coord(uint32_t tile, int tiles_m, int tiles_n) {
-    const uint32_t width = (uint32_t)GROUP_M * (uint32_t)tiles_n;
+__device__ __forceinline__ TileCoord tile_coord(uint32_t tile, int tiles_m, int tiles_n, int group_m = GROUP_M) {
+    const uint32_t width = (uint32_t)group_m * (uint32_t)tiles_n;
     const uint32_t group = tile / width;
     const uint32_t in_group = tile - group * width;
-    const int first_m = (int)group * GROUP_M;
-    const uint32_t group_size = (uint32_t)((tiles_m - first_m) < GROUP_M ? (tiles_m - first_m) : GROUP_M);
+    const int first_m = (int)group * group_m;
+    const uint32_t group_size = (uint32_t)((tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m);
     const uint32_t col = in_group / group_size;
     return TileCoord{first_m + (int)(in_group - col * group_size), (int)col};
 }

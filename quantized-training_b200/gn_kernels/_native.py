@@ -48,6 +48,7 @@ SIGNATURES = {
                                  c_int, c_float, c_void_p]),
     "qt_set_gemm_cta_group": (c_int, [c_int]),
     "qt_set_gemm_sm_margin": (c_int, [c_int]),
+    "qt_set_gemm_group_m": (c_int, [c_int]),
     "qt_int8_mm": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
                            c_int64, c_void_p]),
     "qt_scaled_mm": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,

@@ -437,3 +437,17 @@ def test_bf16_mm_with_column_scale_epilogue(mnk, cta_group):
         assert (rel > 1e-2).float().mean().item() < 1e-5
     assert (out == ref).float().mean().item() > 0.97
     assert nv.device_status() == 0
+
+
+@pytest.mark.parametrize("group_m", [1, 3, 32])
+def test_rasterisation_group_height_does_not_change_results(group_m):
+    """The order in which the persistent grid visits output tiles is a tuning choice (how tall a group of
+    row-tiles sweeps the columns): exact int32 results for any height, ragged tile counts included."""
+    A, B = rand_i8((1300, 640), 7), rand_i8((640, 1100), 8)
+    want = om.int8_mm(A.cpu().numpy(), B.cpu().numpy())
+    nv.check(nv.load().qt_set_gemm_group_m(group_m))
+    try:
+        np.testing.assert_array_equal(gn_kernels.int8_mm(A, B).cpu().numpy(), want)
+    finally:
+        nv.check(nv.load().qt_set_gemm_group_m(0))
+    assert nv.device_status() == 0

@@ -467,3 +467,33 @@ def test_converted_linear_traces_under_torch_compile_without_freezing_the_noise(
         a, b = compiled_sr(x), compiled_sr(x)
     assert not torch.equal(a, b)
     assert (a.float() - b.float()).abs().max().item() < 0.1 * a.float().abs().max().item()
+
+
+def test_converted_model_runs_under_inference_mode_and_the_cache_is_bounded():
+    """Tensors made under torch.inference_mode have no version counter: the activation cache must step aside
+    (the reference's layer works there). After a backward pass the cache is empty again, and it never holds
+    more than its byte cap."""
+    from subclasses.int8 import _quant_cache
+
+    lin = torch.nn.Linear(256, 384, bias=False).bfloat16().cuda()
+    convert_mixed_precision(lin, config=MixedPrecisionConfig())
+    x = randn_bf16((64, 256), seed=91)
+    ref = lin(x)
+    with torch.inference_mode():
+        xi = x.clone()
+        out = lin(xi)
+    assert torch.equal(out, ref.detach())
+    _quant_cache.clear()
+    xr = x.clone().requires_grad_()
+    y = lin(xr)
+    assert len(_quant_cache.entries) >= 1
+    y.sum().backward()
+    assert len(_quant_cache.entries) == 0
+    # the optimizer refuses INT8 weight-only parameters with a clear message
+    from other_optim import AdamWBF16SR
+
+    lin8 = torch.nn.Linear(64, 64, bias=False).bfloat16().cuda()
+    convert_int8_quantized_training(lin8)
+    lin8(randn_bf16((8, 64), seed=3)).sum().backward()
+    with pytest.raises(TypeError, match="INT8 weight-only"):
+        AdamWBF16SR(lin8.parameters(), lr=1e-3).step()

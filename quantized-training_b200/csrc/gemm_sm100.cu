@@ -5,8 +5,9 @@
 //   warp 0      TMA producer   global -> 128B-swizzled shared-memory stages (cp.async.bulk.tensor)
 //   warp 1      MMA issuer     one elected lane issues tcgen05.mma; accumulators live in TMEM
 //   warps 2..9  epilogue       two groups of four warps (one per TMEM lane quarter); group g drains
-//                              accumulator g: tcgen05.ld TMEM -> registers -> scale -> swizzled staging box
-//                              in shared memory -> TMA store (whole 128-byte output lines)
+//                              accumulator g in chunks of 32 columns: tcgen05.ld TMEM -> registers -> scale ->
+//                              swizzled staging box in shared memory -> TMA store (one box of 32 rows x 64
+//                              bytes per chunk)
 // Large problems run as CTA PAIRS (2-CTA clusters, tcgen05 cta_group::2): the pair owns a 256 x 256
 // tile, each CTA stages its 128 rows of A and half of B, the leader CTA issues M=256 MMAs for both
 // and each CTA drains its own 128 accumulator rows. Small problems (M <= 128 or K < 512) use one CTA
@@ -35,9 +36,36 @@ constexpr int BM = 128;      // tile rows per CTA (one TMEM lane per row)
 constexpr int BN = 256;      // tile cols (= UMMA N, one TMEM column per col)
 constexpr int BK = 128;      // reduction elements per stage (8-bit => 128 bytes = one swizzle row)
 constexpr int UMMA_K = 32;   // reduction elements per tcgen05.mma for 8-bit operands
-constexpr int NUM_EPI_WARPS = 8;                       // two groups of four (one warp per TMEM lane quarter); group g drains accumulator g
-constexpr int EPI_GROUP_WARPS = 4;
-constexpr int STORE_STAGE_BYTES = 32 * 128;            // per epilogue warp: 32 rows x 128 bytes, the box of one TMA store
+// Epilogue shape. The three knobs below are compile-time so that alternatives can be built side by side; the
+// defaults are what measured fastest on 16384 x 4096 x K (K = 128 .. 2048) and ties the rest at large K:
+// sixteen warps (two per lane quarter) gained nothing over eight, 64-column chunks (128-byte boxes) were 5-15 %
+// slower at K <= 2048, a second staging box per warp changed nothing (the wait for a box's read-out is short), and
+// neither did letting every warp work on every tile (EPI_GROUPS 1: half the epilogue latency per tile).
+#ifndef QT_EPI_WARPS
+#define QT_EPI_WARPS 8
+#endif
+#ifndef QT_EPI_GROUPS
+#define QT_EPI_GROUPS 2
+#endif
+#ifndef QT_EPI_CHUNK
+#define QT_EPI_CHUNK 32
+#endif
+#ifndef QT_EPI_STAGE_BUFS
+#define QT_EPI_STAGE_BUFS 1
+#endif
+constexpr int NUM_EPI_WARPS = QT_EPI_WARPS;            // two groups; group g drains accumulator g
+constexpr int EPI_GROUPS = QT_EPI_GROUPS;              // 2: the groups take alternate tiles; 1: every warp works on every tile
+constexpr int EPI_GROUP_WARPS = NUM_EPI_WARPS / EPI_GROUPS;   // four (one per TMEM lane quarter) or a multiple
+constexpr int EPI_COL_SPLIT = EPI_GROUP_WARPS / 4;     // warps sharing a lane quarter split the tile's columns between them
+constexpr int EPI_WARP_COLS = BN / EPI_COL_SPLIT;
+constexpr int EPI_CHUNK = QT_EPI_CHUNK;                // accumulator columns an epilogue warp takes per step (one TMEM load)
+constexpr int STORE_BOX_BYTES = EPI_CHUNK * 2;         // bytes per row of a staging box: one chunk of bf16 outputs, half a chunk of 4-byte ones
+constexpr int STORE_BUFS = QT_EPI_STAGE_BUFS;          // staging boxes per epilogue warp, used in turn
+constexpr int STORE_BOX_TOTAL = 32 * STORE_BOX_BYTES;  // one box: 32 rows, what one TMA store sends
+constexpr int STORE_STAGE_BYTES = STORE_BUFS * STORE_BOX_TOTAL;
+static_assert(NUM_EPI_WARPS == 8 || NUM_EPI_WARPS == 16, "epilogue warps");
+static_assert(EPI_CHUNK == 32 || EPI_CHUNK == 64, "chunk width");
+static_assert((EPI_WARP_COLS / EPI_CHUNK) % 2 == 0, "the staging boxes alternate by chunk parity");
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;   // + TMA producer warp + MMA issuer warp
 constexpr int TMEM_COLS = 512;                         // 2 accumulators x BN fp32/int32 columns
 constexpr int MAX_STAGES = 6;
@@ -307,38 +335,47 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
         }
     } else {
-        // ===== epilogue: group g (four warps, one per TMEM lane quarter) drains accumulator g, i.e. every
-        // second tile of this CTA, so two tiles are in the epilogue at a time =====
+        // ===== epilogue: two groups of warps; group g drains accumulator g, i.e. every second tile of this CTA, so
+        // two tiles are in the epilogue at a time. Inside a group a warp owns the 32 accumulator rows of its TMEM lane
+        // quarter and, when two warps share a quarter, one half of the tile's columns; it takes them in chunks of
+        // EPI_CHUNK columns. The chunk code is a chain of short latencies (TMEM load, conversions, shared-memory
+        // staging, proxy fence, TMA store) and is bound by instruction fetch and issue, so it is kept compact =====
+        const int e = warp - 2;
         const int ew = warp & 3;                          // TMEM lane quarter this warp may read
-        const int grp = (warp - 2) / EPI_GROUP_WARPS;     // accumulator buffer = parity of the CTA's tile count
+        const int grp = e / EPI_GROUP_WARPS;
+        int acc = EPI_GROUPS == 2 ? grp : 0;              // accumulator buffer = parity of the CTA's tile count
+        const int half = (e >> 2) % EPI_COL_SPLIT;        // which part of the tile's columns
         const int esz = (EPI == EPI_RAW || p.scale_dtype == QT_F32) ? 4 : 2;
-        const bool via_tma = p.tma_store != 0;
-        const uint32_t stage_addr = smem_base + C::SMEM_STORE_OFF + (uint32_t)(warp - 2) * STORE_STAGE_BYTES;
-        // this lane's row of the staging box; 16-byte piece q of the row sits at piece q ^ (row % 8)
-        // (the 128-byte swizzle the output tensor map declares): conflict-free vector stores
-        const uint32_t stage_row = stage_addr + (uint32_t)lane * 128u;
-        const uint32_t swz = (uint32_t)(lane & 7);
+        const bool via_tma = p.tma_store == 1;
+        const uint32_t stage_addr = smem_base + C::SMEM_STORE_OFF + (uint32_t)e * STORE_STAGE_BYTES;
+        // this lane's row of the staging box; 16-byte piece q of the row sits at piece q ^ (row % 8) for 128-byte rows,
+        // q ^ ((row / 2) % 4) for 64-byte rows (the swizzle the output tensor map declares): conflict-free vector stores
+        const uint32_t stage_row = stage_addr + (uint32_t)lane * (uint32_t)STORE_BOX_BYTES;
+        const uint32_t swz = STORE_BOX_BYTES == 128 ? (uint32_t)(lane & 7) : (uint32_t)((lane >> 1) & 3);
+        constexpr int PIECES = STORE_BOX_BYTES / 16;
         uint32_t acc_phase = 0;
         bool ok = true;
-        const uint32_t empty_bar_addr = CG == 2 ? map_to_cta(tmem_empty_bar(grp), 0) : tmem_empty_bar(grp);
 
-        // Scales are requested one tile ahead: this lane's row scale, and its 8 of the tile's 256 column
-        // scales. Every warp of the group then writes all 256 column scales (as fp32) to the group's
-        // shared array: the four warps write identical values, so no barrier is needed between them, and
-        // a warp only gets here after all four handed the previous accumulator back, which they do after
-        // their last read of the previous tile's scales.
-        float* cs_grp = reinterpret_cast<float*>(smem + C::SMEM_COLSCALE_OFF) + grp * BN;
-        const uint32_t cs_grp_addr = smem_base + C::SMEM_COLSCALE_OFF + (uint32_t)grp * BN * 4u;
-        float next_row_scale = 0.0f;
+        // Scales are requested one tile ahead and stay as loaded (raw bits) until the tile starts, so that nothing
+        // waits for them where they are requested: this lane's row scale, and its 8 of the tile's 256 column
+        // scales. Every warp of the group then writes all 256 column scales (as fp32) to the group's shared array:
+        // the warps write identical values, so no barrier is needed between them, and a warp only gets here after
+        // all of the group handed the previous accumulator back, which they do after their last read of the previous
+        // tile's scales.
+        const bool scale_is_bf16 = p.scale_dtype == QT_BF16;
+        uint32_t next_rs_raw = 0;          // bf16: the 16 bits as loaded; fp32: the value's bits
         uint4 next_cs[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
         bool next_cs_packed = false;
         auto request_scales = [&](const WorkItem& w) {
             const int64_t r = (int64_t)w.m * (BM * CG) + (int64_t)cta_rank * BM + ew * 32 + lane;
-            next_row_scale = (r < p.M) ? (p.scale_a ? load_scale(p.scale_a, p.scale_dtype, r) : 1.0f) : 0.0f;
+            if (r >= p.M) next_rs_raw = 0u;
+            else if (p.scale_a == nullptr) next_rs_raw = scale_is_bf16 ? 0x3F80u : 0x3F800000u;
+            else if (scale_is_bf16) next_rs_raw = __ldg(reinterpret_cast<const unsigned short*>(p.scale_a) + r);
+            else next_rs_raw = __ldg(reinterpret_cast<const uint32_t*>(p.scale_a) + r);
             next_cs_packed = load_col_scales8(next_cs, p, (int64_t)w.n * BN + lane * 8);
         };
-        uint32_t work = first_tile + (uint32_t)grp * tile_step;
-        const uint32_t work_step = 2 * tile_step;
+        uint32_t work = first_tile + (EPI_GROUPS == 2 ? (uint32_t)grp * tile_step : 0u);
+        const uint32_t work_step = (uint32_t)EPI_GROUPS * tile_step;
         WorkItem next_item = locate(work < num_work ? work : 0u);
         if constexpr (EPI == EPI_ROWCOL) {
             if (work < num_work) request_scales(next_item);
@@ -346,17 +383,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         for (; work < num_work && ok; work += work_step) {
             const WorkItem tc = next_item;
             const int split = tc.split;
-            const int64_t m0 = (int64_t)tc.m * (BM * CG) + (int64_t)cta_rank * BM, n0 = (int64_t)tc.n * BN;
+            const int64_t m0 = (int64_t)tc.m * (BM * CG) + (int64_t)cta_rank * BM;
+            const int64_t n0 = (int64_t)tc.n * BN + half * EPI_WARP_COLS;   // first column of this warp's half
             const int64_t row0 = m0 + ew * 32;
             const int64_t row = row0 + lane;
             // split-K partials go out raw, one [M][N] plane per split
             uint32_t* ws_row = (p.splits > 1 && row < p.M) ? p.ws + ((int64_t)split * p.M + row) * p.N : nullptr;
 
-            const float row_scale = next_row_scale;
-
-            ok = mbar_wait(tmem_full_bar(grp), acc_phase, s_abort, p.status, 0x400 | grp);
+            // the column scales of a tile sit in the shared array of its accumulator
+            float* cs_grp = reinterpret_cast<float*>(smem + C::SMEM_COLSCALE_OFF) + acc * BN;
+            const uint32_t cs_grp_addr = smem_base + C::SMEM_COLSCALE_OFF + (uint32_t)acc * BN * 4u;
+            const uint32_t empty_bar_addr = CG == 2 ? map_to_cta(tmem_empty_bar(acc), 0) : tmem_empty_bar(acc);
+            ok = mbar_wait(tmem_full_bar(acc), acc_phase, s_abort, p.status, 0x400 | acc);
             if (!ok) break;
             tcgen05_fence_after();
+            const float row_scale = __uint_as_float(scale_is_bf16 ? next_rs_raw << 16 : next_rs_raw);
             if constexpr (EPI == EPI_ROWCOL) {
                 if (p.splits == 1) {
                     uint4 lo = next_cs[0], hi = next_cs[1];
@@ -371,7 +412,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 }
             }
 
-            const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(grp * BN);
+            const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * BN + half * EPI_WARP_COLS);
             // hand the accumulator back to the MMA issuer (after this warp's last TMEM load has completed)
             auto release_acc = [&]() {
                 tcgen05_fence_before();
@@ -381,169 +422,179 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     else mbar_arrive(empty_bar_addr);
                 }
             };
-            // Scale (or pass through) one 32-column chunk held in registers and send it out, eight columns
-            // at a time so that few values are live at once.
-            auto emit = [&](const uint32_t (&r)[32], int c, auto odd_tag, auto last_tag) {
-                constexpr bool ODD = decltype(odd_tag)::value;    // chunk parity, known at compile time
-                constexpr bool LAST = decltype(last_tag)::value;  // the tile's last chunk
-                const int64_t n = n0 + c * 32;
-                if (ws_row != nullptr) {
-                    if (n < p.N) {
-                        uint32_t* dst = ws_row + n;
-                        if (n + 32 <= p.N && (p.N & 7) == 0) {
+            constexpr int CW = EPI_CHUNK;
+            constexpr int CHUNKS = EPI_WARP_COLS / CW;
+            uint32_t r[CW];
+            auto tmem_ld_chunk = [&](uint32_t taddr) { tmem_ld_cols(taddr, r); };
+            // The chunk loops below are real loops over compact bodies, one per output form, chosen once per tile:
+            // the epilogue is bound by instruction fetch and issue, not by arithmetic. Every form issues the next
+            // chunk's TMEM load as soon as r is free, so that it is in flight during the staging and the store.
+
+            // r (accumulator values) -> scaled outputs: 16 bf16 pairs in w (BF16) or 32 fp32 values back in r.
+            // cbase = the chunk's first column in the group's shared scale array.
+            auto scale_chunk = [&](auto csf_tag, auto bf16_tag, uint32_t (&w)[CW / 2], int cbase) {
+                constexpr bool CSF = decltype(csf_tag)::value;     // (acc * col_scale) * row_scale instead of (acc * row_scale) * col_scale
+                constexpr bool BF16 = decltype(bf16_tag)::value;
+                const float2 rs2 = make_float2(row_scale, row_scale);
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8)
-                                st_global_v8(dst + j, r[j], r[j + 1], r[j + 2], r[j + 3], r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
-                        } else {
+                for (int g = 0; g < CW / 8; ++g) {
+                    const float4 c0 = *reinterpret_cast<const float4*>(cs_grp + cbase + g * 8);      // broadcast reads
+                    const float4 c1 = *reinterpret_cast<const float4*>(cs_grp + cbase + g * 8 + 4);
+                    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (n + j < p.N) dst[j] = r[j];
-                        }
-                    }
-                    return;
-                }
-                if (p.splits > 1) return;  // a row beyond M of a split-K partial
-                // The last chunk takes its column scales into registers up front and hands the accumulator
-                // back before converting: the next tile's scales may be written once all four warps of the
-                // group are past their last read of this tile's.
-                float4 csr[(LAST && EPI == EPI_ROWCOL) ? 8 : 1];
-                if constexpr (LAST && EPI == EPI_ROWCOL) {
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) csr[q] = *reinterpret_cast<const float4*>(cs_grp + c * 32 + q * 4);
-                    // the arrive below carries no memory ordering when it crosses to the peer CTA: make it
-                    // wait for the scale values themselves (loads of one thread from shared memory return in order)
-                    asm volatile("" ::"f"(csr[0].x), "f"(csr[1].x), "f"(csr[2].x), "f"(csr[3].x), "f"(csr[4].x), "f"(csr[5].x),
-                                 "f"(csr[6].x), "f"(csr[7].w)
-                                 : "memory");
-                    release_acc();
-                }
-                // eight output values as 32-bit words: 8 words (4-byte outputs) or 4 (bf16 pairs)
-                auto convert8 = [&](uint32_t (&w)[8], int g) {
-                    if constexpr (EPI == EPI_RAW) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) w[j] = r[g * 8 + j];
-                    } else {
-                        float4 c0, c1;
-                        if constexpr (LAST) {
-                            c0 = csr[2 * g]; c1 = csr[2 * g + 1];
-                        } else {
-                            c0 = *reinterpret_cast<const float4*>(cs_grp + c * 32 + g * 8);      // broadcast reads
-                            c1 = *reinterpret_cast<const float4*>(cs_grp + c * 32 + g * 8 + 4);
-                        }
-                        const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-                        // (acc * row_scale) * col_scale, two columns per packed fp32x2 multiply
-                        float v[8];
-                        const float2 rs2 = make_float2(row_scale, row_scale);
-#pragma unroll
-                        for (int j = 0; j < 8; j += 2) {
-                            float a0 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j] : __uint_as_float(r[g * 8 + j]);
-                            float a1 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j + 1] : __uint_as_float(r[g * 8 + j + 1]);
-                            if constexpr (KIND == 2) {
-                                if (p.round_acc_first) {
-                                    const uint32_t rb = pack_bf16x2(a0, a1);
-                                    a0 = __uint_as_float(rb << 16);
-                                    a1 = __uint_as_float(rb & 0xFFFF0000u);
-                                }
+                    for (int j = 0; j < 8; j += 2) {
+                        float a0 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j] : __uint_as_float(r[g * 8 + j]);
+                        float a1 = (KIND == 0) ? (float)(int32_t)r[g * 8 + j + 1] : __uint_as_float(r[g * 8 + j + 1]);
+                        if constexpr (KIND == 2) {
+                            if (p.round_acc_first) {
+                                const uint32_t rb = pack_bf16x2(a0, a1);
+                                a0 = __uint_as_float(rb << 16);
+                                a1 = __uint_as_float(rb & 0xFFFF0000u);
                             }
-                            // fp32 multiplication is not associative: the order is the caller's (a product
-                            // computed in transposed form keeps the rounding of the untransposed one)
-                            const float2 t = p.col_scale_first ? __fmul2_rn(__fmul2_rn(make_float2(a0, a1), make_float2(cs[j], cs[j + 1])), rs2)
-                                                               : __fmul2_rn(__fmul2_rn(make_float2(a0, a1), rs2), make_float2(cs[j], cs[j + 1]));
-                            v[j] = t.x; v[j + 1] = t.y;
                         }
-                        if (esz == 2) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+                        // fp32 multiplication is not associative: the order is the caller's (a product computed in
+                        // transposed form keeps the rounding of the untransposed one). Two columns per packed multiply.
+                        const float2 cs2 = make_float2(cs[j], cs[j + 1]);
+                        const float2 t = CSF ? __fmul2_rn(__fmul2_rn(make_float2(a0, a1), cs2), rs2)
+                                             : __fmul2_rn(__fmul2_rn(make_float2(a0, a1), rs2), cs2);
+                        if constexpr (BF16) {
+                            w[g * 4 + j / 2] = pack_bf16x2(t.x, t.y);
                         } else {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) w[j] = __float_as_uint(v[j]);
-                        }
-                    }
-                };
-                if (via_tma) {
-                    // a staging box holds 128 bytes per row: one chunk of 4-byte outputs, two of bf16
-                    const bool first_of_box = esz == 4 || !ODD;
-                    const bool last_of_box = esz == 4 || ODD;
-                    if (esz == 4) {
-                        if (lane == 0) bulk_store_wait_read();   // the previous box has left shared memory
-                        __syncwarp();
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            uint32_t w[8];
-                            convert8(w, g);
-                            st_shared_v4(stage_row + (((uint32_t)(2 * g) ^ swz) << 4), w[0], w[1], w[2], w[3]);
-                            st_shared_v4(stage_row + (((uint32_t)(2 * g + 1) ^ swz) << 4), w[4], w[5], w[6], w[7]);
-                        }
-                    } else {
-                        // convert first, then wait: the previous box's store was issued just before, and
-                        // its read of the staging buffer overlaps this chunk's arithmetic
-                        uint32_t w[4][8];
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) convert8(w[g], g);
-                        if (first_of_box) {
-                            if (lane == 0) bulk_store_wait_read();
-                            __syncwarp();
-                        }
-#pragma unroll
-                        for (int g = 0; g < 4; ++g)
-                            st_shared_v4(stage_row + (((uint32_t)((ODD ? 4 : 0) + g) ^ swz) << 4), w[g][0], w[g][1], w[g][2], w[g][3]);
-                    }
-                    if (last_of_box) {
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        const int64_t nb = (esz == 4) ? n : n - 32;   // first column of the box
-                        if (lane == 0 && row0 < p.M && nb < p.N) {
-                            tma_store_2d(&tmap_c, stage_addr, (int)(nb * esz), (int)row0);
-                            bulk_store_commit();
-                        }
-                    }
-                    return;
-                }
-                // an output whose base or pitch is not 16-byte aligned: element stores (unrolled: the chunk
-                // registers must never be indexed dynamically)
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint32_t w[8];
-                    convert8(w, g);
-                    if (row < p.M) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int64_t at = row * p.ldc + n + g * 8 + j;
-                            if (n + g * 8 + j < p.N) {
-                                if (esz == 4) reinterpret_cast<uint32_t*>(p.c)[at] = w[j];
-                                else reinterpret_cast<uint16_t*>(p.c)[at] = (uint16_t)((w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu);
-                            }
+                            r[g * 8 + j] = __float_as_uint(t.x);
+                            r[g * 8 + j + 1] = __float_as_uint(t.y);
                         }
                     }
                 }
             };
-            // two register buffers: the TMEM load of chunk c+1 is in flight while chunk c goes out. The
-            // accumulator is handed back as soon as its last chunk is in registers.
-            constexpr int CHUNKS = BN / 32;
-            const bool scales_in_smem = EPI == EPI_ROWCOL && p.splits == 1;
-            uint32_t ra[32], rb[32];
-            tmem_ld_32x32(t_row, ra);
+            // after the tile's last read of the shared column scales the accumulator can go back (its last TMEM load
+            // completed before the chunk started); the arrive carries no memory ordering when it crosses to the peer
+            // CTA, so it is made to wait for values computed from those reads
+            auto release_after = [&](uint32_t a, uint32_t b, uint32_t c_, uint32_t d) {
+                asm volatile("" ::"r"(a), "r"(b), "r"(c_), "r"(d) : "memory");
+                release_acc();
+            };
+
+            tmem_ld_chunk(t_row);
             // while that load is in flight: find this group's next tile and request its scales
             if (work + work_step < num_work) {
                 next_item = locate(work + work_step);
                 if constexpr (EPI == EPI_ROWCOL) request_scales(next_item);
             }
+            if (p.splits > 1) {
+                // split-K partial: raw accumulators, this lane's row of the split's plane
 #pragma unroll 1
-            for (int c = 0; c < CHUNKS - 2; c += 2) {
-                tmem_ld_wait();
-                tmem_ld_32x32(t_row + (c + 1) * 32, rb);
-                emit(ra, c, std::false_type{}, std::false_type{});
-                tmem_ld_wait();
-                tmem_ld_32x32(t_row + (c + 2) * 32, ra);
-                emit(rb, c + 1, std::true_type{}, std::false_type{});
+                for (int c = 0; c < CHUNKS; ++c) {
+                    const int64_t n = n0 + c * CW;
+                    tmem_ld_wait();
+                    if (c == CHUNKS - 1) release_acc();
+                    if (ws_row != nullptr && n < p.N) {
+                        uint32_t* dst = ws_row + n;
+                        if (n + CW <= p.N && (p.N & 7) == 0) {
+#pragma unroll
+                            for (int j = 0; j < CW; j += 8)
+                                st_global_v8(dst + j, r[j], r[j + 1], r[j + 2], r[j + 3], r[j + 4], r[j + 5], r[j + 6], r[j + 7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < CW; ++j)
+                                if (n + j < p.N) dst[j] = r[j];
+                        }
+                    }
+                    if (c + 1 < CHUNKS) tmem_ld_chunk(t_row + (c + 1) * CW);
+                }
+            } else if (via_tma && esz == 2) {
+                // bf16 output through the staging box: one chunk = one box of 32 rows
+#pragma unroll 1
+                for (int c = 0; c < CHUNKS; ++c) {
+                    const int64_t n = n0 + c * CW;
+                    uint32_t w[CW / 2];
+                    tmem_ld_wait();
+                    if (p.col_scale_first) scale_chunk(std::true_type{}, std::true_type{}, w, half * EPI_WARP_COLS + c * CW);
+                    else scale_chunk(std::false_type{}, std::true_type{}, w, half * EPI_WARP_COLS + c * CW);
+                    if (c + 1 < CHUNKS) tmem_ld_chunk(t_row + (c + 1) * CW);
+                    else release_after(w[0], w[CW / 8 + 1], w[CW / 4 + 2], w[CW / 2 - 1]);
+                    // the previous box's store was issued a whole chunk ago: its read of the staging buffer has
+                    // overlapped this chunk's TMEM wait and arithmetic
+                    const uint32_t buf = STORE_BUFS == 2 ? (uint32_t)(c & 1) * (uint32_t)STORE_BOX_TOTAL : 0u;   // (CHUNKS is even)
+                    if (lane == 0) {
+                        if constexpr (STORE_BUFS == 2) bulk_store_wait_read_but_one();
+                        else bulk_store_wait_read();
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int g = 0; g < PIECES; ++g)
+                        st_shared_v4(stage_row + buf + (((uint32_t)g ^ swz) << 4), w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        // (a group is committed also when the box lies outside the output: the waits count groups)
+                        if (row0 < p.M && n < p.N) tma_store_2d(&tmap_c, stage_addr + buf, (int)(n * 2), (int)row0);
+                        bulk_store_commit();
+                    }
+                }
+            } else {
+                // 4-byte outputs (raw int32 / fp32, or scaled fp32): two boxes per chunk; and outputs
+                // whose base or pitch is not 16-byte aligned: element stores
+#pragma unroll 1
+                for (int c = 0; c < CHUNKS; ++c) {
+                    const int64_t n = n0 + c * CW;
+                    uint32_t w[CW / 2];
+                    tmem_ld_wait();
+                    if constexpr (EPI == EPI_ROWCOL) {
+                        if (esz == 2) {
+                            if (p.col_scale_first) scale_chunk(std::true_type{}, std::true_type{}, w, half * EPI_WARP_COLS + c * CW);
+                            else scale_chunk(std::false_type{}, std::true_type{}, w, half * EPI_WARP_COLS + c * CW);
+                        } else {
+                            if (p.col_scale_first) scale_chunk(std::true_type{}, std::false_type{}, w, half * EPI_WARP_COLS + c * CW);
+                            else scale_chunk(std::false_type{}, std::false_type{}, w, half * EPI_WARP_COLS + c * CW);
+                        }
+                        if (c == CHUNKS - 1) {
+                            if (esz == 2) release_after(w[0], w[CW / 8 + 1], w[CW / 4 + 2], w[CW / 2 - 1]);
+                            else release_after(r[0], r[CW / 4 + 1], r[CW / 2 + 2], r[CW - 1]);
+                        }
+                    } else {
+                        if (c == CHUNKS - 1) release_acc();
+                    }
+                    if (via_tma) {
+#pragma unroll
+                        for (int hb = 0; hb < 2; ++hb) {
+                            const uint32_t buf = STORE_BUFS == 2 ? (uint32_t)hb * (uint32_t)STORE_BOX_TOTAL : 0u;
+                            if (lane == 0) {
+                                if constexpr (STORE_BUFS == 2) bulk_store_wait_read_but_one();   // the box used two stores ago has left shared memory
+                                else bulk_store_wait_read();
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int g = 0; g < PIECES; ++g)
+                                st_shared_v4(stage_row + buf + (((uint32_t)g ^ swz) << 4), r[hb * (CW / 2) + 4 * g], r[hb * (CW / 2) + 4 * g + 1],
+                                             r[hb * (CW / 2) + 4 * g + 2], r[hb * (CW / 2) + 4 * g + 3]);
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            const int64_t nb = n + hb * (CW / 2);   // first column of the box
+                            if (lane == 0) {
+                                if (row0 < p.M && nb < p.N) tma_store_2d(&tmap_c, stage_addr + buf, (int)(nb * 4), (int)row0);
+                                bulk_store_commit();
+                            }
+                        }
+                    } else if (row < p.M) {
+                        // (unrolled: the chunk registers must never be indexed dynamically)
+#pragma unroll
+                        for (int j = 0; j < CW; ++j) {
+                            if (n + j < p.N) {
+                                const int64_t at = row * p.ldc + n + j;
+                                if (esz == 4) reinterpret_cast<uint32_t*>(p.c)[at] = r[j];
+                                else reinterpret_cast<uint16_t*>(p.c)[at] = (uint16_t)((w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu);
+                            }
+                        }
+                    }
+                    if (c + 1 < CHUNKS) tmem_ld_chunk(t_row + (c + 1) * CW);
+                }
             }
-            tmem_ld_wait();
-            tmem_ld_32x32(t_row + (CHUNKS - 1) * 32, rb);
-            emit(ra, CHUNKS - 2, std::false_type{}, std::false_type{});
-            tmem_ld_wait();
-            if (!scales_in_smem) release_acc();   // (the scaled epilogue releases inside its last emit)
-            emit(rb, CHUNKS - 1, std::true_type{}, std::true_type{});
-            acc_phase ^= 1u;
+            if constexpr (EPI_GROUPS == 2) {
+                acc_phase ^= 1u;
+            } else {
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
         }
         // shared memory must outlive the last store's read of it; global visibility follows at grid end
         if (via_tma && lane == 0) bulk_store_wait_all();
@@ -756,13 +807,14 @@ int gemm_dispatch(int epi, const void* a, int a_dtype, int64_t a_sm, int64_t a_s
     if (b_mn) { if (int rc = make_tmap(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)b_pitch, 128, BK)) return rc; }
     else      { if (int rc = make_tmap(&tb, b, (uint64_t)K, (uint64_t)N, (uint64_t)b_pitch, BK, (uint32_t)b_rows)) return rc; }
 
-    // the output as a byte tensor (rows of N * esz bytes): boxes of 32 rows x 128 bytes, clipped at the edges
+    // the output as a byte tensor (rows of N * esz bytes): boxes of 32 rows x STORE_BOX_BYTES, clipped at the edges
     const int esz = (epi == EPI_RAW || p.scale_dtype == QT_F32) ? 4 : 2;
     p.tma_store = (p.splits == 1 && aligned_to(p.c, 16) && (p.ldc * esz) % 16 == 0) ? 1 : 0;
     p.cs_vec = (epi == EPI_ROWCOL && aligned_to(p.scale_b, 16)) ? 1 : 0;
     CUtensorMap tc = ta;  // a valid map even when unused
     if (p.tma_store) {
-        if (int rc = make_tmap(&tc, p.c, (uint64_t)(N * esz), (uint64_t)M, (uint64_t)(p.ldc * esz), 128, 32)) return rc;
+        if (int rc = make_tmap(&tc, p.c, (uint64_t)(N * esz), (uint64_t)M, (uint64_t)(p.ldc * esz), STORE_BOX_BYTES, 32,
+                               STORE_BOX_BYTES == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)) return rc;
     }
 
     if (int rc = device_status_ptr(&p.status)) return rc;

@@ -811,11 +811,13 @@ rowwise_full_kernel(const RowwiseParams p) {
                 const float amax = __uint_as_float(__reduce_max_sync(gmask, fold_halves(m2)));
                 const float scale = scale_of(amax, qmax, rqmax);
                 const Divider2 div(fmaxf(scale, p.eps));
-                if (ok[2 * j]) {
-                    if ((t & 7) == 0) store_scale(p.scale, p.scale_dtype, (int64_t)row * (nvec >> 4) + (vpos[2 * j] >> 4), scale);
-                    dst[vpos[2 * j]] = quantize_vec8<false>(lo, div, p.q_dtype, 0, p.keys, 0);
-                    dst[vpos[2 * j + 1]] = quantize_vec8<false>(hi, div, p.q_dtype, 0, p.keys, 0);
-                }
+                // (the arithmetic runs unconditionally, on zeros where the tile lies beyond the row, so that only the
+                // stores are predicated and the loop body has no branches)
+                const uint2 qlo = quantize_vec8<false>(lo, div, p.q_dtype, 0, p.keys, 0);
+                const uint2 qhi = quantize_vec8<false>(hi, div, p.q_dtype, 0, p.keys, 0);
+                if (ok[2 * j] && (t & 7) == 0) store_scale(p.scale, p.scale_dtype, (int64_t)row * (nvec >> 4) + (vpos[2 * j] >> 4), scale);
+                if (ok[2 * j]) dst[vpos[2 * j]] = qlo;
+                if (ok[2 * j]) dst[vpos[2 * j + 1]] = qhi;
             }
         } else {
             uint32_t m2 = 0u;
@@ -840,8 +842,11 @@ rowwise_full_kernel(const RowwiseParams p) {
             const Divider2 div(fmaxf(scale, p.eps));
             if (t == 0) store_scale(p.scale, p.scale_dtype, row, scale);
 #pragma unroll
-            for (int i = 0; i < VPT; ++i)
-                if (ok[i]) dst[vpos[i]] = quantize_vec8<SR>(cur[i], div, p.q_dtype, ctr + vpos[i], p.keys, p.offset);
+            for (int i = 0; i < VPT; ++i) {
+                // (computed unconditionally, on zeros where the vector lies beyond the row: only the store is predicated)
+                const uint2 q = quantize_vec8<SR>(cur[i], div, p.q_dtype, ctr + vpos[i], p.keys, p.offset);
+                if (ok[i]) dst[vpos[i]] = q;
+            }
         }
         dst += dst_step;
         row += step;

@@ -164,17 +164,31 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // Scale blocks of B narrower than this thread's 128 columns (qn = 16, 32 or 64): one scale per
             // 16-column chunk, fetched per reduction block. Otherwise one scale serves the whole row segment.
             constexpr bool narrow = NARROW;
-            auto chunk_scale = [&](int kb, int c) {
+            // The scales of a reduction block are found by walking: element offsets of this thread's scale of A and
+            // of B advance by one stride every kq-th block (no division or 64-bit multiply per block).
+            int64_t sa_off = sa_row * p.sa_s0, sb_off = sb_col * p.sb_s1, sb_kb_off = 0;
+            int until_next = p.kq;   // blocks left under the current scales
+            auto chunk_scale = [&](int64_t kb_off, int c) {
                 const int64_t col = n0 + half * HN + c * 16;
-                return load_scale(p.scale_b, p.scale_dtype, (int64_t)(kb / p.kq) * p.sb_s0 + ((col < p.N ? col : n0) / p.qn) * p.sb_s1);
+                return load_scale(p.scale_b, p.scale_dtype, kb_off + ((col < p.N ? col : n0) / p.qn) * p.sb_s1);
+            };
+            auto block_scale = [&]() {
+                return load_scale(p.scale_a, p.scale_dtype, sa_off) * (narrow ? 1.0f : load_scale(p.scale_b, p.scale_dtype, sb_off));
             };
             // scale of K block 0, then always one block ahead
-            float s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0) * (narrow ? 1.0f : load_scale(p.scale_b, p.scale_dtype, sb_col * p.sb_s1));
+            float s_next = block_scale();
             for (int kb = 0; kb < num_kb; ++kb) {
                 const float s = s_next;
-                if (kb + 1 < num_kb)
-                    s_next = load_scale(p.scale_a, p.scale_dtype, sa_row * p.sa_s0 + (int64_t)((kb + 1) / p.kq) * p.sa_s1) *
-                             (narrow ? 1.0f : load_scale(p.scale_b, p.scale_dtype, (int64_t)((kb + 1) / p.kq) * p.sb_s0 + sb_col * p.sb_s1));
+                const int64_t sb_kb_cur = narrow ? sb_kb_off : 0;   // (narrow form: the current block's row of B scales)
+                if (kb + 1 < num_kb) {
+                    if (--until_next == 0) {
+                        until_next = p.kq;
+                        sa_off += p.sa_s1;
+                        if constexpr (narrow) sb_kb_off += p.sb_s0;
+                        else sb_off += p.sb_s0;
+                        s_next = block_scale();
+                    }
+                }
                 ok = mbar_wait(part_full_bar(buf), buf_phase, s_abort, p.status, 0x800 | buf);
                 if (!ok) break;
                 tcgen05_fence_after();
@@ -185,7 +199,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 // packed fp32x2 form (half the issue slots); measured 1.37 -> 1.56 POPS at 8192^3 against a
                 // magic-number conversion that spent a second fp32 operation per element.
                 auto promote = [&](const uint32_t (&r)[16], int c) {
-                    const float sc = narrow ? s * chunk_scale(kb, c) : s;
+                    const float sc = narrow ? s * chunk_scale(sb_kb_cur, c) : s;
                     const float2 s2 = make_float2(sc, sc);
 #pragma unroll
                     for (int j = 0; j < 16; j += 2) {

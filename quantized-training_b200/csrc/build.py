@@ -72,6 +72,41 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return OUT
 
 
+CHECK_OUT = CSRC.parent / "gn_kernels" / "libqt_b200_check.so"
+CHECKED_SOURCES = ["quantize.cu"]   # the translation units that carry store guards
+
+
+def build_checked(force: bool = False) -> Path:
+    """The debug library: the same code with -DQT_BOUNDS_CHECK on the sources that carry store guards (every
+    global store of the quantize kernels checks its address against the ranges its entry point declared and
+    reports through the device status word instead of writing outside them). The other objects are the
+    release ones, so build() runs first."""
+    build(force=False)
+    deps = [CSRC / s for s in CHECKED_SOURCES] + [CSRC / h for h in HEADERS] + [Path(__file__), OUT]
+    if not force and CHECK_OUT.exists() and all(d.stat().st_mtime <= CHECK_OUT.stat().st_mtime for d in deps):
+        return CHECK_OUT
+    nvcc = _nvcc()
+    objdir = CSRC / "build"
+    objs = []
+    for src in SOURCES:
+        if src in CHECKED_SOURCES:
+            obj = objdir / (src + ".check.o")
+            res = subprocess.run([nvcc, *NVCC_FLAGS, "-DQT_BOUNDS_CHECK", "-c", str(CSRC / src), "-o", str(obj)],
+                                 stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"nvcc failed on {src} (checked build):\n{res.stdout}")
+        else:
+            obj = objdir / (src + ".o")
+        objs.append(str(obj))
+    res = subprocess.run([nvcc, "-shared", "-o", str(CHECK_OUT), *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed (checked build):\n{res.stdout}")
+    return CHECK_OUT
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    if "--checked" in sys.argv:
+        print(build_checked(force="--force" in sys.argv))

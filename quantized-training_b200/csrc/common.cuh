@@ -126,6 +126,48 @@ __device__ __forceinline__ Philox4 philox4x32_10(uint64_t ctr, uint64_t offset, 
     return Philox4{c0, c1, c2, c3};
 }
 
+// ---- store guard (debug build) -----------------------------------------------------------------
+// With -DQT_BOUNDS_CHECK every global store of the quantize kernels first checks its address against the
+// output ranges the entry point declared for the launch. A store outside them is skipped and its site
+// recorded in the device status word (0xB00 | site), which qt_device_status reports; nothing traps. The
+// release build compiles the checks away. It covers what a memory checker would on the write side.
+#ifdef QT_BOUNDS_CHECK
+struct StoreGuard {
+    const char* lo[8];
+    const char* hi[8];
+    int n;          // ranges in use; -1 = unchecked launch (peer destinations)
+    int* status;
+    void add(const void* p, int64_t bytes) {
+        if (p != nullptr && bytes > 0 && n >= 0 && n < 8) { lo[n] = static_cast<const char*>(p); hi[n] = lo[n] + bytes; ++n; }
+    }
+    __device__ bool ok(const void* p, int bytes, int site) const {
+        if (n < 0) return true;
+        const char* c = static_cast<const char*>(p);
+        for (int i = 0; i < n; ++i)
+            if (c >= lo[i] && c + bytes <= hi[i]) return true;
+        atomicCAS(status, 0, 0xB00 | site);
+        return false;
+    }
+};
+#define QT_GUARD_FIELD ::qt::StoreGuard guard;
+#define QT_GUARD_OK(g, ptr, bytes, site) ((g).ok((ptr), (bytes), (site)))
+#define QT_GUARD_INIT(g)                                          \
+    do {                                                          \
+        (g).n = 0;                                                \
+        int* st_ = nullptr;                                       \
+        if (int rc_ = ::qt::device_status_ptr(&st_)) return rc_;  \
+        (g).status = st_;                                         \
+    } while (0)
+#define QT_GUARD_ADD(g, ptr, bytes) (g).add((ptr), (int64_t)(bytes))
+#define QT_GUARD_OFF(g) ((g).n = -1)
+#else
+#define QT_GUARD_FIELD
+#define QT_GUARD_OK(g, ptr, bytes, site) (true)
+#define QT_GUARD_INIT(g) ((void)0)
+#define QT_GUARD_ADD(g, ptr, bytes) ((void)0)
+#define QT_GUARD_OFF(g) ((void)0)
+#endif
+
 // ---- device numerics ------------------------------------------------------------------------
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
@@ -137,6 +179,13 @@ __device__ __forceinline__ void store_scale(void* scale, int scale_dtype, int64_
     else
         reinterpret_cast<float*>(scale)[idx] = v;
 }
+
+#define QT_STORE_SCALE(g, scale, scale_dtype, idx, v, site)                                                                 \
+    do {                                                                                                                    \
+        if (QT_GUARD_OK(g, static_cast<char*>(scale) + (int64_t)(idx) * ((scale_dtype) == QT_BF16 ? 2 : 4),                   \
+                        (scale_dtype) == QT_BF16 ? 2 : 4, site))                                                            \
+            ::qt::store_scale(scale, scale_dtype, idx, v);                                                                  \
+    } while (0)
 
 // One quantized byte from a pre-divided value v = x / scale.
 //   int8: round-half-even (or floor(v + u) when stochastic), clamp [-128, 127]

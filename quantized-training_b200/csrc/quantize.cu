@@ -242,6 +242,7 @@ __device__ __forceinline__ void store_bytes8(uint8_t* q, int64_t idx, int64_t va
 constexpr int kMaxScatter = 16;   // destinations of the scatter form (GPUs of one NVLink domain)
 
 struct RowwiseParams {
+    QT_GUARD_FIELD
     const void* x;
     int64_t rows, cols, stride;
     uint8_t* q;
@@ -408,8 +409,9 @@ __device__ __forceinline__ uint4 updated_vec8(uint2 qb, float s, const uint4& a,
 // shared memory. 2. The CTAs of the thread-block cluster fold through distributed shared memory; each CTA
 // owns a slice of the columns and issues one atomic max per column for the whole cluster.
 template <int TPR, int VPT>
-__device__ __forceinline__ void fold_column_maxima(uint32_t (&colmax)[VPT][4], uint32_t* s_col, int sub, int t, int64_t cols,
-                                                   float* col_absmax) {
+__device__ __forceinline__ void fold_column_maxima(uint32_t (&colmax)[VPT][4], uint32_t* s_col, int sub, int t, const RowwiseParams& p) {
+    const int64_t cols = p.cols;
+    float* col_absmax = p.col_absmax;
     constexpr int RPC = kThreads / TPR;
     constexpr int PAIRS = TPR * VPT * 4;
     if constexpr (RPC > 1) {
@@ -446,8 +448,8 @@ __device__ __forceinline__ void fold_column_maxima(uint32_t (&colmax)[VPT][4], u
         }
         const int64_t c0 = (int64_t)pair * 2;
         // fp32 bit patterns of non-negative values order like unsigned integers
-        if (c0 < cols && (m & 0xFFFFu)) atomicMax(reinterpret_cast<unsigned int*>(col_absmax + c0), m << 16);
-        if (c0 + 1 < cols && (m >> 16)) atomicMax(reinterpret_cast<unsigned int*>(col_absmax + c0 + 1), m & 0xFFFF0000u);
+        if (c0 < cols && (m & 0xFFFFu) && QT_GUARD_OK(p.guard, col_absmax + c0, 4, 27)) atomicMax(reinterpret_cast<unsigned int*>(col_absmax + c0), m << 16);
+        if (c0 + 1 < cols && (m >> 16) && QT_GUARD_OK(p.guard, col_absmax + c0 + 1, 4, 27)) atomicMax(reinterpret_cast<unsigned int*>(col_absmax + c0 + 1), m & 0xFFFF0000u);
     }
     cluster.sync();  // nobody leaves while a peer may still read its shared memory
 }
@@ -578,9 +580,9 @@ rowwise_kernel(const RowwiseParams p) {
         const Divider2 div(fmaxf(scale, p.eps));
         if constexpr (SCATTER) {
             if (valid && t == 0)
-                for (int d = 0; d < p.n_dst; ++d) store_scale(p.scale_dst[d], p.scale_dtype, p.dst_row0 + row, scale);
+                for (int d = 0; d < p.n_dst; ++d) QT_STORE_SCALE(p.guard, p.scale_dst[d], p.scale_dtype, p.dst_row0 + row, scale, 1);
         } else {
-            if (valid && t == 0) store_scale(p.scale, p.scale_dtype, row, scale);
+            if (valid && t == 0) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, row, scale, 2);
         }
 
         uint8_t* qrow = p.q + row * p.cols;
@@ -592,9 +594,10 @@ rowwise_kernel(const RowwiseParams p) {
                 const uint2 bytes = quantize_vec8<SR>(cur[i], div, p.q_dtype, (uint64_t)(idx0 + col) >> 3, p.keys, p.offset);
                 if constexpr (SCATTER) {
                     const int64_t at = (p.dst_row0 + row) * p.cols + col;
-                    for (int d = 0; d < p.n_dst; ++d) *reinterpret_cast<uint2*>(p.q_dst[d] + at) = bytes;
+                    for (int d = 0; d < p.n_dst; ++d)
+                        if (QT_GUARD_OK(p.guard, p.q_dst[d] + at, 8, 3)) *reinterpret_cast<uint2*>(p.q_dst[d] + at) = bytes;
                 } else {
-                    *reinterpret_cast<uint2*>(qrow + col) = bytes;
+                    if (QT_GUARD_OK(p.guard, qrow + col, 8, 4)) *reinterpret_cast<uint2*>(qrow + col) = bytes;
                 }
             }
         }
@@ -625,7 +628,7 @@ rowwise_kernel(const RowwiseParams p) {
         }
     }
 
-    if constexpr (COLABS) fold_column_maxima<TPR, VPT>(colmax, s_col, sub, t, p.cols, p.col_absmax);
+    if constexpr (COLABS) fold_column_maxima<TPR, VPT>(colmax, s_col, sub, t, p);
 }
 
 // ---- producer arithmetic ---------------------------------------------------------------------------
@@ -778,13 +781,13 @@ rowwise_full_kernel(const RowwiseParams p) {
             }
             const float ss = row_sum(__fadd_rn(acc.x, acc.y), parity);
             const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)p.cols), p.norm_eps));
-            if (t == 0 && p.rstd) p.rstd[row] = rstd;
+            if (t == 0 && p.rstd && QT_GUARD_OK(p.guard, p.rstd + row, 4, 5)) p.rstd[row] = rstd;
             const float2 rstd2 = make_float2(rstd, rstd);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 cur[i] = make_uint4(rmsnorm_word(cur[i].x, wv[i].x, rstd2), rmsnorm_word(cur[i].y, wv[i].y, rstd2),
                                     rmsnorm_word(cur[i].z, wv[i].z, rstd2), rmsnorm_word(cur[i].w, wv[i].w, rstd2));
-                if (ok[i]) ydst[vpos[i]] = cur[i];
+                if (ok[i] && QT_GUARD_OK(p.guard, ydst + vpos[i], 16, 6)) ydst[vpos[i]] = cur[i];
             }
             ydst += dst_step;
         }
@@ -794,7 +797,7 @@ rowwise_full_kernel(const RowwiseParams p) {
                 const uint4 u = u_buf[i];
                 cur[i] = make_uint4(silu_mul_word(cur[i].x, u.x), silu_mul_word(cur[i].y, u.y), silu_mul_word(cur[i].z, u.z),
                                     silu_mul_word(cur[i].w, u.w));
-                if (ok[i]) ydst[vpos[i]] = cur[i];
+                if (ok[i] && QT_GUARD_OK(p.guard, ydst + vpos[i], 16, 6)) ydst[vpos[i]] = cur[i];
             }
             ydst += dst_step;
         }
@@ -815,9 +818,9 @@ rowwise_full_kernel(const RowwiseParams p) {
                 // stores are predicated and the loop body has no branches)
                 const uint2 qlo = quantize_vec8<false>(lo, div, p.q_dtype, 0, p.keys, 0);
                 const uint2 qhi = quantize_vec8<false>(hi, div, p.q_dtype, 0, p.keys, 0);
-                if (ok[2 * j] && (t & 7) == 0) store_scale(p.scale, p.scale_dtype, (int64_t)row * (nvec >> 4) + (vpos[2 * j] >> 4), scale);
-                if (ok[2 * j]) dst[vpos[2 * j]] = qlo;
-                if (ok[2 * j]) dst[vpos[2 * j + 1]] = qhi;
+                if (ok[2 * j] && (t & 7) == 0) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, (int64_t)row * (nvec >> 4) + (vpos[2 * j] >> 4), scale, 7);
+                if (ok[2 * j] && QT_GUARD_OK(p.guard, dst + vpos[2 * j], 8, 8)) dst[vpos[2 * j]] = qlo;
+                if (ok[2 * j] && QT_GUARD_OK(p.guard, dst + vpos[2 * j + 1], 8, 8)) dst[vpos[2 * j + 1]] = qhi;
             }
         } else {
             uint32_t m2 = 0u;
@@ -840,12 +843,12 @@ rowwise_full_kernel(const RowwiseParams p) {
             }
             const float scale = scale_of(__uint_as_float(abits), qmax, rqmax);
             const Divider2 div(fmaxf(scale, p.eps));
-            if (t == 0) store_scale(p.scale, p.scale_dtype, row, scale);
+            if (t == 0) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, row, scale, 9);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 // (computed unconditionally, on zeros where the vector lies beyond the row: only the store is predicated)
                 const uint2 q = quantize_vec8<SR>(cur[i], div, p.q_dtype, ctr + vpos[i], p.keys, p.offset);
-                if (ok[i]) dst[vpos[i]] = q;
+                if (ok[i] && QT_GUARD_OK(p.guard, dst + vpos[i], 8, 10)) dst[vpos[i]] = q;
             }
         }
         dst += dst_step;
@@ -875,7 +878,7 @@ rowwise_full_kernel(const RowwiseParams p) {
             process(a, it & 1);
         }
     }
-    if constexpr (COLABS) fold_column_maxima<TPR, VPT>(colmax, s_col, sub, t, p.cols, p.col_absmax);
+    if constexpr (COLABS) fold_column_maxima<TPR, VPT>(colmax, s_col, sub, t, p);
 }
 
 // Any width, any alignment: one CTA per row, two passes (the second normally hits L2).
@@ -891,7 +894,9 @@ __global__ void __launch_bounds__(kThreads) rowwise_generic_kernel(const Rowwise
         for (int64_t c = threadIdx.x; c < p.cols; c += kThreads) {
             const float a = fabsf(to_float<XT>(xrow[c]));
             amax = fmaxf(amax, a);
-            if constexpr (COLABS) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c), __float_as_uint(a));
+            if constexpr (COLABS) {
+                if (QT_GUARD_OK(p.guard, p.col_absmax + c, 4, 11)) atomicMax(reinterpret_cast<unsigned int*>(p.col_absmax + c), __float_as_uint(a));
+            }
         }
         amax = warp_max(amax);
         if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
@@ -904,12 +909,12 @@ __global__ void __launch_bounds__(kThreads) rowwise_generic_kernel(const Rowwise
         __syncthreads();
         const float scale = __fdiv_rn(s_amax, qmax);
         const float d = fmaxf(scale, p.eps);
-        if (threadIdx.x == 0) store_scale(p.scale, p.scale_dtype, row, scale);
+        if (threadIdx.x == 0) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, row, scale, 12);
         for (int64_t c = threadIdx.x; c < p.cols; c += kThreads) {
             const float v = __fdiv_rn(to_float<XT>(xrow[c]), d);
             const int64_t idx = row * p.cols + c;
             const float u = p.stochastic ? uniform1(idx, p.seed, p.offset) : 0.0f;
-            p.q[idx] = (uint8_t)quantize_byte(v, p.q_dtype, p.stochastic != 0, u);
+            if (QT_GUARD_OK(p.guard, p.q + idx, 1, 13)) p.q[idx] = (uint8_t)quantize_byte(v, p.q_dtype, p.stochastic != 0, u);
         }
         __syncthreads();
     }
@@ -1064,6 +1069,11 @@ int producer_args(RowwiseParams& p, const void* x, int64_t rows, int64_t cols, i
     p.x = x; p.rows = rows; p.cols = cols; p.stride = stride;
     p.y = reinterpret_cast<__nv_bfloat16*>(y); p.q = reinterpret_cast<uint8_t*>(q); p.scale = scale; p.col_absmax = col_absmax;
     p.q_dtype = q_dtype; p.scale_dtype = scale_dtype; p.eps = eps; p.vec_load = 1; p.vec_store = 1;
+    QT_GUARD_INIT(p.guard);
+    QT_GUARD_ADD(p.guard, y, rows * cols * 2);
+    QT_GUARD_ADD(p.guard, q, rows * cols);
+    QT_GUARD_ADD(p.guard, scale, rows * (scale_dtype == QT_BF16 ? 2 : 4));
+    QT_GUARD_ADD(p.guard, col_absmax, cols * 4);
     return QT_OK;
 }
 
@@ -1098,6 +1108,10 @@ int quantize_rowwise_impl(const void* x, int x_dtype, int64_t rows, int64_t cols
     const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
     p.vec_load = aligned_to(x, 16) && ((stride * esz) % 16 == 0);
     p.vec_store = aligned_to(q, 8) && (cols % 8 == 0);
+    QT_GUARD_INIT(p.guard);
+    QT_GUARD_ADD(p.guard, q, rows * cols);
+    QT_GUARD_ADD(p.guard, scale, rows * (scale_dtype == QT_BF16 ? 2 : 4));
+    if (want_colabs) QT_GUARD_ADD(p.guard, col_absmax, cols * 4);
 
     return launch_rowwise(p, x_dtype, want_colabs, stream);
 }
@@ -1195,6 +1209,7 @@ __global__ void __launch_bounds__(kThreads) col_absmax_kernel(const XT* __restri
 // ---- column-wise quantize + transpose ---------------------------------------------------------
 
 struct ColwiseParams {
+    QT_GUARD_FIELD
     const void* x;
     int64_t rows, cols, stride;
     int64_t tiles_per_cta;  // consecutive 128-row tiles handled by one CTA
@@ -1234,7 +1249,7 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_kernel(const ColwisePar
         const float sc = div_rn(am, qmax);
         dsc[k] = fmaxf(sc, p.eps);
         rcp[k] = EXACT_DIV ? 0.0f : recip_rn(dsc[k]);
-        if (blockIdx.y == 0 && rq == 0 && col + k < p.cols) store_scale(p.scale, p.scale_dtype, col + k, sc);
+        if (blockIdx.y == 0 && rq == 0 && col + k < p.cols) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, col + k, sc, 14);
     }
 
     // A CTA walks `tiles_per_cta` consecutive row tiles of its column strip, so the 128-byte output
@@ -1298,9 +1313,10 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_kernel(const ColwisePar
                 const uint32_t word = tile[cc][lane];
                 uint8_t* dst = p.qt + oc * p.rows + orow0;
                 if (orow0 + 4 <= p.rows && p.vec_store) {
-                    *reinterpret_cast<uint32_t*>(dst) = word;
+                    if (QT_GUARD_OK(p.guard, dst, 4, 15)) *reinterpret_cast<uint32_t*>(dst) = word;
                 } else {
-                    for (int j = 0; j < 4 && orow0 + j < p.rows; ++j) dst[j] = (uint8_t)((word >> (8 * j)) & 0xFFu);
+                    for (int j = 0; j < 4 && orow0 + j < p.rows; ++j)
+                        if (QT_GUARD_OK(p.guard, dst + j, 1, 16)) dst[j] = (uint8_t)((word >> (8 * j)) & 0xFFu);
                 }
             }
         }
@@ -1331,7 +1347,7 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_fast_kernel(const Colwi
         const float sc = div_rn(p.col_absmax[col + k], 127.0f);
         dsc[k] = fmaxf(sc, p.eps);
         rcp[k] = recip_rn(dsc[k]);
-        if (blockIdx.y == 0 && rq == 0) store_scale(p.scale, p.scale_dtype, col + k, sc);
+        if (blockIdx.y == 0 && rq == 0) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, col + k, sc, 17);
     }
 
     const int64_t row_tiles = p.rows / kTileR;
@@ -1378,7 +1394,7 @@ __global__ void __launch_bounds__(kThreads, 3) colwise_t_fast_kernel(const Colwi
 #pragma unroll
         for (int i = 0; i < kTileC / 8; ++i) {
             const int cc = i * 8 + warp;
-            *reinterpret_cast<uint32_t*>(d) = tile[cc][lane ^ ((cc >> 5) << 2)];
+            if (QT_GUARD_OK(p.guard, d, 4, 18)) *reinterpret_cast<uint32_t*>(d) = tile[cc][lane ^ ((cc >> 5) << 2)];
             d += dst_step;
         }
         dst += kTileR;
@@ -1419,12 +1435,12 @@ __global__ void __launch_bounds__(kThreads) colwise_kernel(const ColwiseParams p
             const int64_t c = c0 + k;
             if (c >= p.cols) break;
             const float sc = div_rn(p.col_absmax[c], qmax);
-            if (row == 0) store_scale(p.scale, p.scale_dtype, c, sc);
+            if (row == 0) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, c, sc, 19);
             if (row < p.rows) {
                 const float v = div_rn(to_float<XT>(x[row * p.stride + c]), fmaxf(sc, p.eps));
                 const int64_t at = row * p.cols + c;
                 const float u = p.stochastic ? uniform1(at, p.seed, p.offset) : 0.0f;
-                p.qt[at] = (uint8_t)quantize_byte(v, p.q_dtype, p.stochastic != 0, u);
+                if (QT_GUARD_OK(p.guard, p.qt + at, 1, 22)) p.qt[at] = (uint8_t)quantize_byte(v, p.q_dtype, p.stochastic != 0, u);
             }
         }
     }
@@ -1433,6 +1449,7 @@ __global__ void __launch_bounds__(kThreads) colwise_kernel(const ColwiseParams p
 // ---- tile-wise ------------------------------------------------------------------------------
 
 struct TileParams {
+    QT_GUARD_FIELD
     const void* x;
     int64_t rows, cols, stride;
     uint8_t* q;
@@ -1495,7 +1512,7 @@ __global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p
             const float sc = div_rn(amax, qmax);
             const Divider<EXACT_DIV> div(fmaxf(sc, p.eps));
             if (row < p.rows && col < p.cols) {
-                if (l16 == 0) store_scale(p.scale, p.scale_dtype, row * p.scale_cols + (col >> 7), sc);
+                if (l16 == 0) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, row * p.scale_cols + (col >> 7), sc, 23);
                 uint2 bytes;
                 if constexpr (sizeof(XT) == 2 && !EXACT_DIV) {
                     bytes = quantize_vec8<false>(v[j].raw, Divider2(div.d, div.r, div.d, div.r), p.q_dtype, 0, PhiloxKeys{}, 0);
@@ -1503,7 +1520,8 @@ __global__ void __launch_bounds__(kThreads) tile_1x128_kernel(const TileParams p
                     divide8(f, div, p.q_dtype != QT_I8);
                     bytes = pack8(f, p.q_dtype, false, zero_u);
                 }
-                store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
+                if (QT_GUARD_OK(p.guard, p.q + row * p.cols + col, (int)((p.cols - col) < 8 ? (p.cols - col) : 8), 20))
+                    store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
             }
         }
 #pragma unroll
@@ -1544,7 +1562,7 @@ __global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams
     for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, s_red[w]);
     const float sc = __fdiv_rn(amax, qmax);
     const Divider<EXACT_DIV> div(fmaxf(sc, p.eps));
-    if (threadIdx.x == 0) store_scale(p.scale, p.scale_dtype, tile_r * p.scale_cols + tile_c, sc);
+    if (threadIdx.x == 0) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, tile_r * p.scale_cols + tile_c, sc, 24);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int64_t row = tile_r * 128 + r16 + 16 * i;
@@ -1558,7 +1576,8 @@ __global__ void __launch_bounds__(kThreads) tile_128x128_kernel(const TileParams
                 divide8(f, div, p.q_dtype != QT_I8);
                 bytes = pack8(f, p.q_dtype, false, zero_u);
             }
-            store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
+            if (QT_GUARD_OK(p.guard, p.q + row * p.cols + col, (int)((p.cols - col) < 8 ? (p.cols - col) : 8), 21))
+                store_bytes8(p.q, row * p.cols + col, p.cols - col, bytes, p.vec_store != 0);
         }
     }
 }
@@ -1594,11 +1613,12 @@ __global__ void __launch_bounds__(kThreads, 2) tile_128x128_fast_kernel(const Ti
         for (int w = 1; w < kThreads / 32; ++w) { const uint32_t o = s_red[parity][w]; abits = o > abits ? o : abits; }
         const float sc = scale_of(__uint_as_float(abits), qmax, rqmax);
         const Divider2 div(fmaxf(sc, p.eps));
-        if (threadIdx.x == 0) store_scale(p.scale, p.scale_dtype, (int64_t)tr * p.scale_cols + tc, sc);
+        if (threadIdx.x == 0) QT_STORE_SCALE(p.guard, p.scale, p.scale_dtype, (int64_t)tr * p.scale_cols + tc, sc, 25);
         uint8_t* dst = p.q + ((int64_t)tr * 128 + r16) * p.cols + (int64_t)tc * 128 + c16 * 8;
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<uint2*>(dst + (int64_t)i * 16 * p.cols) = quantize_vec8<false>(v[i], div, p.q_dtype, 0, PhiloxKeys{}, 0);
+            if (QT_GUARD_OK(p.guard, dst + (int64_t)i * 16 * p.cols, 8, 26))
+                *reinterpret_cast<uint2*>(dst + (int64_t)i * 16 * p.cols) = quantize_vec8<false>(v[i], div, p.q_dtype, 0, PhiloxKeys{}, 0);
     };
 
     uint4 a[8], b[8];
@@ -1733,6 +1753,9 @@ extern "C" int qt_quantize_colwise_t(const void* x, int x_dtype, int64_t rows, i
     const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
     p.vec_load = aligned_to(x, 16) && ((x_row_stride * esz) % 16 == 0);
     p.vec_store = aligned_to(qt_out, 4) && (rows % 4 == 0);
+    QT_GUARD_INIT(p.guard);
+    QT_GUARD_ADD(p.guard, qt_out, rows * cols);
+    QT_GUARD_ADD(p.guard, scale, cols * (scale_dtype == QT_BF16 ? 2 : 4));
     const int64_t col_tiles = (cols + kTileC - 1) / kTileC;
     int64_t row_tiles = (rows + kTileR - 1) / kTileR;
     if (row_tiles < 1) row_tiles = 1;  // rows == 0 still writes the (zero) scales
@@ -1774,6 +1797,9 @@ extern "C" int qt_quantize_colwise(const void* x, int x_dtype, int64_t rows, int
     p.x = x; p.rows = rows; p.cols = cols; p.stride = x_row_stride; p.col_absmax = col_absmax;
     p.qt = reinterpret_cast<uint8_t*>(q); p.scale = scale; p.q_dtype = q_dtype; p.scale_dtype = scale_dtype;
     p.eps = eps; p.stochastic = stochastic; p.seed = seed; p.offset = offset;
+    QT_GUARD_INIT(p.guard);
+    QT_GUARD_ADD(p.guard, q, rows * cols);
+    QT_GUARD_ADD(p.guard, scale, cols * (scale_dtype == QT_BF16 ? 2 : 4));
     const int64_t work = (rows > 0 ? rows : 1) * ((cols + 7) / 8);
     const int64_t want = (work + kThreads - 1) / kThreads, cap = (int64_t)num_sms() * 8;
     const unsigned grid = (unsigned)(want < cap ? want : cap);
@@ -1798,11 +1824,17 @@ extern "C" int qt_quantize_tile(const void* x, int x_dtype, int64_t rows, int64_
     const size_t esz = x_dtype == QT_BF16 ? 2 : 4;
     p.vec_load = aligned_to(x, 16) && ((x_row_stride * esz) % 16 == 0);
     p.vec_store = aligned_to(q, 8) && (cols % 8 == 0);
+    QT_GUARD_INIT(p.guard);
+    QT_GUARD_ADD(p.guard, q, rows * cols);
+    QT_GUARD_ADD(p.guard, scale, ((rows + tile_r - 1) / tile_r) * p.scale_cols * (scale_dtype == QT_BF16 ? 2 : 4));
     const bool fast = x_dtype == QT_BF16 && eps >= 1e-30f && p.vec_load && p.vec_store && cols % 128 == 0;
     if (tile_r == 1 && fast && cols <= 16384 && rows < ((int64_t)1 << 30)) {
         RowwiseParams rp = {};
         rp.x = x; rp.rows = rows; rp.cols = cols; rp.stride = x_row_stride; rp.q = p.q; rp.scale = scale;
         rp.q_dtype = q_dtype; rp.scale_dtype = scale_dtype; rp.eps = eps;
+        QT_GUARD_INIT(rp.guard);
+        QT_GUARD_ADD(rp.guard, q, rows * cols);
+        QT_GUARD_ADD(rp.guard, scale, rows * p.scale_cols * (scale_dtype == QT_BF16 ? 2 : 4));
         int rc = -1;
         if (cols <= 512) rc = launch_tile_1x128<32, 2>(rp, stream);
         else if (cols <= 1024) rc = launch_tile_1x128<32, 4>(rp, stream);
@@ -1853,6 +1885,7 @@ extern "C" int qt_rmsnorm_quantize(const void* x, int64_t rows, int64_t cols, in
     QT_REQUIRE(weight, "rmsnorm_quantize: weight is null");
     if (!aligned_to(weight, 16)) return fail(QT_ERR_UNSUPPORTED, "rmsnorm_quantize: weight must be 16-byte aligned");
     p.w_norm = reinterpret_cast<const __nv_bfloat16*>(weight); p.norm_eps = norm_eps; p.rstd = rstd;
+    QT_GUARD_ADD(p.guard, rstd, rows * 4);
     return launch_producer<1>(p, stream);
 }
 
@@ -1891,6 +1924,8 @@ extern "C" int qt_quantize_rowwise_scatter(const void* x, int x_dtype, int64_t r
     p.q_dtype = q_dtype; p.scale_dtype = scale_dtype; p.eps = eps; p.vec_load = 1; p.vec_store = 1;
     p.n_dst = n_dst; p.dst_row0 = dst_row0;
     for (int d = 0; d < n_dst; ++d) { p.q_dst[d] = reinterpret_cast<uint8_t*>(q_dst[d]); p.scale_dst[d] = scale_dst[d]; }
+    QT_GUARD_INIT(p.guard);
+    QT_GUARD_OFF(p.guard);   // up to 16 gathered buffers, most of them in peers' memory: this launch is not range-checked
     return launch_rowwise_bf16<false, false, 0, true>(p, reinterpret_cast<cudaStream_t>(stream_));
 }
 
@@ -1912,6 +1947,9 @@ extern "C" int qt_int8_weight_update(void* q, void* scale, int64_t rows, int64_t
     p.q_dtype = QT_I8; p.scale_dtype = QT_BF16; p.eps = eps; p.stochastic = 1;
     p.seed = seed; p.offset = offset; p.keys = philox_keys(seed); p.vec_load = 1; p.vec_store = 1;
     p.t1 = reinterpret_cast<const __nv_bfloat16*>(t1); p.t2 = reinterpret_cast<const __nv_bfloat16*>(t2); p.value = value;
+    QT_GUARD_INIT(p.guard);
+    QT_GUARD_ADD(p.guard, q, rows * cols);
+    QT_GUARD_ADD(p.guard, scale, rows * 2);
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     return mode == 0 ? launch_rowwise_bf16<false, true, 1>(p, stream) : launch_rowwise_bf16<false, true, 2>(p, stream);
 }

@@ -42,6 +42,17 @@ def test_library_exports_every_declared_symbol(lib):
     assert set(_native.SIGNATURES) <= set(declared_symbols())
 
 
+def test_debug_library_with_store_guards_exports_the_same_symbols(lib):
+    """build() also makes the -DQT_BOUNDS_CHECK library that the GPU store-guard test runs beside this one."""
+    from gn_kernels import _native
+
+    path = Path(_native.__file__).resolve().parent / "libqt_b200_check.so"
+    assert path.exists(), "build() did not produce the debug library"
+    chk = ctypes.CDLL(str(path))
+    for name in declared_symbols():
+        assert hasattr(chk, name), f"{name} missing from the debug library"
+
+
 def test_version_and_error_strings(lib):
     assert b"sm_100a" in lib.qt_version()
     assert isinstance(lib.qt_last_error(), bytes)

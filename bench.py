@@ -304,16 +304,16 @@ def run_reference(args, rank: int):
         return
     size = args.size
     # A full 8192^3 pass is seconds of CPU work. The requested warm-up and step counts are honoured as far
-    # as a budget of about two minutes allows: one pass is timed first, and the counts are cut to fit.
+    # as a time limit of about two minutes allows: one pass is timed first, and the counts are cut to fit.
     t0 = time.perf_counter()
     time_cpu_path(size, 1, 0)
     one = time.perf_counter() - t0
-    budget_passes = max(2, int(75.0 / max(one, 1e-3)))
-    warmup = max(0, min(args.warmup, budget_passes // 4))
-    steps = max(1, min(args.steps, budget_passes - warmup))
+    passes_that_fit = max(2, int(75.0 / max(one, 1e-3)))
+    warmup = max(0, min(args.warmup, passes_that_fit // 4))
+    steps = max(1, min(args.steps, passes_that_fit - warmup))
     tops, threads, dt = time_cpu_path(size, steps, warmup)
     sample = (f"{steps} full passes of the {size}^3 workload after {warmup + 1} warm-up passes "
-              f"(requested --steps {args.steps} --warmup {args.warmup}; cut to a 75 s budget at {one:.1f} s per pass)")
+              f"(requested --steps {args.steps} --warmup {args.warmup}; cut to fit 75 s at {one:.1f} s per pass)")
     line = {
         "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup + 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

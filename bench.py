@@ -75,6 +75,7 @@ def parse_args():
     ap.add_argument("--lead-in-seconds", type=float, default=0.25, help="--workload sweep: untimed replays of a case before it is timed")
     ap.add_argument("--plain-launches", action="store_true", help="--workload quantize: plain launches instead of CUDA-graph replays (for a profiler run)")
     ap.add_argument("--only", default=None, help="--workload quantize: only the kernels whose name contains this text")
+    ap.add_argument("--no-triton-comparator", action="store_true", help="--workload sweep: skip the Triton comparator beside the scaled matmuls")
     ap.add_argument("--no-clock-sampler", action="store_true", help="do not run nvidia-smi beside the timed region")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0, help="keep warming up at least this long (0 under a profiler)")
     return ap.parse_args()
@@ -728,6 +729,104 @@ def quantize_lines(M: int, K: int, launches: int, dev, graph: bool = True, only:
     return out
 
 
+_TRITON_COMPARATOR = None
+
+
+def _triton_scaled_mm_comparator():
+    """A Triton row/column-scaled INT8 / FP8 matmul of the usual tiled form (program per output tile, grouped
+    rasterisation, K loop of tl.dot, scales applied to the accumulator in the epilogue) -- the structure of the
+    kernel the reference runs (kernels/gn_kernels/triton_mm.py:146-220), written here from that description.
+    A comparator for the sweep only: nothing in the product imports Triton. Returns fn(A, B, sa, sb) -> bf16
+    [M, N] that tries a few tile shapes on first use and keeps the fastest, or None when Triton is unusable."""
+    global _TRITON_COMPARATOR
+    if _TRITON_COMPARATOR is not None:
+        return _TRITON_COMPARATOR or None
+    try:
+        import triton
+        import triton.language as tl
+    except Exception:   # noqa: BLE001
+        _TRITON_COMPARATOR = False
+        return None
+
+    @triton.jit
+    def kernel(a_ptr, b_ptr, c_ptr, sa_ptr, sb_ptr, M, N, K, sam, sak, sbk, sbn, scm, scn,
+               BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr, GROUP_M: tl.constexpr, INT8: tl.constexpr):
+        pid = tl.program_id(0)
+        tiles_m = tl.cdiv(M, BM)
+        tiles_n = tl.cdiv(N, BN)
+        width = GROUP_M * tiles_n
+        group = pid // width
+        first_m = group * GROUP_M
+        group_size = min(tiles_m - first_m, GROUP_M)
+        pid_m = first_m + (pid % width) % group_size
+        pid_n = (pid % width) // group_size
+        offs_m = pid_m * BM + tl.arange(0, BM)
+        offs_n = pid_n * BN + tl.arange(0, BN)
+        offs_k = tl.arange(0, BK)
+        a_ptrs = a_ptr + offs_m[:, None] * sam + offs_k[None, :] * sak
+        b_ptrs = b_ptr + offs_k[:, None] * sbk + offs_n[None, :] * sbn
+        if INT8:
+            acc = tl.zeros((BM, BN), dtype=tl.int32)
+        else:
+            acc = tl.zeros((BM, BN), dtype=tl.float32)
+        for _ in range(0, tl.cdiv(K, BK)):   # the sweep's sizes are multiples of every tile shape tried
+            a = tl.load(a_ptrs)
+            b = tl.load(b_ptrs)
+            if INT8:
+                acc = tl.dot(a, b, acc, out_dtype=tl.int32)
+            else:
+                acc = tl.dot(a, b, acc)
+            a_ptrs += BK * sak
+            b_ptrs += BK * sbk
+        sa = tl.load(sa_ptr + offs_m).to(tl.float32)
+        sb = tl.load(sb_ptr + offs_n).to(tl.float32)
+        out = acc.to(tl.float32) * sa[:, None] * sb[None, :]
+        tl.store(c_ptr + offs_m[:, None] * scm + offs_n[None, :] * scn, out.to(tl.bfloat16))
+
+    configs = [(128, 256, 128, 3, 8), (128, 128, 128, 4, 4), (256, 128, 128, 3, 8), (128, 256, 64, 4, 8), (128, 128, 64, 4, 4)]
+    best = {}
+
+    def run(A, B, sa, sb, cfg=None):
+        M, K = A.shape
+        N = B.shape[1]
+        key = (M, N, K, A.dtype, A.stride(), B.stride())
+        C = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+
+        def launch(c):
+            bm, bn, bk, stages, warps = c
+            grid = (triton.cdiv(M, bm) * triton.cdiv(N, bn),)
+            kernel[grid](A, B, C, sa, sb, M, N, K, A.stride(0), A.stride(1), B.stride(0), B.stride(1), C.stride(0), C.stride(1),
+                         BM=bm, BN=bn, BK=bk, GROUP_M=8, INT8=(A.dtype == torch.int8), num_stages=stages, num_warps=warps)
+
+        if key not in best:
+            timed, why = [], "no tile shape divides the problem"
+            for c in configs:
+                if M % c[0] or N % c[1] or K % c[2]:
+                    continue
+                try:
+                    launch(c)
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(5):
+                        launch(c)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    timed.append((e0.elapsed_time(e1), c))
+                except Exception as exc:   # noqa: BLE001 -- a tile shape this Triton cannot compile or fit
+                    why = f"{type(exc).__name__}: {str(exc)[-300:]}"
+                    continue
+            if not timed:
+                raise RuntimeError(f"no Triton tile shape compiled ({why})")
+            best[key] = min(timed)[1]
+        launch(best[key])
+        return C
+
+    run.best = best
+    _TRITON_COMPARATOR = run
+    return run
+
+
 def run_sweep(args):
     """The reference's GEMM benchmark grid (benchmark_mm.py:33-34,70-145): M = N = K in {1024, 2048, 4096, 8192}
     x layouts {A@B.T, A@B, A.T@B} x {int8_mm, row-scaled INT8, row-scaled FP8 e4m3, tile-scaled INT8, tile-scaled
@@ -792,6 +891,20 @@ def run_sweep(args):
                         line["library"] = {"what": lib_name, "tops": round(2.0 * M * N * K / (lms * 1e-3) / 1e12, 1), "us_per_launch": round(lms * 1e3, 2)}
                     except Exception as exc:   # a layout or shape the library refuses
                         line["library"] = {"what": lib_name, "unavailable": f"{type(exc).__name__}: {str(exc)[:120]}"}
+                if name.startswith("scaled_mm") and not args.no_triton_comparator:
+                    tri = _triton_scaled_mm_comparator()
+                    ops = (A8, B8) if "int8" in name else (Af, Bf)
+                    if tri is None:
+                        line["triton_comparator"] = {"unavailable": "import triton failed"}
+                    else:
+                        try:
+                            tms = _time_graph(lambda i: tri(ops[0][i], ops[1][i], sa, sb), n_sets, launches, lead_in_s=args.lead_in_seconds)
+                            cfg = tri.best.get((M, N, K, ops[0][0].dtype, ops[0][0].stride(), ops[1][0].stride()))
+                            line["triton_comparator"] = {"what": "own Triton restatement of the reference's scaled matmul (comparator only)",
+                                                         "tops": round(2.0 * M * N * K / (tms * 1e-3) / 1e12, 1), "us_per_launch": round(tms * 1e3, 2),
+                                                         "tile_stages_warps": list(cfg) if cfg else None}
+                        except Exception as exc:   # noqa: BLE001
+                            line["triton_comparator"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}
                 print(json.dumps(line), flush=True)
             del A8, B8, Af, Bf
             torch.cuda.empty_cache()

@@ -3,11 +3,15 @@
 //     acc[m,n] += fp32(partial[m,n]) * scale_a[m / qm, kb] * scale_b[kb, n / qn]
 // which is the loop of the reference's _tile_scaled_mm_kernel (kernels/gn_kernels/triton_mm.py:314-331).
 //
-// One persistent CTA per SM owns 128 x 256 tiles; 10 warps: TMA producer, MMA issuer, eight promotion /
-// epilogue warps that keep the fp32 accumulator (128 values per thread: one row, 128 columns, i.e. one
-// scale block of B) in registers. TMEM holds two 256-column partial buffers, so the tensor core works
-// on the next K block while the current one is promoted. The promotion (one convert + one fused multiply-add per element per K
-// block) is what bounds this kernel, not the tensor pipe. All waits are bounded.
+// One persistent CTA per SM owns 128 x 256 tiles; 12 warps in three warpgroups: the first holds the TMA
+// producer and the MMA issuer (its other two warps idle), the other two are the eight promotion / epilogue
+// warps that keep the fp32 accumulator (128 values per thread: one row, 128 columns, i.e. one scale block of
+// B) in registers. TMEM holds two 256-column partial buffers, so the tensor core works on the next K block
+// while the current one is promoted. The promotion (one convert + one fused multiply-add per element per K
+// block) is what bounds this kernel, not the tensor pipe: a TMEM load takes a couple of hundred cycles to
+// return, so a warp needs a large chunk in flight while it promotes the previous one. The registers for that
+// (128 accumulators + two 32-column chunks) come from the first warpgroup, which gives most of its share
+// back (setmaxnreg). All waits are bounded.
 #include "tcgen05.cuh"
 
 namespace qt {
@@ -20,8 +24,22 @@ constexpr int TBM = 128, TBN = 256, TBK = 128;
 constexpr int T_UMMA_K = 32;
 constexpr int T_STAGES = 4;
 constexpr int T_A_BYTES = TBM * TBK, T_B_BYTES = TBN * TBK, T_STAGE_BYTES = T_A_BYTES + T_B_BYTES;
-constexpr int T_EPI_WARPS = 8;                   // two promotion warps per TMEM lane quarter, 128 columns each
-constexpr int T_THREADS = 64 + 32 * T_EPI_WARPS;
+#ifndef QT_TILE_EPI_WARPS
+#define QT_TILE_EPI_WARPS 8
+#endif
+// promotion warps: 8 (two per TMEM lane quarter, 128 columns each) or 16 (four, 64 columns each; measured 5-15 % slower:
+// the chunks halve and the accumulators spill at 112 registers)
+constexpr int T_EPI_WARPS = QT_TILE_EPI_WARPS;
+constexpr int T_COL_PARTS = T_EPI_WARPS / 4;
+constexpr int T_WARP_COLS = TBN / T_COL_PARTS;   // columns of the tile a promotion warp owns
+constexpr int T_CHUNK = T_WARP_COLS / 4;         // a reduction block is promoted in four chunks
+static_assert(T_EPI_WARPS == 8 || T_EPI_WARPS == 16, "promotion warps");
+constexpr int T_FIRST_EPI_WARP = 4;              // warps 0..3: producer, MMA issuer and two idle warps (one warpgroup)
+constexpr int T_THREADS = 32 * (T_FIRST_EPI_WARP + T_EPI_WARPS);
+// registers per thread after the warpgroups rebalance: 128 x 56 + 256 x 224 = 64512, or 128 x 24 + 512 x 112 = 60416,
+// of the SM's 65536. Slack is deliberate: with 32 / 120 (all 65536, every scheduler's 16384 exactly) the increase
+// never completed and the kernel hung, and setmaxnreg has no timeout.
+constexpr int T_REGS_SMALL = T_EPI_WARPS == 8 ? 56 : 24, T_REGS_LARGE = T_EPI_WARPS == 8 ? 224 : 112;
 constexpr int T_BUFS = 2;                       // TMEM partial buffers of TBN columns
 constexpr int T_TMEM_COLS = T_BUFS * TBN;       // 512
 constexpr int T_SMEM_BAR_OFF = T_STAGES * T_STAGE_BYTES;
@@ -43,7 +61,7 @@ struct TileGemmParams {
     int* status;
 };
 
-// NARROW: the scale blocks of B are narrower than a thread's 128 columns (qn = 16, 32, 64); the common wide case
+// NARROW: the scale blocks of B are narrower than a thread's columns (qn = 16, 32, 64 against 128); the common wide case
 // keeps its own instantiation (the extra scale fetches cost registers the promotion loop has none to spare of).
 template <int KIND, bool A_MN, bool B_MN, bool NARROW>
 __global__ void __launch_bounds__(T_THREADS, 1)
@@ -81,6 +99,9 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem_ptr;
 
+    if (warp < T_FIRST_EPI_WARP) {
+    // the first warpgroup hands registers back before its warps take their roles
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(T_REGS_SMALL));
     if (warp == 0) {
         // ===== TMA producer =====
         int stage = 0;
@@ -144,11 +165,14 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (++buf == T_BUFS) { buf = 0; buf_phase ^= 1u; }
             }
         }
+    }
     } else {
-        // ===== promotion + epilogue: thread = one row x 64 columns, fp32 accumulators in registers =====
+        // ===== promotion + epilogue: thread = one row x 128 columns, fp32 accumulators in registers =====
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(T_REGS_LARGE));
         const int ew = warp & 3;
-        const int half = (warp - 2) >> 2;
-        constexpr int HN = TBN / 2;
+        const int half = (warp - T_FIRST_EPI_WARP) >> 2;
+        constexpr int HN = T_WARP_COLS;
+        constexpr int CW = T_CHUNK;
         int buf = 0;
         uint32_t buf_phase = 0;
         bool ok = true;
@@ -172,13 +196,26 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int64_t col = n0 + half * HN + c * 16;
                 return load_scale(p.scale_b, p.scale_dtype, kb_off + ((col < p.N ? col : n0) / p.qn) * p.sb_s1);
             };
-            auto block_scale = [&]() {
-                return load_scale(p.scale_a, p.scale_dtype, sa_off) * (narrow ? 1.0f : load_scale(p.scale_b, p.scale_dtype, sb_off));
+            // The scales are requested one block ahead and kept as loaded (raw bits): decoding or multiplying them
+            // where they are requested would make the warp wait there for the loads, once per block.
+            const bool scale_is_bf16 = p.scale_dtype == QT_BF16;
+            auto load_raw = [&](const void* base, int64_t off) -> uint32_t {
+                return scale_is_bf16 ? (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(base) + off)
+                                     : __ldg(reinterpret_cast<const uint32_t*>(base) + off);
             };
-            // scale of K block 0, then always one block ahead
-            float s_next = block_scale();
+            auto decode = [&](uint32_t raw) { return __uint_as_float(scale_is_bf16 ? raw << 16 : raw); };
+            uint32_t sa_raw = load_raw(p.scale_a, sa_off), sb_raw = narrow ? 0u : load_raw(p.scale_b, sb_off);
+            // Chunks of a quarter of the warp's columns through two register buffers: the next TMEM load is in flight while the current
+            // chunk is promoted, and the first chunk of the NEXT reduction block is requested before the last chunk
+            // of this one is promoted, so a block does not start with a barrier wait and an exposed TMEM load.
+            uint32_t ra[CW], rb[CW];
+            auto partial_row = [&](int b) { return tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(b * TBN + half * HN); };
+            ok = mbar_wait(part_full_bar(buf), buf_phase, s_abort, p.status, 0x800 | buf);
+            if (!ok) break;
+            tcgen05_fence_after();
+            tmem_ld_cols(partial_row(buf), ra);
             for (int kb = 0; kb < num_kb; ++kb) {
-                const float s = s_next;
+                const float s = decode(sa_raw) * (narrow ? 1.0f : decode(sb_raw));
                 const int64_t sb_kb_cur = narrow ? sb_kb_off : 0;   // (narrow form: the current block's row of B scales)
                 if (kb + 1 < num_kb) {
                     if (--until_next == 0) {
@@ -186,46 +223,52 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         sa_off += p.sa_s1;
                         if constexpr (narrow) sb_kb_off += p.sb_s0;
                         else sb_off += p.sb_s0;
-                        s_next = block_scale();
+                        sa_raw = load_raw(p.scale_a, sa_off);
+                        if constexpr (!narrow) sb_raw = load_raw(p.scale_b, sb_off);
                     }
                 }
-                ok = mbar_wait(part_full_bar(buf), buf_phase, s_abort, p.status, 0x800 | buf);
-                if (!ok) break;
-                tcgen05_fence_after();
-                const uint32_t t_row = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(buf * TBN + half * HN);
-                // 16-column chunks through two register buffers: the next TMEM load is in flight while
-                // the current chunk is promoted. The fp32 pipe bounds this loop, so the int8 partial is
-                // converted by the integer-to-float instruction (another pipe) and the multiply-add is the
-                // packed fp32x2 form (half the issue slots); measured 1.37 -> 1.56 POPS at 8192^3 against a
-                // magic-number conversion that spent a second fp32 operation per element.
-                auto promote = [&](const uint32_t (&r)[16], int c) {
-                    const float sc = narrow ? s * chunk_scale(sb_kb_cur, c) : s;
-                    const float2 s2 = make_float2(sc, sc);
+                const uint32_t t_row = partial_row(buf);
+                // The int8 partial is converted by the integer-to-float instruction (not the fp32 pipe) and the
+                // multiply-add is the packed fp32x2 form (half the issue slots); measured 1.37 -> 1.56 POPS at 8192^3
+                // against a magic-number conversion that spent a second fp32 operation per element.
+                auto promote = [&](const uint32_t (&r)[CW], int c) {
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        float2 x;
-                        if constexpr (KIND == 0)
-                            x = make_float2((float)(int32_t)r[j], (float)(int32_t)r[j + 1]);
-                        else
-                            x = make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                        acc2[c * 8 + j / 2] = __ffma2_rn(x, s2, acc2[c * 8 + j / 2]);
+                    for (int h = 0; h < CW / 16; ++h) {
+                        const float sc = narrow ? s * chunk_scale(sb_kb_cur, (CW / 16) * c + h) : s;
+                        const float2 s2 = make_float2(sc, sc);
+#pragma unroll
+                        for (int j = 0; j < 16; j += 2) {
+                            float2 x;
+                            if constexpr (KIND == 0)
+                                x = make_float2((float)(int32_t)r[h * 16 + j], (float)(int32_t)r[h * 16 + j + 1]);
+                            else
+                                x = make_float2(__uint_as_float(r[h * 16 + j]), __uint_as_float(r[h * 16 + j + 1]));
+                            acc2[c * (CW / 2) + h * 8 + j / 2] = __ffma2_rn(x, s2, acc2[c * (CW / 2) + h * 8 + j / 2]);
+                        }
                     }
                 };
-                uint32_t ra[16], rb[16];
-                tmem_ld_32x16(t_row, ra);
-#pragma unroll
-                for (int c = 0; c < HN / 16; c += 2) {
-                    tmem_ld_wait();
-                    tmem_ld_32x16(t_row + (c + 1) * 16, rb);
-                    promote(ra, c);
-                    tmem_ld_wait();
-                    if (c + 2 < HN / 16) tmem_ld_32x16(t_row + (c + 2) * 16, ra);
-                    promote(rb, c + 1);
-                }
+                tmem_ld_wait();
+                tmem_ld_cols(t_row + CW, rb);
+                promote(ra, 0);
+                tmem_ld_wait();
+                tmem_ld_cols(t_row + 2 * CW, ra);
+                promote(rb, 1);
+                tmem_ld_wait();
+                tmem_ld_cols(t_row + 3 * CW, rb);
+                promote(ra, 2);
+                tmem_ld_wait();
+                // every value of this partial is in registers (the wait above is warp-wide): the buffer goes back to
+                // the tensor core
                 tcgen05_fence_before();
-                __syncwarp();
                 if (lane == 0) mbar_arrive(part_empty_bar(buf));
                 if (++buf == T_BUFS) { buf = 0; buf_phase ^= 1u; }
+                if (kb + 1 < num_kb) {
+                    ok = mbar_wait(part_full_bar(buf), buf_phase, s_abort, p.status, 0x800 | buf);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    tmem_ld_cols(partial_row(buf), ra);
+                }
+                promote(rb, 3);
             }
             if (!ok) break;
             float acc[HN];
@@ -282,7 +325,7 @@ int launch_tile(const CUtensorMap& ta, const CUtensorMap& tb, const TileGemmPara
 template <int KIND>
 int launch_tile_layout(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const TileGemmParams& p, uint32_t idesc,
                        int grid, cudaStream_t stream) {
-    if (p.qn < TBN / 2) {
+    if (p.qn < T_WARP_COLS) {
         if (!a_mn && !b_mn) return launch_tile<KIND, false, false, true>(ta, tb, p, idesc, grid, stream);
         if (!a_mn && b_mn) return launch_tile<KIND, false, true, true>(ta, tb, p, idesc, grid, stream);
         if (a_mn && b_mn) return launch_tile<KIND, true, true, true>(ta, tb, p, idesc, grid, stream);

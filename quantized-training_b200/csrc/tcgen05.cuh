@@ -41,6 +41,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking probe of a phase (no suspend-time hint): what a wait tries first, since on the hot paths the
+// phase has usually completed long before it is asked for.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Records `code` in the device status block (first code wins) and copies it to the pinned host word whose
 // device-visible address sits 8 bytes into the block, so the host sees it without synchronising.
 __device__ __forceinline__ void record_status(int* status, int code) {
@@ -61,7 +75,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                                           unsigned long long limit_ns = WAIT_LIMIT_NS) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
     // the limit is wall time, not a poll count: it holds whether or not the hardware honours the hint
     const unsigned long long t0 = global_timer_ns();
     for (uint32_t i = 0;; ++i) {
@@ -241,6 +255,7 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x16(taddr, r); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---- descriptors ----------------------------------------------------------------------------

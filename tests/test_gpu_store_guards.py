@@ -21,7 +21,13 @@ CHECK_LIB = Path(nv.__file__).resolve().parent / "libqt_b200_check.so"
 @pytest.fixture(scope="module")
 def libs():
     if not CHECK_LIB.exists():
-        pytest.fail(f"{CHECK_LIB.name} is missing: build it with `python quantized-training_b200/csrc/build.py --checked`")
+        # normally built beside the release library; build it here (nvcc, a minute or two) when it is not
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location("qt_b200_build", CHECK_LIB.parents[1] / "csrc" / "build.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build_checked()
     chk = ctypes.CDLL(str(CHECK_LIB))
     for name, (res, args) in nv.SIGNATURES.items():
         fn = getattr(chk, name)

@@ -240,6 +240,31 @@ def test_tile_scaled_mm_infers_other_block_shapes(blocks, kind):
     assert nv.device_status() == 0
 
 
+@pytest.mark.parametrize("mnk", [(2304, 4096, 128), (2304, 4096, 256), (200, 384, 384), (2500, 3968, 512)])
+@pytest.mark.parametrize("kind", ["int8", "e4m3"])
+def test_tile_scaled_mm_many_tiles_per_cta_short_reductions_and_ragged_edges(mnk, kind):
+    """More tiles than SMs (a CTA walks several tiles, the partial buffers and their phases carry over from one
+    tile to the next), reductions of one to four blocks (the request for the next block's first chunk has
+    nothing to ask for at the last block), and M / N that end inside a tile."""
+    M, N, K = mnk
+    g = torch.Generator().manual_seed(M + N + K)
+    if kind == "int8":
+        A, B = rand_i8((M, K), 71), rand_i8((K, N), 72)
+    else:
+        A = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn).cuda()
+        B = torch.randn(K, N, generator=g).to(torch.float8_e4m3fn).cuda()
+    sa = (torch.rand(M, K // 128, generator=g) / 64 + 1e-3).bfloat16().cuda()
+    sb = (torch.rand(K // 128, N // 128, generator=g) / 64 + 1e-3).bfloat16().cuda()
+    out = gn_kernels.scaled_mm(A, B.T.contiguous().T, sa, sb)
+    a_np = A.cpu().numpy() if kind == "int8" else bits_of(A)
+    b_np = B.cpu().numpy() if kind == "int8" else bits_of(B)
+    want = om.tile_scaled_mm(a_np, b_np, values_of(sa), values_of(sb), kind=kind)
+    np.testing.assert_allclose(values_of(out), want, rtol=1e-2 if kind == "int8" else 1.6e-2, atol=1e-4)
+    assert nv.device_status() == 0
+    out2 = gn_kernels.scaled_mm(A, B.T.contiguous().T, sa, sb)
+    assert torch.equal(out, out2)
+
+
 @pytest.mark.parametrize("mnk", [(1024, 1024, 32768), (256, 256, 8192), (2048, 256, 16384), (300, 520, 12288), (128, 256, 8192)])
 @pytest.mark.parametrize("layout", ["A@B.T", "A.T@B"])
 def test_split_k_is_bit_exact(mnk, layout, cta_group):

@@ -76,6 +76,7 @@ def parse_args():
     ap.add_argument("--plain-launches", action="store_true", help="--workload quantize: plain launches instead of CUDA-graph replays (for a profiler run)")
     ap.add_argument("--only", default=None, help="--workload quantize: only the kernels whose name contains this text")
     ap.add_argument("--no-triton-comparator", action="store_true", help="--workload sweep: skip the Triton comparator beside the scaled matmuls")
+    ap.add_argument("--no-gemm-variants", action="store_true", help="leave the other GEMM forms (FP8, tile-scaled, other layouts) out of the N=1 line")
     ap.add_argument("--no-clock-sampler", action="store_true", help="do not run nvidia-smi beside the timed region")
     ap.add_argument("--min-warmup-seconds", type=float, default=1.0, help="keep warming up at least this long (0 under a profiler)")
     return ap.parse_args()
@@ -910,6 +911,55 @@ def run_sweep(args):
             torch.cuda.empty_cache()
 
 
+def gemm_variant_lines(dev, size: int = 8192, launches: int = 10, lead_in_s: float = 0.15) -> list:
+    """The other GEMM forms of the path at size^3, for the default line: raw INT8, row-scaled INT8 in the two other
+    layouts, row-scaled FP8, tile-scaled INT8 and FP8 (A@B.T unless the name says otherwise). Same timing as the
+    sweep (CUDA-graph replays over rotating operand sets, a short loaded lead-in); fractions against twice the
+    measured bf16 burst and against the nominal dense rate."""
+    import gn_kernels
+
+    _, bf16_peak, peak_kind = measured_peaks()
+    peak = 2.0 * bf16_peak
+    S = size
+    n_sets = 3
+
+    def col(t):
+        return t.T.contiguous().T
+
+    A8 = [torch.randint(-128, 128, (S, S), dtype=torch.int8, device=dev) for _ in range(n_sets)]
+    B8 = [torch.randint(-128, 128, (S, S), dtype=torch.int8, device=dev) for _ in range(n_sets)]
+    sa = (torch.rand(S, 1, device=dev) * 0.01 + 0.001).bfloat16()
+    sb = (torch.rand(1, S, device=dev) * 0.01 + 0.001).bfloat16()
+    ta = (torch.rand(S, S // 128, device=dev) * 0.01 + 0.001).bfloat16()
+    tb = (torch.rand(S // 128, S // 128, device=dev) * 0.01 + 0.001).bfloat16()
+    out = []
+
+    def add(name, fn):
+        try:
+            ms = _time_graph(fn, n_sets, launches, lead_in_s=lead_in_s)
+            tops = 2.0 * S ** 3 / (ms * 1e-3) / 1e12
+            out.append({"kernel": name, "size": S, "tops": round(tops, 1), "us_per_launch": round(ms * 1e3, 1),
+                        "frac_of_2x_measured_bf16": round(tops / peak, 3), "frac_of_nominal_4500": round(tops / NOMINAL_INT8_DENSE_TOPS, 3)})
+        except Exception as exc:   # noqa: BLE001 -- a missing entry must not lose the line
+            out.append({"kernel": name, "size": S, "error": f"{type(exc).__name__}: {str(exc)[:160]}"})
+
+    Bt = [col(b) for b in B8]                                    # [K, N] with K contiguous: A@B.T
+    add("int8_mm A@B.T (int32 out)", lambda i: gn_kernels.int8_mm(A8[i], Bt[i]))
+    add("scaled_mm int8 A@B", lambda i: gn_kernels.scaled_mm(A8[i], B8[i], sa, sb))
+    At = [col(a) for a in A8]
+    add("scaled_mm int8 A.T@B", lambda i: gn_kernels.scaled_mm(At[i], B8[i], sa, sb))
+    del At
+    add("tile_scaled_mm int8 (1x128, 128x128) A@B.T", lambda i: gn_kernels.scaled_mm(A8[i], Bt[i], ta, tb))
+    Af = [a.to(torch.bfloat16).mul_(0.01).to(torch.float8_e4m3fn) for a in A8]
+    Bf = [col(b.to(torch.bfloat16).mul_(0.01).to(torch.float8_e4m3fn)) for b in B8]
+    del A8, B8, Bt
+    add("scaled_mm e4m3 A@B.T", lambda i: gn_kernels.scaled_mm(Af[i], Bf[i], sa, sb))
+    add("tile_scaled_mm e4m3 (1x128, 128x128) A@B.T", lambda i: gn_kernels.scaled_mm(Af[i], Bf[i], ta, tb))
+    out.append({"timed_as": f"CUDA-graph replays of {launches} launches over {n_sets} operand sets, {lead_in_s} s loaded lead-in, median of 5",
+                "peak": peak, "peak_is": f"2 x {peak_kind} dense bf16 burst"})
+    return out
+
+
 def run_quantize(args):
     """The HBM-bound kernels of the path on one [M, K] bf16 tensor (--mnk M N K; N is ignored; default
     32768 x 2048, the activation of a 2048-wide layer at 32768 tokens): one JSON line per kernel."""
@@ -1322,6 +1372,10 @@ def main():
         del A, W, out
         torch.cuda.empty_cache()
         line["quantize"] = quantize_lines(32768, 2048, 20, dev)
+    if world == 1 and not args.no_gemm_variants and (gM, gN, gK) == (8192, 8192, 8192):
+        # the path's other GEMM forms at the same size (FP8, tile-scaled, the other layouts, raw INT8)
+        torch.cuda.empty_cache()
+        line["gemm_variants"] = gemm_variant_lines(dev)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
